@@ -1,0 +1,99 @@
+"""ctypes binding of ``libgmb200.so`` (declarations: ``include/gm_b200.h``).
+
+The library is the only compute path of this package.  :func:`lib` raises a
+``RuntimeError`` when the shared object is absent or fails to load; nothing
+falls back to PyTorch or to a CPU implementation.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import functools
+from pathlib import Path
+from typing import Any
+
+import torch
+
+LIBRARY = Path(__file__).resolve().parent / "libgmb200.so"
+ABI_VERSION = 1
+
+GM_F32, GM_F64, GM_BF16 = 0, 1, 2
+_DTYPES = {torch.float32: GM_F32, torch.float64: GM_F64, torch.bfloat16: GM_BF16}
+
+_P, _I, _L, _D = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_double
+
+#: name -> argument ctypes, in the order of include/gm_b200.h
+SIGNATURES: dict[str, list[Any]] = {
+    "gm_softmax_forward": [_P] * 8 + [_L, _L, _I, _I, _I, _I, _D, _L, _I, _P, _P],
+    "gm_softmax_backward": [_P] * 10 + [_L, _L, _I, _I, _I, _I, _D, _L, _I, _P, _P, _P],
+    "gm_conv_forward": [_P] * 10 + [_L, _L, _I, _I, _I, _I, _I, _I, _P, _P],
+    "gm_conv_backward": [_P] * 11 + [_L, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P],
+    "gm_attention_forward": [_P] * 9 + [_L, _L, _L, _I, _I, _I, _I, _D, _I, _P, _P, _P],
+    "gm_attention_backward": [_P] * 12 + [_L, _L, _L, _I, _I, _I, _I, _D, _I, _P, _P, _P, _P, _P],
+}
+#: entry points that return a size instead of a status
+SIZE_QUERIES: dict[str, list[Any]] = {
+    "gm_attention_backward_scratch_bytes": [_L, _L, _I, _I],
+}
+
+
+@functools.cache
+def lib() -> ctypes.CDLL:
+    """Load the shared library once and declare every entry point."""
+    if not LIBRARY.exists():
+        raise RuntimeError(
+            f"{LIBRARY} is missing: build it with `python -m gm_attention_b200.build` "
+            "(this package has no CPU or PyTorch fallback)"
+        )
+    handle = ctypes.CDLL(str(LIBRARY))
+    handle.gm_abi_version.restype = ctypes.c_int
+    handle.gm_last_error.restype = ctypes.c_char_p
+    if handle.gm_abi_version() != ABI_VERSION:
+        raise RuntimeError(f"{LIBRARY} has ABI {handle.gm_abi_version()}, this package expects {ABI_VERSION}: rebuild it")
+    for name, argtypes in SIGNATURES.items():
+        fn = getattr(handle, name)
+        fn.argtypes = argtypes
+        fn.restype = ctypes.c_int
+    for name, argtypes in SIZE_QUERIES.items():
+        fn = getattr(handle, name)
+        fn.argtypes = argtypes
+        fn.restype = ctypes.c_int64
+    return handle
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPES[dtype]
+    except KeyError:
+        raise RuntimeError(f"unsupported dtype {dtype}") from None
+
+
+def ptr(tensor: torch.Tensor | None) -> int | None:
+    """Device address of a tensor's first element (``None`` for an absent or empty tensor)."""
+    if tensor is None or tensor.numel() == 0:
+        return None
+    return tensor.data_ptr()
+
+
+def stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def call(name: str, *args: Any) -> None:
+    """Invoke an entry point; a non-zero status becomes ``RuntimeError`` with the library's message."""
+    handle = lib()
+    status = getattr(handle, name)(*args)
+    if status != 0:
+        message = handle.gm_last_error().decode(errors="replace")
+        raise RuntimeError(f"{name} failed ({status}): {message}")
+
+
+def require_cuda(*tensors: torch.Tensor) -> torch.device:
+    """All tensors on one CUDA device; that device is returned."""
+    device = tensors[0].device
+    if device.type != "cuda":
+        raise RuntimeError("gm_attention_b200 runs on CUDA tensors only (there is no CPU path)")
+    for t in tensors:
+        if t.device != device:
+            raise RuntimeError("every tensor must live on the same device")
+    return device

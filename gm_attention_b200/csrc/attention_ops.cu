@@ -1,0 +1,450 @@
+// Op-level kernels behind the reference extension's four attention entry
+// points: scores + neighbourhood softmax (forward, backward) and the depthwise
+// steerable convolution under given weights (forward, backward).
+//
+// Semantics follow src/gm_attention/nn/fused/attention.h of the reference
+// (scores :145-165, softmax :295-316, softmax backward :320-348, depthwise
+// message :174-206, its backward :211-232); the kernels themselves are new:
+//
+//  * scores: one block per target, one WARP per edge with the lanes striding
+//    the key row (coalesced 128-byte reads of k_j), per-head sums by warp
+//    shuffle; the row's logits live in shared memory (or, for very large
+//    neighbourhoods, in the alpha output itself) and are normalised there.
+//  * every per-column walk (softmax backward, conv forward/backward) runs one
+//    thread per flat column with the column's slot (frequency, head, copy,
+//    real/imaginary part, partner column) decoded ONCE per block into shared
+//    memory instead of once per (column, edge).
+#include "common.cuh"
+
+namespace gmb {
+namespace {
+
+constexpr int MAX_H = 8;
+constexpr int MAX_F = 8;
+constexpr int DESC = 5;
+
+// One flat column's slot. order < 0: the column belongs to no descriptor row.
+struct ColumnSlot {
+  int16_t order;    // frequency n (0: scalar)
+  int16_t head;     // head owning the column
+  int16_t partner;  // +1 for a real part, -1 for an imaginary part, 0 for a scalar
+  int16_t copy;     // copy index within the head, a
+  int16_t mult;     // copies per head, a_n
+  int16_t coff;     // coefficient offset of the frequency
+};
+
+__device__ __forceinline__ ColumnSlot decode_column(const int64_t* desc, int F, int H, int c) {
+  ColumnSlot s{-1, 0, 0, 0, 0, 0};
+  for (int f = 0; f < F; ++f) {
+    const int64_t* row = desc + f * DESC;
+    const int n = (int)row[0], a_n = (int)row[1], off = (int)row[2], dim = (int)row[4];
+    if (c >= off && c < off + H * a_n * dim) {
+      const int local = c - off, copy = local / dim, part = local % dim;
+      s.order = (int16_t)n;
+      s.head = (int16_t)(copy / a_n);
+      s.copy = (int16_t)(copy % a_n);
+      s.mult = (int16_t)a_n;
+      s.coff = (int16_t)row[3];
+      s.partner = (int16_t)(dim == 1 ? 0 : (part == 0 ? 1 : -1));
+      return s;
+    }
+  }
+  return s;
+}
+
+// ------------------------------------------------------------------ softmax
+
+template <typename T>
+struct SoftmaxArgs {
+  const T *q, *k, *transport, *bias, *alpha_in, *dalpha;
+  const uint8_t* inside;
+  const int64_t *desc, *row_ptr, *source;
+  T *alpha, *dq, *dk;
+  int64_t n_nodes;
+  int D, F, orders, H;
+  int slots;  // shared-memory logit slots per block (0: keep the logits in alpha)
+  T scale;
+};
+
+constexpr int SM_THREADS = 128;
+
+template <typename T>
+__global__ void __launch_bounds__(SM_THREADS) softmax_forward_kernel(SoftmaxArgs<T> a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* q_s = reinterpret_cast<T*>(smem_raw);
+  T* logit_s = q_s + a.D;
+  __shared__ int d_n[MAX_F], d_mult[MAX_F], d_off[MAX_F];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = SM_THREADS / 32;
+  if (threadIdx.x < a.F) {
+    d_n[threadIdx.x] = (int)a.desc[threadIdx.x * DESC + 0];
+    d_mult[threadIdx.x] = (int)a.desc[threadIdx.x * DESC + 1];
+    d_off[threadIdx.x] = (int)a.desc[threadIdx.x * DESC + 2];
+  }
+  for (int64_t i = blockIdx.x; i < a.n_nodes; i += gridDim.x) {
+    const int64_t e0 = a.row_ptr[i], e1 = a.row_ptr[i + 1];
+    const int deg = (int)(e1 - e0);
+    __syncthreads();  // the previous node's reads of q_s / logit_s are done (and d_* are written)
+    if (deg == 0) continue;
+    for (int c = threadIdx.x; c < a.D; c += SM_THREADS) q_s[c] = a.q[i * a.D + c];
+    T* logits = (deg * a.H <= a.slots) ? logit_s : a.alpha + e0 * a.H;
+    __syncthreads();
+    for (int t = warp; t < deg; t += n_warps) {
+      const int64_t e = e0 + t, j = a.source[e];
+      const T* k_j = a.k + j * a.D;
+      const T* tau_e = a.transport + e * a.orders * 2;
+      const T bias = a.bias[e];
+      for (int h = 0; h < a.H; ++h) {
+        T acc = T(0);
+        for (int f = 0; f < a.F; ++f) {
+          const int n = d_n[f], a_n = d_mult[f];
+          if (n == 0) {
+            const int base = d_off[f] + h * a_n;
+            for (int u = lane; u < a_n; u += 32) acc += q_s[base + u] * k_j[base + u];
+          } else {
+            const T tr = tau_e[2 * n], ti = tau_e[2 * n + 1];
+            const int base = d_off[f] + 2 * h * a_n;
+            for (int u = lane; u < a_n; u += 32) {
+              const T kr = k_j[base + 2 * u], ki = k_j[base + 2 * u + 1];
+              acc += q_s[base + 2 * u] * (tr * kr - ti * ki) + q_s[base + 2 * u + 1] * (tr * ki + ti * kr);
+            }
+          }
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) logits[t * a.H + h] = a.scale * acc + bias;
+      }
+    }
+    __syncthreads();
+    for (int h = warp; h < a.H; h += n_warps) {
+      T m = neg_inf<T>();
+      for (int t = lane; t < deg; t += 32) {
+        const T lw = logits[t * a.H + h];
+        if (a.inside[e0 + t] && lw > m) m = lw;  // masked edges never set the shift
+      }
+      m = warp_max(m);
+      T sum = T(0);
+      for (int t = lane; t < deg; t += 32) {
+        const T u = a.inside[e0 + t] ? gm_exp(logits[t * a.H + h] - m) : T(0);
+        logits[t * a.H + h] = u;
+        sum += u;
+      }
+      sum = warp_sum(sum);
+      for (int t = lane; t < deg; t += 32) a.alpha[(e0 + t) * a.H + h] = logits[t * a.H + h] / sum;
+    }
+  }
+}
+
+template <typename T>
+__global__ void softmax_backward_kernel(SoftmaxArgs<T> a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* q_s = reinterpret_cast<T*>(smem_raw);
+  T* total_s = q_s + a.D;  // MAX_H
+  ColumnSlot* slot_s = reinterpret_cast<ColumnSlot*>(total_s + MAX_H);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  for (int c = threadIdx.x; c < a.D; c += blockDim.x) slot_s[c] = decode_column(a.desc, a.F, a.H, c);
+  for (int64_t i = blockIdx.x; i < a.n_nodes; i += gridDim.x) {
+    const int64_t e0 = a.row_ptr[i], e1 = a.row_ptr[i + 1];
+    __syncthreads();
+    for (int c = threadIdx.x; c < a.D; c += blockDim.x) q_s[c] = a.q[i * a.D + c];
+    for (int h = warp; h < a.H; h += n_warps) {
+      T total = T(0);
+      for (int64_t e = e0 + lane; e < e1; e += 32) total += a.alpha_in[e * a.H + h] * a.dalpha[e * a.H + h];
+      total = warp_sum(total);
+      if (lane == 0) total_s[h] = total;
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < a.D; c += blockDim.x) {
+      const ColumnSlot s = slot_s[c];
+      T dq = T(0);
+      if (s.order >= 0) {
+        const T total = total_s[s.head];
+        const T sign = s.partner > 0 ? T(-1) : T(1);
+        const T q_c = q_s[c], q_p = q_s[c + s.partner];
+        for (int64_t e = e0; e < e1; ++e) {
+          const T al = a.alpha_in[e * a.H + s.head];
+          const T ds = a.scale * al * (a.dalpha[e * a.H + s.head] - total);
+          const int64_t j = a.source[e];
+          const T* k_j = a.k + j * a.D;
+          if (s.order == 0) {
+            dq += ds * k_j[c];
+            atomicAdd(a.dk + j * a.D + c, ds * q_c);
+          } else {
+            const T tr = a.transport[(e * a.orders + s.order) * 2], ti = a.transport[(e * a.orders + s.order) * 2 + 1];
+            dq += ds * (tr * k_j[c] + sign * ti * k_j[c + s.partner]);  // (tau k)[c]
+            atomicAdd(a.dk + j * a.D + c, ds * (tr * q_c - sign * ti * q_p));  // (conj(tau) q)[c]
+          }
+        }
+      }
+      a.dq[i * a.D + c] = dq;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ depthwise conv
+
+template <typename T>
+struct ConvArgs {
+  const T *v, *rc, *cc, *transport, *angular, *rho, *weights, *g;
+  const int64_t *desc, *row_ptr, *source;
+  T *out, *dv, *drc, *dcc;
+  int64_t n_nodes;
+  int D, F, orders, A0, W;
+};
+
+template <typename T>
+__device__ __forceinline__ T rho_power(T rho, int n) {  // (r / c)^{2n} by repeated multiplication from 1
+  T s = T(1);
+  for (int i = 0; i < 2 * n; ++i) s *= rho;
+  return s;
+}
+
+template <typename T>
+__global__ void conv_forward_kernel(ConvArgs<T> a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  ColumnSlot* slot_s = reinterpret_cast<ColumnSlot*>(smem_raw);
+  for (int c = threadIdx.x; c < a.D; c += blockDim.x) slot_s[c] = decode_column(a.desc, a.F, 1, c);
+  __syncthreads();
+  for (int64_t i = blockIdx.x; i < a.n_nodes; i += gridDim.x) {
+    const int64_t e0 = a.row_ptr[i], e1 = a.row_ptr[i + 1];
+    for (int c = threadIdx.x; c < a.D; c += blockDim.x) {
+      const ColumnSlot s = slot_s[c];
+      T y = T(0);
+      if (s.order == 0) {
+        for (int64_t e = e0; e < e1; ++e) y += a.weights[e] * (a.rc[e * a.A0 + s.copy] * a.v[a.source[e] * a.D + c]);
+      } else if (s.order > 0) {
+        const int n = s.order, re = s.partner > 0 ? c : c - 1;
+        for (int64_t e = e0; e < e1; ++e) {
+          const T* v_j = a.v + a.source[e] * a.D;
+          const T tr = a.transport[(e * a.orders + n) * 2], ti = a.transport[(e * a.orders + n) * 2 + 1];
+          const T vr = v_j[re], vi = v_j[re + 1];
+          const T zr = tr * vr - ti * vi, zi = tr * vi + ti * vr;  // z = tau v
+          const T* co = a.cc + e * a.W + s.coff;
+          const T Ar = co[2 * s.copy], Ai = co[2 * s.copy + 1];
+          const T Br = co[2 * s.mult + 2 * s.copy], Bi = co[2 * s.mult + 2 * s.copy + 1];
+          const T p = rho_power(a.rho[e], n);
+          const T wr = p * a.angular[(e * a.orders + 2 * n) * 2], wi = p * a.angular[(e * a.orders + 2 * n) * 2 + 1];
+          // m = A z + w (B conj z)
+          const T bzr = Br * zr + Bi * zi, bzi = Bi * zr - Br * zi;
+          const T mr = (Ar * zr - Ai * zi) + (wr * bzr - wi * bzi);
+          const T mi = (Ar * zi + Ai * zr) + (wr * bzi + wi * bzr);
+          y += a.weights[e] * (s.partner > 0 ? mr : mi);
+        }
+      }
+      a.out[i * a.D + c] = y;
+    }
+  }
+}
+
+template <typename T>
+__global__ void conv_backward_kernel(ConvArgs<T> a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* dy_s = reinterpret_cast<T*>(smem_raw);
+  ColumnSlot* slot_s = reinterpret_cast<ColumnSlot*>(dy_s + a.D);
+  for (int c = threadIdx.x; c < a.D; c += blockDim.x) slot_s[c] = decode_column(a.desc, a.F, 1, c);
+  for (int64_t i = blockIdx.x; i < a.n_nodes; i += gridDim.x) {
+    const int64_t e0 = a.row_ptr[i], e1 = a.row_ptr[i + 1];
+    __syncthreads();
+    for (int c = threadIdx.x; c < a.D; c += blockDim.x) dy_s[c] = a.g[i * a.D + c];
+    __syncthreads();
+    for (int c = threadIdx.x; c < a.D; c += blockDim.x) {
+      const ColumnSlot s = slot_s[c];
+      if (s.order == 0) {
+        const T dy = dy_s[c];
+        for (int64_t e = e0; e < e1; ++e) {
+          const int64_t j = a.source[e];
+          const T dm = a.weights[e] * dy;
+          a.drc[e * a.A0 + s.copy] = dm * a.v[j * a.D + c];
+          atomicAdd(a.dv + j * a.D + c, dm * a.rc[e * a.A0 + s.copy]);
+        }
+      } else if (s.order > 0) {
+        const int n = s.order, re = s.partner > 0 ? c : c - 1;
+        const bool real_part = s.partner > 0;
+        const T dyr = dy_s[re], dyi = dy_s[re + 1];
+        for (int64_t e = e0; e < e1; ++e) {
+          const int64_t j = a.source[e];
+          const T* v_j = a.v + j * a.D;
+          const T tr = a.transport[(e * a.orders + n) * 2], ti = a.transport[(e * a.orders + n) * 2 + 1];
+          const T vr = v_j[re], vi = v_j[re + 1];
+          const T zr = tr * vr - ti * vi, zi = tr * vi + ti * vr;
+          const int64_t ci = e * a.W + s.coff + 2 * s.copy;
+          const T Ar = a.cc[ci], Ai = a.cc[ci + 1];
+          const T Br = a.cc[ci + 2 * s.mult], Bi = a.cc[ci + 2 * s.mult + 1];
+          const T p = rho_power(a.rho[e], n);
+          const T wr = p * a.angular[(e * a.orders + 2 * n) * 2], wi = p * a.angular[(e * a.orders + 2 * n) * 2 + 1];
+          const T w_e = a.weights[e];
+          const T dmr = w_e * dyr, dmi = w_e * dyi;
+          // dA = dm conj(z); dB = (dm conj(w)) z
+          const T dAr = dmr * zr + dmi * zi, dAi = dmi * zr - dmr * zi;
+          const T cr = dmr * wr + dmi * wi, ci2 = dmi * wr - dmr * wi;
+          const T dBr = cr * zr - ci2 * zi, dBi = cr * zi + ci2 * zr;
+          a.dcc[ci + (real_part ? 0 : 1)] = real_part ? dAr : dAi;
+          a.dcc[ci + 2 * s.mult + (real_part ? 0 : 1)] = real_part ? dBr : dBi;
+          // dz = conj(A) dm + w (B conj(dm)); dv = conj(tau) dz
+          const T bdr = Br * dmr + Bi * dmi, bdi = Bi * dmr - Br * dmi;
+          const T dzr = (Ar * dmr + Ai * dmi) + (wr * bdr - wi * bdi);
+          const T dzi = (Ar * dmi - Ai * dmr) + (wr * bdi + wi * bdr);
+          const T dvr = tr * dzr + ti * dzi, dvi = tr * dzi - ti * dzr;
+          atomicAdd(a.dv + j * a.D + c, real_part ? dvr : dvi);
+        }
+      }
+    }
+  }
+}
+
+int column_threads(int D) {
+  int t = ((D + 31) / 32) * 32;
+  return t > 512 ? 512 : (t < 32 ? 32 : t);
+}
+
+int grid_for(int64_t n_nodes) { return (int)(n_nodes < (int64_t)1 << 30 ? n_nodes : (int64_t)1 << 30); }
+
+template <typename T>
+int softmax_forward_t(SoftmaxArgs<T> a, int64_t deg_max, cudaStream_t stream) {
+  // Logits in shared memory when the largest neighbourhood fits ~96 KiB; else kept in alpha.
+  const size_t budget = 96 * 1024;
+  size_t want = (size_t)deg_max * a.H;
+  if ((want + a.D) * sizeof(T) > budget) want = 0;
+  a.slots = (int)want;
+  const size_t smem = (a.D + want) * sizeof(T);
+  int status = allow_smem(softmax_forward_kernel<T>, smem, "gm_softmax_forward");
+  if (status != GM_OK) return status;
+  softmax_forward_kernel<T><<<grid_for(a.n_nodes), SM_THREADS, smem, stream>>>(a);
+  return launch_status("gm_softmax_forward");
+}
+
+template <typename T>
+int softmax_backward_t(SoftmaxArgs<T> a, cudaStream_t stream) {
+  const size_t smem = (a.D + MAX_H) * sizeof(T) + a.D * sizeof(ColumnSlot);
+  softmax_backward_kernel<T><<<grid_for(a.n_nodes), column_threads(a.D), smem, stream>>>(a);
+  return launch_status("gm_softmax_backward");
+}
+
+int check_softmax(const void* q, const void* k, const void* transport, const void* bias, const uint8_t* inside,
+                  const int64_t* desc, const int64_t* row_ptr, const int64_t* source, int64_t n_nodes, int64_t n_edges,
+                  int D, int F, int orders, int H, int dtype) {
+  GM_REQUIRE(n_nodes >= 0 && n_edges >= 0, GM_ERR_ARGUMENT, "gm_softmax: negative size");
+  GM_REQUIRE(D >= 1, GM_ERR_ARGUMENT, "gm_softmax: D must be positive");
+  GM_REQUIRE(H >= 1 && H <= MAX_H, GM_ERR_ARGUMENT, "gm_softmax: at most %d heads", MAX_H);
+  GM_REQUIRE(F >= 0 && F <= MAX_F, GM_ERR_ARGUMENT, "gm_softmax: desc must be int64 (F <= %d, %d)", MAX_F, DESC);
+  GM_REQUIRE(orders >= 1, GM_ERR_ARGUMENT, "gm_softmax: transport must be (n_edges, orders, 2)");
+  GM_REQUIRE(dtype == GM_F32 || dtype == GM_F64, GM_ERR_UNSUPPORTED, "gm_softmax: dtype must be float32 or float64");
+  if (n_nodes == 0) return GM_OK;
+  GM_REQUIRE(q && k && desc && row_ptr, GM_ERR_ARGUMENT, "gm_softmax: null pointer");
+  GM_REQUIRE(n_edges == 0 || (transport && bias && inside && source), GM_ERR_ARGUMENT, "gm_softmax: null edge table");
+  return GM_OK;
+}
+
+}  // namespace
+}  // namespace gmb
+
+using namespace gmb;
+
+extern "C" int gm_softmax_forward(const void* q, const void* k, const void* transport, const void* bias,
+                                  const uint8_t* inside, const int64_t* desc, const int64_t* row_ptr,
+                                  const int64_t* source, int64_t n_nodes, int64_t n_edges, int D, int F, int orders,
+                                  int H, double scale, int64_t deg_max, int dtype, void* alpha, void* stream) {
+  int status = check_softmax(q, k, transport, bias, inside, desc, row_ptr, source, n_nodes, n_edges, D, F, orders, H, dtype);
+  if (status != GM_OK || n_nodes == 0 || n_edges == 0) return status;
+  GM_REQUIRE(alpha, GM_ERR_ARGUMENT, "gm_softmax_forward: null alpha");
+  GM_REQUIRE(deg_max >= 1, GM_ERR_ARGUMENT, "gm_softmax_forward: deg_max must be positive");
+  auto run = [&](auto tag) {
+    using T = decltype(tag);
+    SoftmaxArgs<T> a{};
+    a.q = (const T*)q; a.k = (const T*)k; a.transport = (const T*)transport; a.bias = (const T*)bias;
+    a.inside = inside; a.desc = desc; a.row_ptr = row_ptr; a.source = source; a.alpha = (T*)alpha;
+    a.n_nodes = n_nodes; a.D = D; a.F = F; a.orders = orders; a.H = H; a.scale = (T)scale;
+    return softmax_forward_t<T>(a, deg_max, (cudaStream_t)stream);
+  };
+  return dtype == GM_F32 ? run(float()) : run(double());
+}
+
+extern "C" int gm_softmax_backward(const void* dalpha, const void* q, const void* k, const void* transport,
+                                   const void* bias, const uint8_t* inside, const int64_t* desc, const int64_t* row_ptr,
+                                   const int64_t* source, const void* alpha, int64_t n_nodes, int64_t n_edges, int D,
+                                   int F, int orders, int H, double scale, int64_t deg_max, int dtype, void* dq,
+                                   void* dk, void* stream) {
+  (void)deg_max;
+  int status = check_softmax(q, k, transport, bias, inside, desc, row_ptr, source, n_nodes, n_edges, D, F, orders, H, dtype);
+  if (status != GM_OK || n_nodes == 0) return status;
+  GM_REQUIRE(dq && dk, GM_ERR_ARGUMENT, "gm_softmax_backward: null output");
+  GM_REQUIRE(n_edges == 0 || (alpha && dalpha), GM_ERR_ARGUMENT, "gm_softmax_backward: null alpha / dalpha");
+  auto run = [&](auto tag) {
+    using T = decltype(tag);
+    SoftmaxArgs<T> a{};
+    a.q = (const T*)q; a.k = (const T*)k; a.transport = (const T*)transport; a.bias = (const T*)bias;
+    a.inside = inside; a.desc = desc; a.row_ptr = row_ptr; a.source = source;
+    a.alpha_in = (const T*)alpha; a.dalpha = (const T*)dalpha; a.dq = (T*)dq; a.dk = (T*)dk;
+    a.n_nodes = n_nodes; a.D = D; a.F = F; a.orders = orders; a.H = H; a.scale = (T)scale;
+    return softmax_backward_t<T>(a, (cudaStream_t)stream);
+  };
+  return dtype == GM_F32 ? run(float()) : run(double());
+}
+
+namespace {
+
+int check_conv(const void* v, const void* rc, const void* cc, const void* transport, const void* angular, const void* rho,
+               const void* weights, const int64_t* desc, const int64_t* row_ptr, const int64_t* source, int64_t n_nodes,
+               int64_t n_edges, int D, int F, int orders, int A0, int W, int dtype) {
+  GM_REQUIRE(n_nodes >= 0 && n_edges >= 0, GM_ERR_ARGUMENT, "gm_conv: negative size");
+  GM_REQUIRE(D >= 1, GM_ERR_ARGUMENT, "gm_conv: D must be positive");
+  GM_REQUIRE(F >= 0 && F <= MAX_F, GM_ERR_ARGUMENT, "gm_conv: desc must be int64 (F <= %d, %d)", MAX_F, DESC);
+  GM_REQUIRE(A0 >= 0 && W >= 0 && orders >= 1, GM_ERR_ARGUMENT, "gm_conv: bad widths");
+  GM_REQUIRE(dtype == GM_F32 || dtype == GM_F64, GM_ERR_UNSUPPORTED, "gm_conv: dtype must be float32 or float64");
+  if (n_nodes == 0) return GM_OK;
+  GM_REQUIRE(v && desc && row_ptr, GM_ERR_ARGUMENT, "gm_conv: null pointer");
+  if (n_edges > 0) {
+    GM_REQUIRE(transport && angular && rho && weights && source, GM_ERR_ARGUMENT, "gm_conv: null edge table");
+    GM_REQUIRE(A0 == 0 || rc, GM_ERR_ARGUMENT, "gm_conv: rc must hold (1, n_edges, a_0) entries");
+    GM_REQUIRE(W == 0 || cc, GM_ERR_ARGUMENT, "gm_conv: cc must hold (1, n_edges, W) entries");
+  }
+  return GM_OK;
+}
+
+template <typename T>
+ConvArgs<T> conv_args(const void* v, const void* rc, const void* cc, const void* transport, const void* angular,
+                      const void* rho, const void* weights, const int64_t* desc, const int64_t* row_ptr,
+                      const int64_t* source, int64_t n_nodes, int D, int F, int orders, int A0, int W) {
+  ConvArgs<T> a{};
+  a.v = (const T*)v; a.rc = (const T*)rc; a.cc = (const T*)cc; a.transport = (const T*)transport;
+  a.angular = (const T*)angular; a.rho = (const T*)rho; a.weights = (const T*)weights;
+  a.desc = desc; a.row_ptr = row_ptr; a.source = source;
+  a.n_nodes = n_nodes; a.D = D; a.F = F; a.orders = orders; a.A0 = A0; a.W = W;
+  return a;
+}
+
+}  // namespace
+
+extern "C" int gm_conv_forward(const void* v, const void* rc, const void* cc, const void* transport, const void* angular,
+                               const void* rho, const void* weights, const int64_t* desc, const int64_t* row_ptr,
+                               const int64_t* source, int64_t n_nodes, int64_t n_edges, int D, int F, int orders, int A0,
+                               int W, int dtype, void* out, void* stream) {
+  int status = check_conv(v, rc, cc, transport, angular, rho, weights, desc, row_ptr, source, n_nodes, n_edges, D, F, orders, A0, W, dtype);
+  if (status != GM_OK || n_nodes == 0) return status;
+  GM_REQUIRE(out, GM_ERR_ARGUMENT, "gm_conv_forward: null out");
+  auto run = [&](auto tag) {
+    using T = decltype(tag);
+    auto a = conv_args<T>(v, rc, cc, transport, angular, rho, weights, desc, row_ptr, source, n_nodes, D, F, orders, A0, W);
+    a.out = (T*)out;
+    conv_forward_kernel<T><<<grid_for(n_nodes), column_threads(D), D * sizeof(ColumnSlot), (cudaStream_t)stream>>>(a);
+    return launch_status("gm_conv_forward");
+  };
+  return dtype == GM_F32 ? run(float()) : run(double());
+}
+
+extern "C" int gm_conv_backward(const void* g, const void* v, const void* rc, const void* cc, const void* transport,
+                                const void* angular, const void* rho, const void* weights, const int64_t* desc,
+                                const int64_t* row_ptr, const int64_t* source, int64_t n_nodes, int64_t n_edges, int D,
+                                int F, int orders, int A0, int W, int dtype, void* dv, void* drc, void* dcc, void* stream) {
+  int status = check_conv(v, rc, cc, transport, angular, rho, weights, desc, row_ptr, source, n_nodes, n_edges, D, F, orders, A0, W, dtype);
+  if (status != GM_OK || n_nodes == 0 || n_edges == 0) return status;
+  GM_REQUIRE(g && dv, GM_ERR_ARGUMENT, "gm_conv_backward: null g / dv");
+  GM_REQUIRE((A0 == 0 || drc) && (W == 0 || dcc), GM_ERR_ARGUMENT, "gm_conv_backward: null coefficient gradient");
+  auto run = [&](auto tag) {
+    using T = decltype(tag);
+    auto a = conv_args<T>(v, rc, cc, transport, angular, rho, weights, desc, row_ptr, source, n_nodes, D, F, orders, A0, W);
+    a.g = (const T*)g; a.dv = (T*)dv; a.drc = (T*)drc; a.dcc = (T*)dcc;
+    const size_t smem = D * sizeof(T) + D * sizeof(ColumnSlot);
+    conv_backward_kernel<T><<<grid_for(n_nodes), column_threads(D), smem, (cudaStream_t)stream>>>(a);
+    return launch_status("gm_conv_backward");
+  };
+  return dtype == GM_F32 ? run(float()) : run(double());
+}

@@ -1,0 +1,134 @@
+/* libgmb200 -- C ABI of the B200 (sm_100a) fused neighbourhood kernels.
+ *
+ * Every entry point takes plain device pointers and sizes, launches on the
+ * given CUDA stream (a cudaStream_t passed as void*; NULL = the legacy default
+ * stream), never synchronises, never throws, and returns a status code:
+ *
+ *    0  GM_OK
+ *   -1  GM_ERR_ARGUMENT     a null pointer, a negative size, a shape the layout forbids
+ *   -2  GM_ERR_UNSUPPORTED  a dtype / head count / width outside the kernels' bounds
+ *   -3  GM_ERR_CUDA         the launch (or a CUDA call around it) failed
+ *   -4  GM_ERR_LIMIT        a documented fixed capacity was exceeded
+ *
+ * gm_last_error() returns the calling thread's last message.  Unless stated
+ * otherwise the caller owns every buffer; outputs documented as "accumulated"
+ * must be zeroed by the caller before the call (the Python host layer does it
+ * with one cudaMemsetAsync on the same stream).
+ *
+ * Element types: GM_F32, GM_F64 store and compute in that type; GM_BF16 stores
+ * node fields as bfloat16 and computes / accumulates in fp32 (per-edge tables
+ * are then fp32).
+ *
+ * Citations name files of the reference project masonfaldet/gm-attention by
+ * their path inside that project.
+ */
+#ifndef GM_B200_H
+#define GM_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { GM_OK = 0, GM_ERR_ARGUMENT = -1, GM_ERR_UNSUPPORTED = -2, GM_ERR_CUDA = -3, GM_ERR_LIMIT = -4 };
+enum { GM_F32 = 0, GM_F64 = 1, GM_BF16 = 2 };
+
+/* Library identity: ABI version (bumped on any signature change) and the last
+ * error message of the calling thread. */
+int gm_abi_version(void);
+const char* gm_last_error(void);
+
+/* ------------------------------------------------------------------------
+ * Scores + neighbourhood softmax (drop-in for the reference extension's
+ * softmax_forward / softmax_backward:
+ * src/gm_attention/nn/fused/attention_cpu.cpp:197-252, arithmetic
+ * src/gm_attention/nn/fused/attention.h:295-348).
+ *
+ *   q, k        (n_nodes, D)            node fields, flat layout
+ *   transport   (n_edges, orders, 2)    (cos k*gamma, sin k*gamma), k = 0..orders-1
+ *   bias        (n_edges)               log window + log quadrature weight
+ *   inside      (n_edges) uint8         window > 0
+ *   desc        (F, 5) int64            rows (n, a_n per head, flat offset, coeff offset, dim)
+ *   row_ptr     (n_nodes + 1) int64, source (n_edges) int64   target-major CSR
+ *   alpha       (n_edges, H)            out
+ *   dq          (n_nodes, D)            out (written)
+ *   dk          (n_nodes, D)            out, ACCUMULATED (zero it first)
+ * dtype: GM_F32 or GM_F64.
+ * ------------------------------------------------------------------------ */
+int gm_softmax_forward(const void* q, const void* k, const void* transport, const void* bias, const uint8_t* inside,
+                       const int64_t* desc, const int64_t* row_ptr, const int64_t* source, int64_t n_nodes,
+                       int64_t n_edges, int D, int F, int orders, int H, double scale, int64_t deg_max, int dtype,
+                       void* alpha, void* stream);
+
+int gm_softmax_backward(const void* dalpha, const void* q, const void* k, const void* transport, const void* bias,
+                        const uint8_t* inside, const int64_t* desc, const int64_t* row_ptr, const int64_t* source,
+                        const void* alpha, int64_t n_nodes, int64_t n_edges, int D, int F, int orders, int H,
+                        double scale, int64_t deg_max, int dtype, void* dq, void* dk, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Depthwise steerable convolution under given per-edge weights (drop-in for
+ * conv_forward / conv_backward: attention_cpu.cpp:94-145, arithmetic
+ * attention.h:174-232, 265-287).
+ *
+ *   v          (n_nodes, D)
+ *   rc         (n_edges, A0)   scalar coefficients R (may be NULL when A0 == 0)
+ *   cc         (n_edges, W)    per frequency n >= 1: A (a_n, 2) then B (a_n, 2) at the row's coeff offset
+ *   transport, angular (n_edges, orders, 2); rho (n_edges) = r / cutoff; weights (n_edges)
+ *   out        (n_nodes, D)    out
+ *   dv         (n_nodes, D)    out, ACCUMULATED (zero it first)
+ *   drc, dcc   shaped as rc, cc; every entry written
+ * dtype: GM_F32 or GM_F64.
+ * ------------------------------------------------------------------------ */
+int gm_conv_forward(const void* v, const void* rc, const void* cc, const void* transport, const void* angular,
+                    const void* rho, const void* weights, const int64_t* desc, const int64_t* row_ptr,
+                    const int64_t* source, int64_t n_nodes, int64_t n_edges, int D, int F, int orders, int A0, int W,
+                    int dtype, void* out, void* stream);
+
+int gm_conv_backward(const void* g, const void* v, const void* rc, const void* cc, const void* transport,
+                     const void* angular, const void* rho, const void* weights, const int64_t* desc,
+                     const int64_t* row_ptr, const int64_t* source, int64_t n_nodes, int64_t n_edges, int D, int F,
+                     int orders, int A0, int W, int dtype, void* dv, void* drc, void* dcc, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Fully fused gauge attention on a general CSR neighbourhood graph:
+ *
+ *   out_i = sum_e softmax_e( scale <q_i, tau(e) k_j> + bias_e ) * tau_n(e) v_j
+ *
+ * = the reference's scores+softmax op (attention.h:145-165, 295-316) followed
+ * by its eager value path: transport_field (nn/kernels.py:156-189), weighting
+ * by alpha, scatter_add_to_nodes (nn/_scatter.py:36-46) -- with alpha and every
+ * per-edge field kept in registers.  The reference documents such a fused op
+ * (attention.h:1-39) but exports no entry point for it.
+ *
+ * The geometry (row_ptr, source, tables) describes ONE sample of n_nodes
+ * points; q, k, v, out hold `batch` samples back to back, (batch * n_nodes, D),
+ * and share it (pass batch = 1 with a tiled geometry for the reference's
+ * disjoint-union batching, edge_geometry.py:216-252).
+ *
+ *   desc_host   (F, 5) int64 in HOST memory (rows as above)
+ *   transport   (n_edges, orders, 2), bias (n_edges): fp32 for GM_F32 / GM_BF16, fp64 for GM_F64
+ *   lse         (batch * n_nodes, H)   fp32 (fp64 for GM_F64): log-sum-exp of each row's logits
+ *   H must be 1, 2, 4 or 8.
+ * Backward: dq, dk, dv are fully written (zero-initialised inside).  With
+ * GM_BF16 the source-side sums accumulate in fp32 in `scratch`
+ * (gm_attention_backward_scratch_bytes bytes, caller-provided, contents
+ * undefined on return); other dtypes ignore it.
+ * ------------------------------------------------------------------------ */
+int gm_attention_forward(const void* q, const void* k, const void* v, const void* transport, const void* bias,
+                         const uint8_t* inside, const int64_t* desc_host, const int64_t* row_ptr, const int64_t* source,
+                         int64_t n_nodes, int64_t n_edges, int64_t batch, int D, int F, int orders, int H, double scale,
+                         int dtype, void* out, void* lse, void* stream);
+
+int64_t gm_attention_backward_scratch_bytes(int64_t n_nodes, int64_t batch, int D, int dtype);
+
+int gm_attention_backward(const void* dout, const void* q, const void* k, const void* v, const void* out, const void* lse,
+                          const void* transport, const void* bias, const uint8_t* inside, const int64_t* desc_host,
+                          const int64_t* row_ptr, const int64_t* source, int64_t n_nodes, int64_t n_edges, int64_t batch,
+                          int D, int F, int orders, int H, double scale, int dtype, void* dq, void* dk, void* dv,
+                          void* scratch, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GM_B200_H */

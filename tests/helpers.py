@@ -1,0 +1,119 @@
+"""Shared builders for the tests: lattices, per-edge constants, seeded inputs.
+
+Geometry comes from the numpy oracle (``oracle/geometry_np.py``), never from
+the package under test, so that operator tests and geometry tests fail
+independently.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from functools import lru_cache
+
+import numpy as np
+import torch
+
+from oracle import geometry_np as G
+
+from gm_attention_b200.fields import FieldType
+
+
+@dataclass
+class Case:
+    """One attention problem on a midpoint lattice, as numpy arrays in ``dtype``."""
+
+    nlat: int
+    nlon: int
+    radius: float
+    heads: int
+    head_type: FieldType
+    full_type: FieldType
+    desc: np.ndarray  # (F, 5) int64
+    row_ptr: np.ndarray
+    source: np.ndarray
+    target: np.ndarray
+    transport: np.ndarray  # (E, orders, 2)
+    angular: np.ndarray
+    rho: np.ndarray
+    weights: np.ndarray
+    bias: np.ndarray
+    inside: np.ndarray
+    scale: float
+    max_degree: int
+
+    @property
+    def n_nodes(self) -> int:
+        return self.nlat * self.nlon
+
+    @property
+    def width(self) -> int:
+        return self.full_type.dimension
+
+
+def descriptor_rows(head_type: FieldType, heads: int) -> np.ndarray:
+    full = head_type.scaled(heads)
+    starts = {n: s.start for n, s in full.slices().items()}
+    rows, coff = [], 0
+    for n, a in head_type.items():
+        rows.append([n, a, starts[n], 0 if n == 0 else coff, 1 if n == 0 else 2])
+        if n:
+            coff += 4 * a
+    return np.array(rows, np.int64).reshape(-1, 5)
+
+
+@lru_cache(maxsize=16)
+def _edges(nlat: int, nlon: int, radius: float, max_frequency: int, dtype_name: str) -> G.Edges:
+    return G.lattice_edges(G.midpoint_lattice(nlat, nlon), radius, max_frequency, np.dtype(dtype_name).type)
+
+
+def window_values(r: np.ndarray, cutoff: float, kind: str) -> np.ndarray:
+    if kind == "hard":
+        slack = 1e-10 if r.dtype == np.float64 else 1e-5
+        return (r <= cutoff + slack).astype(r.dtype)
+    return (np.maximum(1.0 - (r / r.dtype.type(cutoff)) ** 2, 0) ** 2).astype(r.dtype)
+
+
+def make_case(nlat: int, nlon: int, radius: float, head_type: dict[int, int], heads: int, dtype=np.float32,
+              window: str = "hard", max_frequency: int = 4) -> Case:
+    e = _edges(nlat, nlon, float(radius), max_frequency, np.dtype(dtype).name)
+    attn = FieldType(head_type)
+    dt = np.dtype(dtype).type
+    tiny = np.finfo(dtype).tiny
+    win = window_values(e.distances, radius, window)
+    quad = e.tangent_quadrature_weights
+    bias = (np.log(np.maximum(win, tiny)) + np.log(np.maximum(quad, tiny))).astype(dtype)
+    as_pairs = lambda z: np.ascontiguousarray(np.stack([z.real, z.imag], -1).astype(dtype))
+    degree = np.diff(e.row_ptr)
+    return Case(nlat, nlon, float(radius), heads, attn, attn.scaled(heads), descriptor_rows(attn, heads), e.row_ptr.copy(),
+                e.source_index.copy(), e.target_index.copy(), as_pairs(e.transport_phases), as_pairs(e.angular_phases),
+                (e.distances / dt(radius)).astype(dtype), (win * quad).astype(dtype), bias, (win > 0).astype(np.uint8),
+                1.0 / math.sqrt(attn.dimension), int(degree.max()))
+
+
+def seeded(shape: tuple[int, ...], seed: int, dtype=np.float32, count: int = 1) -> list[np.ndarray]:
+    """``count`` N(0, 1) arrays drawn in order from one torch CPU generator (fp32 draws, then cast)."""
+    gen = torch.Generator().manual_seed(seed)
+    return [torch.randn(*shape, generator=gen, dtype=torch.float32).numpy().astype(dtype) for _ in range(count)]
+
+
+def cuda(a: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def rel_err(a, b) -> float:
+    a = np.asarray(a, np.float64)
+    b = np.asarray(b, np.float64)
+    return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30))
+
+
+def assert_close(actual, expected, rtol: float, atol: float, what: str = "") -> None:
+    """``|a - e| <= atol + rtol * |e|`` elementwise, reported with the worst offender."""
+    a = np.asarray(actual, np.float64)
+    e = np.asarray(expected, np.float64)
+    assert a.shape == e.shape, f"{what}: shape {a.shape} vs {e.shape}"
+    if a.size == 0:
+        return
+    excess = np.abs(a - e) - (atol + rtol * np.abs(e))
+    worst = int(np.argmax(excess))
+    assert excess.flat[worst] <= 0, f"{what}: |{a.flat[worst]} - {e.flat[worst]}| exceeds atol={atol} rtol={rtol} (max abs diff {np.abs(a - e).max():.3e})"
