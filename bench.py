@@ -1,0 +1,390 @@
+"""Benchmark of the fused gauge-attention layer (forward + backward).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--dtype bf16|f32] [--impl ours|reference]
+
+Metric: neighbour-edges per second of one fused gauge-attention layer, forward +
+backward, where one edge is one (target <- source) CSR entry of one sample;
+``value = batch * E1 / t(fwd + bwd)``.  Workload: the 256 x 512 midpoint
+equiangular lattice, radius 3 pi / 256 (E1 = 13 527 040), batch 8, 4 heads of
+16 x (m = 0, 1, 2) (D = 320); inputs ~ N(0, 1) from a fixed seed (synthetic
+stand-ins for the shallow-water fields the reference trains on).
+
+One JSON line is printed by rank 0.  ``value`` is timed with the inputs
+resident in HBM; ``e2e`` is the same step driven from pinned HOST buffers with
+the host->device and device->host copies inside the timed region.  With N > 1
+the sphere is cut into edge-balanced latitude bands (one per rank), the key /
+value halos are exchanged before the forward and the gradient halos after the
+backward, all inside the timed region.
+
+``--impl reference`` times the reference's own CPU implementation of the same
+layer on the host cores: its compiled scores+softmax driver (oracle/_ref, built
+from the reference's sources) plus a C port of its eager value path, one
+sample per worker process.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+HEADLINE = dict(nlat=256, nlon=512, radius_rows=3, batch=8, heads=4, head_type={0: 16, 1: 16, 2: 16})
+SMALL = dict(nlat=64, nlon=128, radius_rows=3, batch=2, heads=4, head_type={0: 16, 1: 16, 2: 16})
+L2_BYTES = 126 * 1024 * 1024
+
+
+def parse() -> argparse.Namespace:
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=10)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--dtype", choices=["bf16", "f32"], default="bf16")
+    p.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    p.add_argument("--workload", choices=["headline", "small"], default="headline")
+    p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--no-e2e", action="store_true")
+    return p.parse_args()
+
+
+# ----------------------------------------------------------------------------- CPU legs (oracle = checker / baseline only)
+
+def _cpu_sample_step(job: tuple) -> float:
+    """One sample's forward + backward on one core: reference C++ scores+softmax driver
+    (oracle/_ref) when present, C port of the value path; returns seconds."""
+    nlat, nlon, radius, head_type, heads, seed, use_ref = job
+    import numpy as np
+    import torch
+
+    from oracle import oracle as O
+    from tests.helpers import make_case, seeded
+
+    torch.set_num_threads(1)
+    c = make_case(nlat, nlon, radius, head_type, heads, dtype=np.float32)
+    q, k, v, g = seeded((c.n_nodes, c.width), seed, np.float32, 4)
+    ref = None
+    if use_ref:
+        from oracle import build_ref
+        ref = build_ref.load("gm_fused_attention_cpu")
+    t0 = time.perf_counter()
+    if ref is not None:
+        t = torch.from_numpy
+        tables = (t(c.transport), t(c.bias), t(c.inside), t(c.desc), t(c.row_ptr), t(c.source))
+        alpha = ref.softmax_forward(t(q), t(k), *tables, c.heads, c.scale, c.max_degree)
+        O.value_forward(alpha.numpy(), v, c.transport, c.desc, c.row_ptr, c.source, c.heads)
+        dalpha, _ = O.value_backward(g, alpha.numpy(), v, c.transport, c.desc, c.row_ptr, c.source, c.heads)
+        ref.softmax_backward(t(dalpha), t(q), t(k), *tables, alpha, c.heads, c.scale, c.max_degree)
+    else:
+        O.attention_forward(q, k, v, c.transport, c.bias, c.inside, c.desc, c.row_ptr, c.source, c.heads, c.scale, 1)
+        O.attention_backward(g, q, k, v, c.transport, c.bias, c.inside, c.desc, c.row_ptr, c.source, c.heads, c.scale, 1)
+    return time.perf_counter() - t0
+
+
+def cpu_layer_rate(cfg: dict, repeats: int = 1) -> dict:
+    """Edges/s of the layer on the host cores, on a bounded sample: the workload's head
+    layout on a 32 x 64 lattice at the same radius in rows, one sample per core."""
+    import multiprocessing as mp
+
+    import numpy as np
+
+    from oracle import build_ref
+    from tests.helpers import make_case
+
+    nlat, nlon = 64, 128
+    radius = cfg["radius_rows"] * math.pi / nlat
+    cores = os.cpu_count() or 1
+    per_core = 3
+    use_ref = (build_ref.OUT / "gm_fused_attention_cpu.so").exists()
+    edges = int(make_case(nlat, nlon, radius, cfg["head_type"], cfg["heads"], dtype=np.float32).source.shape[0])
+    jobs = [(nlat, nlon, radius, cfg["head_type"], cfg["heads"], s, use_ref) for s in range(cores * per_core)]
+    best = float("inf")
+    with mp.get_context("fork").Pool(cores) as pool:
+        pool.map(_cpu_sample_step, jobs[:cores])  # warm: builds the geometry cache, loads the libraries
+        for _ in range(repeats):
+            t0 = time.perf_counter()
+            pool.map(_cpu_sample_step, jobs)
+            best = min(best, time.perf_counter() - t0)
+    return {"value": len(jobs) * edges / best, "unit": "edges/s", "cores": cores, "kind": "reference" if use_ref else "port",
+            "sample": f"{len(jobs)} samples ({per_core} per core) of the workload's head layout on a {nlat}x{nlon} lattice, radius {cfg['radius_rows']}pi/{nlat}, "
+                      f"{edges} edges each, fp32; scores+softmax fwd/bwd = "
+                      + ("the reference's compiled C++ driver" if use_ref else "C port") + ", value path = C port of the reference's eager path",
+            "seconds": best}
+
+
+def run_reference(args: argparse.Namespace, cfg: dict) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, args.steps)
+    base = None
+    times = []
+    for _ in range(max(0, min(args.warmup, 1))):
+        cpu_layer_rate(cfg)
+    for _ in range(min(steps, 3)):
+        base = cpu_layer_rate(cfg)
+        times.append(base["seconds"])
+    assert base is not None
+    sec = statistics.median(times)
+    value = base["value"] * base["seconds"] / sec
+    line = {
+        "impl": "reference", "metric": "gauge-attn fwd+bwd neighbour-edges/sec", "value": value, "unit": "edges/s", "n_gpus": args.gpus,
+        "steps": min(steps, 3), "warmup": min(args.warmup, 1), "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(cfg, args, 1),
+        "cpu_baseline": {k: base[k] for k in ("unit", "cores", "kind", "sample")} | {"value": value},
+        "e2e": {"value": value, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def workload_config(cfg: dict, args: argparse.Namespace, world: int) -> dict:
+    return {"workload": f"fused gauge attention fwd+bwd, {cfg['nlat']}x{cfg['nlon']} midpoint equiangular lattice, radius "
+                        f"{cfg['radius_rows']}pi/{cfg['nlat']}, batch {cfg['batch']}, {cfg['heads']} heads of 16x(m=0,1,2), D=320",
+            "global_batch": cfg["batch"], "parallelism": f"latitude-bands x{world}" if world > 1 else "single GPU",
+            "l2": "inputs larger than L2 (no flush needed)"}
+
+
+# ----------------------------------------------------------------------------- GPU arm
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int) -> None:
+        self.index, self.proc = index, None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        self.rows = []
+        if self.proc is None:
+            return
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        for line in out.splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) >= 9:
+                self.rows.append(parts)
+
+    def summary(self) -> dict:
+        rows = getattr(self, "rows", [])
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        sm = [float(r[1]) for r in rows if r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[5 + i].lower().startswith("active") for r in rows)]
+        busy = sorted(sm)[len(sm) // 2:] or sm  # upper half = samples under load
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": float(rows[0][2]), "reasons": reasons,
+                "samples": len(rows)}
+
+
+def run_ours(args: argparse.Namespace, cfg: dict) -> None:
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from gm_attention_b200 import _lib
+    from gm_attention_b200.attention import AttentionTables, attention_backward, attention_forward
+    from gm_attention_b200.fields import FieldType
+    from gm_attention_b200.geometry import SphericalLattice, compute_edge_geometry, midpoint_lattice
+    from gm_attention_b200.nn import fused_attention as fa
+    from gm_attention_b200.parallel import BandPlan, HaloExchanger
+
+    _lib.lib()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    nlat, nlon, batch, heads = cfg["nlat"], cfg["nlon"], cfg["batch"], cfg["heads"]
+    radius = cfg["radius_rows"] * math.pi / nlat
+    attn = FieldType(cfg["head_type"])
+    full = attn.scaled(heads)
+    D = full.dimension
+    dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32
+    elem = 2 if args.dtype == "bf16" else 4
+
+    # ---- resident geometry (built once, on the device; not timed)
+    lattice = midpoint_lattice(nlat, nlon, device)
+    w = lattice.band(radius)
+    lo_c, hi_c = lattice.candidate_ranges(radius)
+    row_edges = None
+    if world > 1:
+        # per-row degrees from a count-only pass over column 0 of every row
+        deg = torch.empty(nlat * nlon, dtype=torch.int64, device=device)
+        _lib.call("gm_geometry_count", _lib.ptr(lattice.nodes), nlat * nlon, _lib.ptr(lo_c), _lib.ptr(hi_c), radius, _lib.ptr(deg),
+                  _lib.stream(device))
+        row_degree = deg.reshape(nlat, nlon)[:, 0].tolist()
+        plan = BandPlan.balanced(nlat, nlon, w, row_degree, world)
+    else:
+        plan = BandPlan(nlat, nlon, w, (0, nlat))
+    lo, hi = plan.owned(rank)
+    elo, ehi = plan.extended(rank)
+    rows_ext = ehi - elo
+    # the rank's node set: its extended rows; halo targets examine no candidates (degree 0)
+    sel = slice(elo * nlon, ehi * nlon)
+    sub = SphericalLattice(rows_ext, nlon, lattice.theta[elo:ehi], lattice.nodes[sel].contiguous(),
+                           lattice.quadrature_weights[sel].contiguous(), lattice.frames[sel].contiguous())
+    c_lo, c_hi = (lo_c[sel] - elo * nlon).clone(), (hi_c[sel] - elo * nlon).clamp_max(rows_ext * nlon).clone()
+    c_lo.clamp_min_(0)
+    owned_mask = torch.zeros(rows_ext, dtype=torch.bool, device=device)
+    owned_mask[lo - elo: hi - elo] = True
+    owned_nodes = owned_mask.repeat_interleave(nlon)
+    c_hi = torch.where(owned_nodes, c_hi, c_lo)
+    edges = compute_edge_geometry(sub, sub.frames, radius, max_frequency=2, dtype=torch.float32, candidates=(c_lo, c_hi))
+    geo = fa.geometry(edges, radius, "hard", torch.float32)
+    owner = type("Layer", (), {})()
+    p = fa._plan(owner, attn, full, heads)
+    tables = AttentionTables(geo.transport, geo.bias, geo.inside, geo.row_ptr, geo.source, p.rows, heads, 1.0 / math.sqrt(attn.dimension))
+    local_edges = edges.n_edges * batch
+    n_ext = rows_ext * nlon
+
+    # ---- inputs: seeded N(0, 1), generated on the host, resident on the device for `value`
+    gen = torch.Generator().manual_seed(1234 + rank)
+    shape = (batch, rows_ext, nlon, D)
+    host = [torch.randn(shape, generator=gen, dtype=torch.float32).to(dtype).pin_memory() for _ in range(4)]
+    q, k, v, g = (h.to(device, non_blocking=True) for h in host)
+    flat = lambda t: t.view(batch * n_ext, D)
+    halo = HaloExchanger(plan, rank) if world > 1 else None
+    fwd_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    bwd_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+
+    def step(index: int | None = None):
+        if halo is not None:
+            halo.fill_halos(k, v)
+        if index is not None:
+            fwd_ev[index][0].record()
+        out, lse = attention_forward(flat(q), flat(k), flat(v), tables)
+        if index is not None:
+            fwd_ev[index][1].record()
+            bwd_ev[index][0].record()
+        dq, dk, dv = attention_backward(flat(g), flat(q), flat(k), flat(v), out, lse, tables)
+        if index is not None:
+            bwd_ev[index][1].record()
+        if halo is not None:
+            halo.reduce_halos(dk.view(shape), dv.view(shape))
+        return out, dq, dk, dv
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        start.record()
+        for s in range(args.steps):
+            step(s)
+        stop.record()
+        barrier()
+    ms_total = start.elapsed_time(stop)
+    if world > 1:
+        t = torch.tensor([ms_total], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t)
+        tot = torch.tensor([local_edges], device=device, dtype=torch.int64)
+        dist.all_reduce(tot)
+        total_edges = int(tot)
+    else:
+        total_edges = local_edges
+    ms_step = ms_total / args.steps
+    fwd_ms = statistics.mean(a.elapsed_time(b) for a, b in fwd_ev)
+    bwd_ms = statistics.mean(a.elapsed_time(b) for a, b in bwd_ev)
+
+    # ---- end to end from pinned host buffers (copies inside the timed region)
+    e2e = None
+    if not args.no_e2e:
+        outs_host = [torch.empty(shape, dtype=dtype).pin_memory() for _ in range(4)]
+        def e2e_step():
+            dev = [h.to(device, non_blocking=True) for h in host]
+            qq, kk, vv, gg = dev
+            if halo is not None:
+                halo.fill_halos(kk, vv)
+            out, lse = attention_forward(flat(qq), flat(kk), flat(vv), tables)
+            dq, dk, dv = attention_backward(flat(gg), flat(qq), flat(kk), flat(vv), out, lse, tables)
+            if halo is not None:
+                halo.reduce_halos(dk.view(shape), dv.view(shape))
+            for dst, src in zip(outs_host, (out, dq, dk, dv)):
+                dst.copy_(src.view(shape), non_blocking=True)
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        n_e2e = max(3, min(args.steps, 5))
+        start.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        stop.record()
+        barrier()
+        ms = start.elapsed_time(stop)
+        if world > 1:
+            t = torch.tensor([ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t)
+        nbytes = 4 * batch * n_ext * D * elem
+        e2e = {"value": total_edges / (ms / n_e2e * 1e-3), "unit": "edges/s", "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
+               "ms_per_step": ms / n_e2e, "steps": n_e2e}
+
+    if rank == 0:
+        peaks_path = ROOT / "MEASURED_PEAKS.json"
+        if peaks_path.exists():
+            peak, peak_kind = json.loads(peaks_path.read_text())["hbm_gbs"], "measured"
+        else:
+            peak, peak_kind = 6650.0, "fallback"
+        n_rows = batch * n_ext
+        bwd_bytes = 8 * n_rows * D * elem + n_rows * heads * 4
+        layer_bytes = 12 * n_rows * D * elem + 2 * n_rows * heads * 4
+        achieved = bwd_bytes / (bwd_ms * 1e-3) / 1e9
+        line = {
+            "metric": "gauge-attn fwd+bwd neighbour-edges/sec", "value": total_edges / (ms_step * 1e-3), "unit": "edges/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": args.dtype, "data": "synthetic", "config": workload_config(cfg, args, world),
+            "roofline": {"bound": "hbm", "kernel": "fused_backward_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                         "algorithmic_bytes_per_launch": bwd_bytes, "launch_ms": bwd_ms},
+            "layer": {"fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "algorithmic_bytes": layer_bytes,
+                      "hbm_frac": layer_bytes / ((fwd_ms + bwd_ms) * 1e-3) / 1e9 / peak, "edges": total_edges},
+            "gpu_launches": args.steps * (2 + (2 if args.dtype == "bf16" else 0)),
+            "clocks": clocks.summary(),
+            "e2e": e2e,
+        }
+        if not args.no_cpu_baseline and world == 1:
+            line["cpu_baseline"] = {k: val for k, val in cpu_layer_rate(cfg).items() if k != "seconds"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    args = parse()
+    cfg = HEADLINE if args.workload == "headline" else SMALL
+    if args.impl == "reference":
+        run_reference(args, cfg)
+    else:
+        run_ours(args, cfg)
+
+
+if __name__ == "__main__":
+    main()

@@ -128,6 +128,32 @@ int gm_attention_backward(const void* dout, const void* q, const void* k, const 
                           int D, int F, int orders, int H, double scale, int dtype, void* dq, void* dk, void* dv,
                           void* scratch, void* stream);
 
+/* ------------------------------------------------------------------------
+ * Neighbourhood geometry built on the device (replaces the reference's CPU
+ * KD-tree search + table derivation: discretization/edge_geometry.py:320-396
+ * compute_edge_geometry, :506-619 edge_geometry_from_index, :622-653 row_ptr).
+ *
+ *   nodes      (n_nodes, 3) float64 unit vectors; frames (n_nodes, 3, 2) float64;
+ *   weights    (n_nodes) float64 spherical quadrature weights
+ *   cand_lo/hi (n_nodes) int64 or both NULL: target i only examines sources in [lo[i], hi[i])
+ * gm_geometry_count writes each target's degree (pairs with float64 geodesic
+ * distance <= radius + 1e-10, self-loop included).  The caller forms
+ * row_ptr = [0, cumsum(degree)] and allocates E = row_ptr[n_nodes] entries;
+ * gm_geometry_fill then writes the CSR (target, source ascending within a row)
+ * and the per-edge tables in `dtype` (GM_F32 / GM_F64):
+ *   distances, polar_angles, transport_angles, tangent_weights (E);
+ *   log_coordinates (E, 2); angular_phases, transport_phases (E, max_frequency + 1, 2)
+ *   as (cos, sin) pairs of k * angle.
+ * ------------------------------------------------------------------------ */
+int gm_geometry_count(const double* nodes, int64_t n_nodes, const int64_t* cand_lo, const int64_t* cand_hi, double radius,
+                      int64_t* degree, void* stream);
+
+int gm_geometry_fill(const double* nodes, const double* frames, const double* weights, int64_t n_nodes,
+                     const int64_t* cand_lo, const int64_t* cand_hi, double radius, const int64_t* row_ptr,
+                     int max_frequency, int dtype, int64_t* target, int64_t* source, void* distances,
+                     void* log_coordinates, void* polar_angles, void* transport_angles, void* tangent_weights,
+                     void* angular_phases, void* transport_phases, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -175,73 +175,82 @@ void FN(oracle_conv_backward)(const T* g, const T* v, const T* rc, const T* cc, 
     }
 }
 
-/* The fused layer: alpha from oracle_softmax_forward, then
- * out_i = sum_e alpha_e,h(c) * (tau_n(e) v_j)[c]  -- the reference's eager value path
- * "gather, transport_field (nn/kernels.py:156-189), weight, scatter_add_to_nodes
- * (nn/_scatter.py:36-46)".  `alpha` is caller-provided scratch (E, H).  The geometry
- * describes one sample; `batch` samples of n_nodes rows share it. */
+/* The value path given alpha (E, H): out_i = sum_e alpha_e,h(c) * (tau_n(e) v_j)[c] -- the
+ * reference's eager "gather, transport_field (nn/kernels.py:156-189), weight,
+ * scatter_add_to_nodes (nn/_scatter.py:36-46)" for one sample. */
+void FN(oracle_value_forward)(const T* alpha, const T* v, const T* transport, const int64_t* desc, const int64_t* row_ptr,
+                              const int64_t* source, int64_t n_nodes, int D, int F, int orders, int H, T* out) {
+  for (int64_t i = 0; i < n_nodes; ++i)
+    for (int c = 0; c < D; ++c) {
+      int n, h, part, a, a_n, coff;
+      T y = 0;
+      if (FN(locate)(desc, F, H, c, &n, &h, &part, &a, &a_n, &coff)) {
+        for (int64_t e = row_ptr[i]; e < row_ptr[i + 1]; ++e) {
+          const int64_t j = source[e];
+          if (n == 0) {
+            y += alpha[e * H + h] * v[j * D + c];
+          } else {
+            const T tr = transport[(e * orders + n) * 2], ti = transport[(e * orders + n) * 2 + 1];
+            const T vr = v[j * D + c - part], vi = v[j * D + c - part + 1];
+            y += alpha[e * H + h] * (part == 0 ? tr * vr - ti * vi : tr * vi + ti * vr);
+          }
+        }
+      }
+      out[i * D + c] = y;
+    }
+}
+
+/* Its adjoint: dalpha_e,h = <dO_i, tau v_j>_h (zeroed here, then summed), dv_j += alpha conj(tau) dO_i (zeroed here). */
+void FN(oracle_value_backward)(const T* dout, const T* alpha, const T* v, const T* transport, const int64_t* desc,
+                               const int64_t* row_ptr, const int64_t* source, int64_t n_nodes, int D, int F, int orders, int H,
+                               T* dalpha, T* dv) {
+  const int64_t n_edges = row_ptr[n_nodes];
+  for (int64_t x = 0; x < n_nodes * D; ++x) dv[x] = 0;
+  for (int64_t x = 0; x < n_edges * H; ++x) dalpha[x] = 0;
+  for (int64_t i = 0; i < n_nodes; ++i)
+    for (int c = 0; c < D; ++c) {
+      int n, h, part, a, a_n, coff;
+      if (!FN(locate)(desc, F, H, c, &n, &h, &part, &a, &a_n, &coff)) continue;
+      const T g = dout[i * D + c];
+      for (int64_t e = row_ptr[i]; e < row_ptr[i + 1]; ++e) {
+        const int64_t j = source[e];
+        if (n == 0) {
+          dalpha[e * H + h] += g * v[j * D + c];
+          dv[j * D + c] += alpha[e * H + h] * g;
+        } else {
+          const T tr = transport[(e * orders + n) * 2], ti = transport[(e * orders + n) * 2 + 1];
+          const int re = c - part;
+          const T vr = v[j * D + re], vi = v[j * D + re + 1];
+          dalpha[e * H + h] += g * (part == 0 ? tr * vr - ti * vi : tr * vi + ti * vr);
+          /* d/dv of g * (tau v)[c]: the real part picks (tr, -ti) on (vr, vi), the imaginary part (ti, tr) */
+          if (part == 0) { dv[j * D + re] += alpha[e * H + h] * g * tr; dv[j * D + re + 1] -= alpha[e * H + h] * g * ti; }
+          else           { dv[j * D + re] += alpha[e * H + h] * g * ti; dv[j * D + re + 1] += alpha[e * H + h] * g * tr; }
+        }
+      }
+    }
+}
+
+/* The fused layer = oracle_softmax_forward then oracle_value_forward, per sample.  `alpha` is caller
+ * scratch (E, H).  The geometry describes one sample; `batch` samples of n_nodes rows share it. */
 void FN(oracle_attention_forward)(const T* q, const T* k, const T* v, const T* transport, const T* bias,
                                   const uint8_t* inside, const int64_t* desc, const int64_t* row_ptr, const int64_t* source,
                                   int64_t n_nodes, int64_t batch, int D, int F, int orders, int H, T scale, T* alpha, T* out) {
   for (int64_t b = 0; b < batch; ++b) {
-    const T *qb = q + b * n_nodes * D, *kb = k + b * n_nodes * D, *vb = v + b * n_nodes * D;
-    T* ob = out + b * n_nodes * D;
-    FN(oracle_softmax_forward)(qb, kb, transport, bias, inside, desc, row_ptr, source, n_nodes, D, F, orders, H, scale, alpha);
-    for (int64_t i = 0; i < n_nodes; ++i)
-      for (int c = 0; c < D; ++c) {
-        int n, h, part, a, a_n, coff;
-        T y = 0;
-        if (FN(locate)(desc, F, H, c, &n, &h, &part, &a, &a_n, &coff)) {
-          for (int64_t e = row_ptr[i]; e < row_ptr[i + 1]; ++e) {
-            const int64_t j = source[e];
-            if (n == 0) {
-              y += alpha[e * H + h] * vb[j * D + c];
-            } else {
-              const T tr = transport[(e * orders + n) * 2], ti = transport[(e * orders + n) * 2 + 1];
-              const T vr = vb[j * D + c - part], vi = vb[j * D + c - part + 1];
-              y += alpha[e * H + h] * (part == 0 ? tr * vr - ti * vi : tr * vi + ti * vr);
-            }
-          }
-        }
-        ob[i * D + c] = y;
-      }
+    const int64_t o = b * n_nodes * D;
+    FN(oracle_softmax_forward)(q + o, k + o, transport, bias, inside, desc, row_ptr, source, n_nodes, D, F, orders, H, scale, alpha);
+    FN(oracle_value_forward)(alpha, v + o, transport, desc, row_ptr, source, n_nodes, D, F, orders, H, out + o);
   }
 }
 
-/* Backward of the fused layer by the chain rule through the two stages above:
- * dalpha_e,h = <dO_i, tau v_j>_h ; dv_j += alpha conj(tau) dO_i ; then oracle_softmax_backward.
- * alpha, dalpha: caller scratch (E, H). */
+/* Backward of the fused layer by the chain rule through the two stages.  alpha, dalpha: caller scratch (E, H). */
 void FN(oracle_attention_backward)(const T* dout, const T* q, const T* k, const T* v, const T* transport, const T* bias,
                                    const uint8_t* inside, const int64_t* desc, const int64_t* row_ptr, const int64_t* source,
                                    int64_t n_nodes, int64_t batch, int D, int F, int orders, int H, T scale, T* alpha,
                                    T* dalpha, T* dq, T* dk, T* dv) {
-  const int64_t n_edges = row_ptr[n_nodes];
   for (int64_t b = 0; b < batch; ++b) {
     const int64_t o = b * n_nodes * D;
     FN(oracle_softmax_forward)(q + o, k + o, transport, bias, inside, desc, row_ptr, source, n_nodes, D, F, orders, H, scale, alpha);
-    for (int64_t x = 0; x < n_nodes * D; ++x) dv[o + x] = 0;
-    for (int64_t x = 0; x < n_edges * H; ++x) dalpha[x] = 0;
-    for (int64_t i = 0; i < n_nodes; ++i)
-      for (int c = 0; c < D; ++c) {
-        int n, h, part, a, a_n, coff;
-        if (!FN(locate)(desc, F, H, c, &n, &h, &part, &a, &a_n, &coff)) continue;
-        const T g = dout[o + i * D + c];
-        for (int64_t e = row_ptr[i]; e < row_ptr[i + 1]; ++e) {
-          const int64_t j = source[e];
-          if (n == 0) {
-            dalpha[e * H + h] += g * v[o + j * D + c];
-            dv[o + j * D + c] += alpha[e * H + h] * g;
-          } else {
-            const T tr = transport[(e * orders + n) * 2], ti = transport[(e * orders + n) * 2 + 1];
-            const int re = c - part;
-            const T vr = v[o + j * D + re], vi = v[o + j * D + re + 1];
-            dalpha[e * H + h] += g * (part == 0 ? tr * vr - ti * vi : tr * vi + ti * vr);
-            /* d/dv of g * (tau v)[c]: real part picks (tr, -ti) on (vr, vi); imaginary part (ti, tr) */
-            if (part == 0) { dv[o + j * D + re] += alpha[e * H + h] * g * tr; dv[o + j * D + re + 1] -= alpha[e * H + h] * g * ti; }
-            else           { dv[o + j * D + re] += alpha[e * H + h] * g * ti; dv[o + j * D + re + 1] += alpha[e * H + h] * g * tr; }
-          }
-        }
-      }
+    FN(oracle_value_backward)(dout + o, alpha, v + o, transport, desc, row_ptr, source, n_nodes, D, F, orders, H, dalpha, dv + o);
     FN(oracle_softmax_backward)(dalpha, q + o, k + o, transport, desc, row_ptr, source, alpha, n_nodes, D, F, orders, H, scale,
                                 dq + o, dk + o);
   }

@@ -127,3 +127,23 @@ def attention_backward(dout, q, k, v, transport, bias, inside, desc, row_ptr, so
     _call("oracle_attention_backward", dt, dout, q, k, v, transport, bias, inside, desc, row_ptr, source, ("i64", n),
           ("i64", batch), q.shape[1], desc.shape[0], transport.shape[1], heads, float(scale), alpha, dalpha, dq, dk, dv)
     return dq, dk, dv
+
+
+def value_forward(alpha, v, transport, desc, row_ptr, source, heads):
+    dt = v.dtype
+    alpha, v, transport = _c(alpha), _c(v), _c(transport)
+    desc, row_ptr, source = _c(desc, np.int64), _c(row_ptr, np.int64), _c(source, np.int64)
+    out = np.zeros_like(v)
+    _call("oracle_value_forward", dt, alpha, v, transport, desc, row_ptr, source, ("i64", v.shape[0]), v.shape[1], desc.shape[0],
+          transport.shape[1], heads, out)
+    return out
+
+
+def value_backward(dout, alpha, v, transport, desc, row_ptr, source, heads):
+    dt = v.dtype
+    dout, alpha, v, transport = _c(dout), _c(alpha), _c(v), _c(transport)
+    desc, row_ptr, source = _c(desc, np.int64), _c(row_ptr, np.int64), _c(source, np.int64)
+    dalpha, dv = np.zeros_like(alpha), np.zeros_like(v)
+    _call("oracle_value_backward", dt, dout, alpha, v, transport, desc, row_ptr, source, ("i64", v.shape[0]), v.shape[1],
+          desc.shape[0], transport.shape[1], heads, dalpha, dv)
+    return dalpha, dv

@@ -72,14 +72,14 @@ def dump_geometry() -> None:
             tangent_quadrature_weights=e.tangent_quadrature_weights.numpy(), log_coordinates=e.log_coordinates.numpy(),
             angular_phases=e.angular_phases.numpy(), transport_phases=e.transport_phases.numpy())
     names, counts, sums, degrees = [], [], [], []
-    for nlat, nlon, mult in [(32, 64, 2), (32, 64, 3), (64, 128, 3), (128, 256, 3)]:
+    for nlat, nlon, mult in [(32, 64, 2), (32, 64, 3), (64, 128, 3), (128, 256, 3), (256, 512, 3), (256, 512, 4)]:
         e = reference_edges(nlat, nlon, mult * math.pi / nlat, torch.float32, max_frequency=2)
         deg = (e.row_ptr[1:] - e.row_ptr[:-1]).reshape(nlat, nlon)
         assert bool((deg == deg[:, :1]).all())
         names.append(f"{nlat}x{nlon}_r{mult}")
         counts.append(e.n_edges)
         sums.append(csr_checksum(e.row_ptr.numpy(), e.edge_index[1].numpy()))
-        degrees.append(np.pad(deg[:, 0].numpy(), (0, 128 - nlat)))
+        degrees.append(np.pad(deg[:, 0].numpy(), (0, 256 - nlat)))
     np.savez_compressed(HERE / "geometry_counts.npz", names=np.array(names), counts=np.array(counts, np.int64),
                         checksums=np.array(sums, np.uint64), degrees=np.stack(degrees))
 
