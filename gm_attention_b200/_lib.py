@@ -32,10 +32,12 @@ SIGNATURES: dict[str, list[Any]] = {
     "gm_geometry_count": [_P, _L, _P, _P, _D, _P, _P],
     "gm_geometry_fill": [_P, _P, _P, _L, _P, _P, _D, _P, _I, _I] + [_P] * 10,
     "gm_attention_backward": [_P] * 12 + [_L, _L, _L, _I, _I, _I, _I, _D, _I, _P, _P, _P, _P, _P],
+    "gm_attention_backward_static": [_P] * 12 + [_L, _L, _L, _I, _I, _I, _I, _D, _I, _P, _P, _P, _P],
 }
 #: entry points that return a size instead of a status
 SIZE_QUERIES: dict[str, list[Any]] = {
     "gm_attention_backward_scratch_bytes": [_L, _L, _I, _I],
+    "gm_attention_backward_static_capacity": [],
 }
 
 

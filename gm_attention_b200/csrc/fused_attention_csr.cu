@@ -401,3 +401,71 @@ extern "C" int gm_attention_backward(const void* dout, const void* q, const void
   narrow_to_bf16_kernel<<<blocks, 256, 0, cs>>>((const float*)scratch + count, (__nv_bfloat16*)dv, count);
   return launch_status("gm_attention_backward (narrow)");
 }
+
+// ---------------------------------------------------------------------------
+// gm_attention_backward_static: the backward above for callers that cannot
+// allocate device memory.
+//
+// Some embedders hand the whole device-memory budget to an arena of their own
+// when they start (a serving runtime with a fixed memory plan, a host loop
+// with a hard latency bound that may not take the driver's allocator lock or
+// the device-wide synchronisation cudaMalloc can imply).  They can pass inputs
+// and outputs carved from that arena, but they have nowhere to get the fp32
+// accumulation buffer the bf16 backward wants.  For them the buffer lives
+// inside the library image: a file-scope device array of a fixed size that
+// every GPU loading the library holds until the process exits.
+//
+// The array's name is only a host-side handle; its device address is looked
+// up once per device with cudaGetSymbolAddress (with that device current) and
+// kept.  That lookup happens on the FIRST call made on a device, so make that
+// first call outside any stream capture.  No cudaMalloc, cudaFree or other
+// allocating routine is called.  All calls on a device share the one array:
+// it still holds the previous call's sums, so each call clears it first, and
+// two calls that overlap on the GPU (different streams) race on it -- order
+// them.  Problems larger than the array are refused with GM_ERR_LIMIT.
+// ---------------------------------------------------------------------------
+namespace gmb {
+namespace {
+
+constexpr int64_t STATIC_SCRATCH_BYTES = 32ll << 20;  // 32 MiB: batch * n_nodes * D <= 4 Mi elements
+constexpr int MAX_DEVICES = 64;
+
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
+
+void* g_static_scratch_address[MAX_DEVICES] = {nullptr};
+
+int static_scratch(void** out) {
+  int device = -1;
+  GM_CUDA(cudaGetDevice(&device));
+  GM_REQUIRE(device >= 0 && device < MAX_DEVICES, GM_ERR_LIMIT, "gm_attention_backward_static: device index %d beyond %d", device, MAX_DEVICES);
+  if (g_static_scratch_address[device] == nullptr) {
+    void* address = nullptr;
+    GM_CUDA(cudaGetSymbolAddress(&address, g_static_scratch));
+    g_static_scratch_address[device] = address;
+  }
+  *out = g_static_scratch_address[device];
+  return GM_OK;
+}
+
+}  // namespace
+}  // namespace gmb
+
+extern "C" int64_t gm_attention_backward_static_capacity(void) { return gmb::STATIC_SCRATCH_BYTES; }
+
+extern "C" int gm_attention_backward_static(const void* dout, const void* q, const void* k, const void* v, const void* out,
+                                            const void* lse, const void* transport, const void* bias, const uint8_t* inside,
+                                            const int64_t* desc_host, const int64_t* row_ptr, const int64_t* source,
+                                            int64_t n_nodes, int64_t n_edges, int64_t batch, int D, int F, int orders, int H,
+                                            double scale, int dtype, void* dq, void* dk, void* dv, void* stream) {
+  GM_REQUIRE(n_nodes >= 0 && batch >= 1 && D >= 1, GM_ERR_ARGUMENT, "gm_attention_backward_static: bad sizes");
+  const int64_t need = gm_attention_backward_scratch_bytes(n_nodes, batch, D, dtype);
+  GM_REQUIRE(need <= STATIC_SCRATCH_BYTES, GM_ERR_LIMIT,
+             "gm_attention_backward_static: this problem needs %lld bytes of accumulation space, the built-in buffer holds %lld "
+             "(batch * n_nodes * D <= %lld); use gm_attention_backward with a caller-provided buffer",
+             (long long)need, (long long)STATIC_SCRATCH_BYTES, (long long)(STATIC_SCRATCH_BYTES / 8));
+  void* scratch = nullptr;
+  int status = static_scratch(&scratch);
+  if (status != GM_OK) return status;
+  return gm_attention_backward(dout, q, k, v, out, lse, transport, bias, inside, desc_host, row_ptr, source, n_nodes, n_edges, batch,
+                               D, F, orders, H, scale, dtype, dq, dk, dv, scratch, stream);
+}

@@ -154,6 +154,29 @@ int gm_geometry_fill(const double* nodes, const double* frames, const double* we
                      void* log_coordinates, void* polar_angles, void* transport_angles, void* tangent_weights,
                      void* angular_phases, void* transport_phases, void* stream);
 
+/* ------------------------------------------------------------------------
+ * gm_attention_backward without any device allocation (no counterpart in the
+ * reference, which allocates through ATen).  For embedders that own all device
+ * memory themselves -- a runtime that commits the whole budget to its own
+ * arena at start-up, a latency-bound loop that must stay off the driver's
+ * allocator -- and so cannot obtain the fp32 accumulation buffer the bf16
+ * backward needs.  The buffer is a fixed array inside the library image
+ * (gm_attention_backward_static_capacity() bytes, held by every GPU that loads
+ * the library until the process ends); bigger problems
+ * (2 * batch * n_nodes * D * 4 bytes > capacity) return GM_ERR_LIMIT.
+ * Same arguments as gm_attention_backward minus `scratch`.  The first call on
+ * a device resolves the array's device address: issue it before any stream
+ * capture.  Calls on one device share the array; it is cleared at the start of
+ * each call, and calls that overlap on the GPU race on it.
+ * ------------------------------------------------------------------------ */
+int64_t gm_attention_backward_static_capacity(void);
+
+int gm_attention_backward_static(const void* dout, const void* q, const void* k, const void* v, const void* out,
+                                 const void* lse, const void* transport, const void* bias, const uint8_t* inside,
+                                 const int64_t* desc_host, const int64_t* row_ptr, const int64_t* source, int64_t n_nodes,
+                                 int64_t n_edges, int64_t batch, int D, int F, int orders, int H, double scale, int dtype,
+                                 void* dq, void* dk, void* dv, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
