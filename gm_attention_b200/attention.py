@@ -104,12 +104,14 @@ def attention_backward(dout: Tensor, q: Tensor, k: Tensor, v: Tensor, out: Tenso
 
 
 class GaugeAttention(torch.autograd.Function):
-    """``GaugeAttention.apply(q, k, v, tables) -> out``."""
+    """``GaugeAttention.apply(q, k, v, tables) -> out`` with ``tables`` an
+    :class:`AttentionTables` (any graph) or a :class:`LatticeTables` (equiangular lattice fast path)."""
 
     @staticmethod
-    def forward(ctx: Any, q: Tensor, k: Tensor, v: Tensor, tables: AttentionTables) -> Tensor:
+    def forward(ctx: Any, q: Tensor, k: Tensor, v: Tensor, tables: Any) -> Tensor:
+        forward = lattice_attention_forward if isinstance(tables, LatticeTables) else attention_forward
         with torch.profiler.record_function("gm::attention/fused"):
-            out, lse = attention_forward(q.contiguous(), k.contiguous(), v.contiguous(), tables)
+            out, lse = forward(q.contiguous(), k.contiguous(), v.contiguous(), tables)
         ctx.save_for_backward(q, k, v, out, lse)
         ctx.tables = tables
         return out
@@ -118,6 +120,184 @@ class GaugeAttention(torch.autograd.Function):
     @torch.autograd.function.once_differentiable
     def backward(ctx: Any, grad_out: Tensor) -> tuple:  # type: ignore[override]
         q, k, v, out, lse = ctx.saved_tensors
+        backward = lattice_attention_backward if isinstance(ctx.tables, LatticeTables) else attention_backward
         with torch.profiler.record_function("gm::attention/fused_backward"):
-            dq, dk, dv = attention_backward(grad_out, q.contiguous(), k.contiguous(), v.contiguous(), out, lse, ctx.tables)
+            dq, dk, dv = backward(grad_out, q.contiguous(), k.contiguous(), v.contiguous(), out, lse, ctx.tables)
         return dq, dk, dv, None
+
+
+# ----------------------------------------------------------------------------- equiangular lattices
+
+@dataclass(frozen=True)
+class LatticeTables:
+    """Compact per-(target row, source row, longitude offset) tables of a lattice
+    with longitude-equivariant frames, forward and transposed (see
+    ``gm_lattice_attention_forward`` in ``include/gm_b200.h``)."""
+
+    rows: int
+    nlon: int
+    halo: int  # W
+    entry_stride: int  # ES
+    orders: int  # NORD
+    win_cnt: Tensor
+    win_lo: Tensor
+    win_off: Tensor
+    entries: Tensor
+    row_order: Tensor
+    t_win_cnt: Tensor
+    t_win_lo: Tensor
+    t_win_off: Tensor
+    t_entries: Tensor
+    t_row_order: Tensor
+    desc_rows: tuple[tuple[int, int, int, int, int], ...]
+    heads: int
+    scale: float
+    n_edges: int  # edges of one sample
+
+    def host_descriptor(self) -> Any:
+        flat = [x for row in self.desc_rows for x in row]
+        return (ctypes.c_int64 * len(flat))(*flat)
+
+
+def lattice_layout_supported(rows: tuple[tuple[int, int, int, int, int], ...]) -> bool:
+    """Head layouts the lattice kernels serve: at most one scalar row, at most four
+    complex frequencies, all with the same multiplicity, runs of at most 4 copies per lane."""
+    complex_mult = {a for n, a, *_ in rows if n > 0}
+    scalar = [a for n, a, *_ in rows if n == 0]
+    n_cf = sum(1 for n, *_ in rows if n > 0)
+    if len(scalar) > 1 or len(complex_mult) > 1 or n_cf > 4:
+        return False
+    for lanes in (4, 8):
+        nr = -(-(scalar[0] if scalar else 0) // lanes)
+        uc = -(-(next(iter(complex_mult)) if complex_mult else 0) // lanes)
+        fits = any(nr <= a and n_cf <= b and uc <= c for a, b, c in ((1, 2, 1), (2, 2, 2), (2, 3, 2), (4, 2, 4), (4, 4, 4)))
+        if not fits:
+            return False
+    return True
+
+
+def build_lattice_tables(geometry: Any, rows: int, nlon: int, desc_rows: tuple[tuple[int, int, int, int, int], ...], heads: int,
+                         scale: float) -> LatticeTables:
+    """Collapse per-edge tables (``transport``, ``bias``, ``inside``, ``row_ptr``, ``source`` of a
+    :class:`gm_attention_b200.nn.fused_attention.Geometry` or :class:`AttentionTables`) of a
+    ``rows x nlon`` lattice into compact ones, reading the edges of the targets in column 0.
+    Raises ``ValueError`` when a neighbourhood is not a cyclic run of longitudes per source row
+    (the lattice / frames are then not longitude-symmetric: use the general kernels)."""
+    import numpy as np
+
+    device = geometry.row_ptr.device
+    if nlon % 2:
+        raise ValueError("the lattice path needs an even number of longitudes")
+    row_ptr = geometry.row_ptr.reshape(-1)
+    col0 = torch.arange(rows, device=device) * nlon
+    starts, stops = row_ptr[col0].cpu().numpy(), row_ptr[col0 + 1].cpu().numpy()
+    degree = stops - starts
+    index = np.concatenate([np.arange(a, b) for a, b in zip(starts, stops)]) if degree.sum() else np.zeros(0, np.int64)
+    index_t = torch.from_numpy(index).to(device)
+    source = geometry.source.index_select(0, index_t).cpu().numpy()
+    norders = max((n for n, *_ in desc_rows), default=0)
+    if geometry.transport.shape[1] <= norders:
+        raise ValueError(f"the transport table holds orders < {geometry.transport.shape[1]}, the heads need {norders}")
+    tau = geometry.transport.index_select(0, index_t)[:, 1:norders + 1].float().cpu().numpy()  # (n, NORD, 2)
+    bias = geometry.bias.index_select(0, index_t).float().cpu().numpy()
+    inside = geometry.inside.index_select(0, index_t).cpu().numpy()
+    bias = np.where(inside > 0, bias, -np.inf).astype(np.float32)
+    owner_row = np.repeat(np.arange(rows), degree)
+    src_row, src_lon = source // nlon, source % nlon
+    dlon = np.where(src_lon < nlon // 2, src_lon, src_lon - nlon)
+    drow = src_row - owner_row
+    halo = int(np.abs(drow).max()) if drow.size else 0
+    stride = 8 if 2 * norders + 1 <= 8 else 16
+    width = 2 * halo + 1
+    order = np.lexsort((dlon, drow, owner_row))
+    owner_row, drow, dlon, tau, bias = owner_row[order], drow[order], dlon[order], tau[order], bias[order]
+    win_cnt = np.zeros((rows, width), np.int32)
+    win_lo = np.zeros((rows, width), np.int32)
+    win_off = np.zeros((rows, width), np.int32)
+    key = owner_row * width + (drow + halo)
+    boundaries = np.flatnonzero(np.diff(key, prepend=-1)) if key.size else np.zeros(0, np.int64)
+    ends = np.append(boundaries[1:], key.size)
+    for a, b in zip(boundaries, ends):
+        run = dlon[a:b]
+        if not np.array_equal(run, np.arange(run[0], run[0] + (b - a))):
+            raise ValueError("a neighbourhood is not a contiguous run of longitude offsets: not a longitude-symmetric lattice")
+        i, c = divmod(int(key[a]), width)
+        win_cnt[i, c], win_lo[i, c], win_off[i, c] = b - a, run[0], a
+    entries = np.zeros((key.size, stride), np.float32)
+    entries[:, :2 * norders] = tau.reshape(key.size, 2 * norders)
+    entries[:, 2 * norders] = bias
+    # transposed: owner = source row j, neighbours = targets in row i = j + di that see it; offsets negate, entries reverse
+    t_cnt = np.zeros_like(win_cnt)
+    t_lo = np.zeros_like(win_lo)
+    t_off = np.zeros_like(win_off)
+    t_entries = np.zeros_like(entries)
+    cursor = 0
+    for j in range(rows):
+        for c in range(width):
+            i = j + (c - halo)
+            if not 0 <= i < rows:
+                continue
+            cc = (j - i) + halo
+            n = int(win_cnt[i, cc])
+            if n == 0:
+                continue
+            a = int(win_off[i, cc])
+            t_cnt[j, c], t_lo[j, c], t_off[j, c] = n, -(int(win_lo[i, cc]) + n - 1), cursor
+            t_entries[cursor:cursor + n] = entries[a:a + n][::-1]
+            cursor += n
+    cost = win_cnt.sum(1)
+    t_cost = t_cnt.sum(1)
+    row_order = np.array([r for r in np.argsort(-cost, kind="stable") if cost[r] > 0], np.int32)
+    t_row_order = np.array([r for r in np.argsort(-t_cost, kind="stable") if t_cost[r] > 0], np.int32)
+    dev = lambda x: torch.from_numpy(np.ascontiguousarray(x)).to(device)
+    return LatticeTables(rows, nlon, halo, stride, norders, dev(win_cnt), dev(win_lo), dev(win_off), dev(entries), dev(row_order),
+                         dev(t_cnt), dev(t_lo), dev(t_off), dev(t_entries), dev(t_row_order), tuple(tuple(int(x) for x in r) for r in desc_rows),
+                         heads, float(scale), int(geometry.source.shape[0]))
+
+
+def _check_lattice(q: Tensor, k: Tensor, v: Tensor, t: LatticeTables) -> tuple[torch.device, int]:
+    device = _lib.require_cuda(q, k, v, t.entries)
+    if not (q.dim() == 2 and q.shape == k.shape == v.shape and q.dtype == k.dtype == v.dtype):
+        raise RuntimeError("q, k and v must be (batch * n_nodes, D) tensors of one dtype")
+    if q.dtype not in (torch.float32, torch.bfloat16):
+        raise RuntimeError("the lattice kernels take float32 or bfloat16 node fields")
+    if not (q.is_contiguous() and k.is_contiguous() and v.is_contiguous()):
+        raise RuntimeError("q, k and v must be contiguous")
+    n = t.rows * t.nlon
+    if q.shape[0] % n:
+        raise RuntimeError(f"the node fields hold {q.shape[0]} rows, not a multiple of the lattice's {n} nodes")
+    return device, q.shape[0] // n
+
+
+def lattice_attention_forward(q: Tensor, k: Tensor, v: Tensor, t: LatticeTables) -> tuple[Tensor, Tensor]:
+    device, batch = _check_lattice(q, k, v, t)
+    full = t.row_order.numel() == t.rows
+    out = torch.empty_like(q) if full else torch.zeros_like(q)
+    lse = torch.empty((q.shape[0], t.heads), dtype=torch.float32, device=device) if full else \
+        torch.full((q.shape[0], t.heads), float("-inf"), dtype=torch.float32, device=device)
+    desc = t.host_descriptor()
+    with torch.cuda.device(device):
+        _lib.call("gm_lattice_attention_forward", _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(t.win_cnt), _lib.ptr(t.win_lo),
+                  _lib.ptr(t.win_off), _lib.ptr(t.entries), _lib.ptr(t.row_order), t.row_order.numel(), ctypes.addressof(desc),
+                  len(t.desc_rows), t.rows, t.nlon, batch, q.shape[1], t.heads, t.halo, t.entry_stride, t.orders, float(t.scale),
+                  _lib.dtype_code(q.dtype), _lib.ptr(out), _lib.ptr(lse), _lib.stream(device))
+    return out, lse
+
+
+def lattice_attention_backward(dout: Tensor, q: Tensor, k: Tensor, v: Tensor, out: Tensor, lse: Tensor,
+                               t: LatticeTables) -> tuple[Tensor, Tensor, Tensor]:
+    device, batch = _check_lattice(q, k, v, t)
+    dout = dout.contiguous()
+    alloc = torch.empty_like if t.row_order.numel() == t.rows else torch.zeros_like
+    alloc_t = torch.empty_like if t.t_row_order.numel() == t.rows else torch.zeros_like
+    dq, dk, dv = alloc(q), alloc_t(q), alloc_t(q)
+    delta = torch.empty((q.shape[0], t.heads), dtype=torch.float32, device=device)
+    desc = t.host_descriptor()
+    with torch.cuda.device(device):
+        _lib.call("gm_lattice_attention_backward", _lib.ptr(dout), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(lse),
+                  _lib.ptr(t.win_cnt), _lib.ptr(t.win_lo), _lib.ptr(t.win_off), _lib.ptr(t.entries), _lib.ptr(t.row_order),
+                  t.row_order.numel(), _lib.ptr(t.t_win_cnt), _lib.ptr(t.t_win_lo), _lib.ptr(t.t_win_off), _lib.ptr(t.t_entries),
+                  _lib.ptr(t.t_row_order), t.t_row_order.numel(), ctypes.addressof(desc), len(t.desc_rows), t.rows, t.nlon, batch,
+                  q.shape[1], t.heads, t.halo, t.entry_stride, t.orders, float(t.scale), _lib.dtype_code(q.dtype), _lib.ptr(dq),
+                  _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(delta), _lib.stream(device))
+    return dq, dk, dv

@@ -177,6 +177,41 @@ int gm_attention_backward_static(const void* dout, const void* q, const void* k,
                                  int64_t n_edges, int64_t batch, int D, int F, int orders, int H, double scale, int dtype,
                                  void* dq, void* dk, void* dv, void* stream);
 
+/* ------------------------------------------------------------------------
+ * The fused layer on an equiangular lattice with longitude-equivariant frames
+ * (fast path of gm_attention_forward / gm_attention_backward; same arithmetic).
+ * Every per-edge quantity depends on (target row, source row, longitude offset)
+ * only, so the per-edge tables collapse to compact ones:
+ *
+ *   win_cnt/win_lo/win_off (rows, 2W + 1) int32: for target row i and source row
+ *       j = i + dj (dj in [-W, W]) the neighbours are the cnt longitudes
+ *       t + lo .. t + lo + cnt - 1 (mod nlon) of a target at longitude t, and their
+ *       entries start at entry win_off; cnt = 0: none
+ *   entries (n_entries, ES) fp32: (cos, sin) of n * gamma for n = 1..NORD, then the
+ *       bias (-inf for a pair outside the window's support) at index 2 * NORD
+ *   row_order (n_order_rows) int32: the rows that own targets, heaviest first
+ *   t_*: the same tables transposed (owner = source row, neighbours = the targets
+ *       that see it), used by the backward's source-major pass
+ *
+ * Node fields are (batch, rows, nlon, D), fp32 or bf16 (fp32 arithmetic); head
+ * layouts: an optional scalar block plus complex frequencies sharing one
+ * multiplicity (else GM_ERR_UNSUPPORTED: use the general entry points).
+ * The backward is deterministic (no atomics): dq from a target-major pass, dk
+ * and dv from a source-major pass; rows outside row_order / t_row_order are not
+ * written.  `delta` is caller-provided workspace, (batch * rows * nlon, H) fp32.
+ * ------------------------------------------------------------------------ */
+int gm_lattice_attention_forward(const void* q, const void* k, const void* v, const int* win_cnt, const int* win_lo,
+                                 const int* win_off, const float* entries, const int* row_order, int n_order_rows,
+                                 const int64_t* desc_host, int F, int rows, int nlon, int64_t batch, int D, int H, int W, int ES,
+                                 int NORD, double scale, int dtype, void* out, float* lse, void* stream);
+
+int gm_lattice_attention_backward(const void* dout, const void* q, const void* k, const void* v, const void* out, const float* lse,
+                                  const int* win_cnt, const int* win_lo, const int* win_off, const float* entries,
+                                  const int* row_order, int n_order_rows, const int* t_win_cnt, const int* t_win_lo,
+                                  const int* t_win_off, const float* t_entries, const int* t_row_order, int t_n_order_rows,
+                                  const int64_t* desc_host, int F, int rows, int nlon, int64_t batch, int D, int H, int W, int ES,
+                                  int NORD, double scale, int dtype, void* dq, void* dk, void* dv, float* delta, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

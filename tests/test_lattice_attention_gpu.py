@@ -1,0 +1,113 @@
+"""The equiangular-lattice fast path of the fused layer against the oracle and
+against the general CSR kernels: forward and the deterministic two-pass
+backward, float32 (1e-5 relative / 1e-6 absolute, absolute part scaled by the
+tensor's magnitude) and bf16 storage (2e-2 relative to the magnitude)."""
+
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+
+from tests.helpers import assert_close, cuda, make_case, rel_err, seeded
+
+pytestmark = pytest.mark.gpu
+
+CASES = [
+    # nlat, nlon, radius, head type, heads, window, batch
+    (16, 32, 2 * math.pi / 16, {0: 4, 1: 4, 2: 4}, 2, "hard", 2),         # BASELINE config 1 layout
+    (12, 24, 3 * math.pi / 12, {0: 16, 1: 16, 2: 16}, 4, "hard", 1),      # headline layout; polar windows are whole rows
+    (8, 16, 2.5 * math.pi / 8, {0: 2, 1: 2}, 4, "quartic", 2),             # pairs outside the quartic window's support
+    (10, 20, 2 * math.pi / 10, {0: 8, 1: 8, 2: 8, 3: 8}, 4, "hard", 1),   # BASELINE config 2 layout
+    (8, 256, 1.2 * math.pi / 8, {0: 4, 1: 4, 2: 4}, 2, "hard", 1),        # wide windows: several staged chunks per row
+    (8, 16, 2 * math.pi / 8, {1: 6, 2: 6}, 1, "hard", 2),                 # no scalar block, runs of 2 with idle slots
+    (8, 16, 2 * math.pi / 8, {0: 3, 2: 5}, 2, "hard", 1),                 # odd multiplicities: unaligned runs
+]
+
+
+def tables_for(c):
+    from gm_attention_b200.attention import AttentionTables, build_lattice_tables
+
+    rows = tuple(tuple(int(x) for x in row) for row in c.desc)
+    general = AttentionTables(cuda(c.transport), cuda(c.bias), cuda(c.inside), cuda(c.row_ptr), cuda(c.source), rows, c.heads, c.scale)
+    return general, build_lattice_tables(general, c.nlat, c.nlon, rows, c.heads, c.scale)
+
+
+@pytest.mark.parametrize("case", CASES)
+def test_lattice_matches_oracle_float32(case):
+    from gm_attention_b200.attention import lattice_attention_backward, lattice_attention_forward
+
+    batch = case[6]
+    c = make_case(*case[:5], dtype=np.float32, window=case[5])
+    q, k, v, g = seeded((batch * c.n_nodes, c.width), 51, np.float32, 4)
+    want = O.attention_forward(q, k, v, c.transport, c.bias, c.inside, c.desc, c.row_ptr, c.source, c.heads, c.scale, batch)
+    grads = O.attention_backward(g, q, k, v, c.transport, c.bias, c.inside, c.desc, c.row_ptr, c.source, c.heads, c.scale, batch)
+    _, lat = tables_for(c)
+    assert lat.n_edges == c.source.shape[0]
+    Q, K, V, G = cuda(q), cuda(k), cuda(v), cuda(g)
+    out, lse = lattice_attention_forward(Q, K, V, lat)
+    assert_close(out.cpu().numpy(), want, 1e-5, 1e-6 * max(1.0, np.abs(want).max()), "out")
+    got = lattice_attention_backward(G, Q, K, V, out, lse, lat)
+    for name, a, b in zip(("dq", "dk", "dv"), got, grads):
+        assert_close(a.cpu().numpy(), b, 1e-5, 1e-5 * max(1.0, np.abs(b).max()), name)
+
+
+@pytest.mark.parametrize("case", CASES[:4])
+def test_lattice_bf16_storage(case):
+    from gm_attention_b200.attention import lattice_attention_backward, lattice_attention_forward
+
+    batch = case[6]
+    c = make_case(*case[:5], dtype=np.float32, window=case[5])
+    rounded = [torch.from_numpy(x).bfloat16() for x in seeded((batch * c.n_nodes, c.width), 52, np.float32, 4)]
+    q, k, v, g = (x.float().numpy() for x in rounded)
+    want = O.attention_forward(q, k, v, c.transport, c.bias, c.inside, c.desc, c.row_ptr, c.source, c.heads, c.scale, batch)
+    grads = O.attention_backward(g, q, k, v, c.transport, c.bias, c.inside, c.desc, c.row_ptr, c.source, c.heads, c.scale, batch)
+    _, lat = tables_for(c)
+    Q, K, V, G = (x.cuda() for x in rounded)
+    out, lse = lattice_attention_forward(Q, K, V, lat)
+    assert rel_err(out.float().cpu().numpy(), want) < 2e-2
+    got = lattice_attention_backward(G, Q, K, V, out, lse, lat)
+    for name, a, b in zip(("dq", "dk", "dv"), got, grads):
+        assert rel_err(a.float().cpu().numpy(), b) < 2e-2, name
+
+
+def test_lattice_agrees_with_the_general_kernels_and_is_deterministic():
+    from gm_attention_b200.attention import (attention_backward, attention_forward, lattice_attention_backward,
+                                             lattice_attention_forward)
+
+    c = make_case(16, 32, 3 * math.pi / 16, {0: 16, 1: 16, 2: 16}, 4, dtype=np.float32)
+    general, lat = tables_for(c)
+    Q, K, V, G = (cuda(x) for x in seeded((2 * c.n_nodes, c.width), 53, np.float32, 4))
+    out_a, lse_a = attention_forward(Q, K, V, general)
+    out_b, lse_b = lattice_attention_forward(Q, K, V, lat)
+    assert_close(out_b.cpu().numpy(), out_a.cpu().numpy(), 1e-5, 2e-6, "out")
+    assert_close(lse_b.cpu().numpy(), lse_a.cpu().numpy(), 1e-5, 1e-5, "lse")
+    first = lattice_attention_backward(G, Q, K, V, out_b, lse_b, lat)
+    again = lattice_attention_backward(G, Q, K, V, out_b, lse_b, lat)
+    for a, b in zip(first, again):
+        assert torch.equal(a, b)  # no atomics: bit-identical reruns
+    for name, a, b in zip(("dq", "dk", "dv"), first, attention_backward(G, Q, K, V, out_a, lse_a, general)):
+        assert_close(a.cpu().numpy(), b.cpu().numpy(), 1e-5, 1e-5 * max(1.0, float(b.abs().max())), name)
+
+
+def test_lattice_through_autograd_and_unsupported_layout():
+    from gm_attention_b200.attention import GaugeAttention, build_lattice_tables, lattice_layout_supported
+
+    c = make_case(8, 16, 2 * math.pi / 8, {0: 4, 1: 4, 2: 4}, 2, dtype=np.float32)
+    _, lat = tables_for(c)
+    q, k, v = (cuda(x).requires_grad_(True) for x in seeded((c.n_nodes, c.width), 54, np.float32, 3))
+    g, = seeded((c.n_nodes, c.width), 55, np.float32)
+    out = GaugeAttention.apply(q, k, v, lat)
+    (out * cuda(g)).sum().backward()
+    grads = O.attention_backward(g, q.detach().cpu().numpy(), k.detach().cpu().numpy(), v.detach().cpu().numpy(), c.transport, c.bias,
+                                 c.inside, c.desc, c.row_ptr, c.source, c.heads, c.scale, 1)
+    for name, a, b in zip(("dq", "dk", "dv"), (q.grad, k.grad, v.grad), grads):
+        assert_close(a.cpu().numpy(), b, 1e-5, 1e-5 * max(1.0, np.abs(b).max()), name)
+    odd = make_case(6, 12, 2 * math.pi / 6, {1: 3, 3: 2}, 1, dtype=np.float32)
+    rows = tuple(tuple(int(x) for x in row) for row in odd.desc)
+    assert not lattice_layout_supported(rows)
+    assert lattice_layout_supported(lat.desc_rows)
