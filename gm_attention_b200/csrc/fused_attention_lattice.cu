@@ -115,22 +115,21 @@ __global__ void __launch_bounds__(LAT_THREADS) lattice_kernel(LatArgs<S> a) {
   float* s2 = smem + (size_t)SC * pitch;
   float* sstat = s2 + (size_t)SC * pitch;  // (SC, 2): lse, delta of the staged rows (pass S)
 
-  // The lane's runs: scalars u = ls * NR + x (valid below a0), complex copies u = ls * UC + x (valid below ac).
-  // Invalid slots keep zero owner values (so they contribute nothing) and are never written.
+  // The lane's runs: scalars u = ls * NR + x (valid below a0), complex copies u = ls * UC + x (valid below ac,
+  // frequency below n_cf).  An invalid slot keeps zero owner values, reads a clamped (valid, finite) staged
+  // element so that it contributes exactly nothing, and is never written.  With ALIGNED the host guarantees
+  // that every slot of every lane is valid and every run starts on its vector boundary.
   const int real_u0 = ls * NR, cx_u0 = ls * UC;
-  // head-local offsets of the runs, clamped into the row so that idle slots read finite staged data
-  const int real_loc = min(real_u0, max(P.a0 - NR, 0));
-  int cx_loc[NCF > 0 ? NCF : 1];
-#pragma unroll
-  for (int f = 0; f < NCF; ++f) cx_loc[f] = P.a0 + 2 * P.ac * min(f, max(P.n_cf - 1, 0)) + 2 * min(cx_u0, max(P.ac - UC, 0));
-  // after clamping, the slot x of the run reads copy (loc-derived) u'; it is a real owner only if u' == u
-  const bool real_shifted = real_loc != real_u0, cx_shifted = min(cx_u0, max(P.ac - UC, 0)) != cx_u0;
+  auto real_valid = [&](int x) { return ALIGNED || real_u0 + x < P.a0; };
+  auto cx_valid = [&](int f, int x) { return ALIGNED || (f < P.n_cf && cx_u0 + x < P.ac); };
+  auto real_at = [&](int x) { return ALIGNED ? real_u0 + x : min(real_u0 + x, max(P.a0 - 1, 0)); };
+  auto cx_at = [&](int f, int x) {
+    return ALIGNED ? P.a0 + 2 * (P.ac * f + cx_u0 + x) : P.a0 + 2 * (P.ac * min(f, max(P.n_cf - 1, 0)) + min(cx_u0 + x, max(P.ac - 1, 0)));
+  };
 
   Slice<NR, NC> o1[TT], o2[TT], acc1[TT], acc2[TT];
   float own_lse[TT], own_delta[TT], m[TT], l[TT];
   bool own_ok[TT];
-  auto real_valid = [&](int x) { return !real_shifted && real_u0 + x < P.a0; };
-  auto cx_valid = [&](int f, int x) { return f < P.n_cf && !cx_shifted && cx_u0 + x < P.ac; };
 #pragma unroll
   for (int tt = 0; tt < TT; ++tt) {
     const int t = c0 + group * TT + tt;
@@ -212,20 +211,38 @@ __global__ void __launch_bounds__(LAT_THREADS) lattice_kernel(LatArgs<S> a) {
         const bool staged = p >= p0 && p < p0 + np;
         const int pl = staged ? p - p0 : 0;
         Slice<NR, NC> n1, n2;
-        if constexpr (NR > 0) {
-          load_run<NR, ALIGNED>(s1 + pl * pitch + real_loc, n1.re);
-          load_run<NR, ALIGNED>(s2 + pl * pitch + real_loc, n2.re);
-        }
-#pragma unroll
-        for (int f = 0; f < NCF; ++f) {
-          float t1[2 * UC], t2[2 * UC];
-          load_run<2 * UC, ALIGNED>(s1 + pl * pitch + cx_loc[f], t1);
-          load_run<2 * UC, ALIGNED>(s2 + pl * pitch + cx_loc[f], t2);
-#pragma unroll
-          for (int x = 0; x < UC; ++x) {
-            n1.cr[f * UC + x] = t1[2 * x]; n1.ci[f * UC + x] = t1[2 * x + 1];
-            n2.cr[f * UC + x] = t2[2 * x]; n2.ci[f * UC + x] = t2[2 * x + 1];
+        const float* row1 = s1 + pl * pitch;
+        const float* row2 = s2 + pl * pitch;
+        if constexpr (ALIGNED) {
+          if constexpr (NR > 0) {
+            load_run<NR, true>(row1 + real_u0, n1.re);
+            load_run<NR, true>(row2 + real_u0, n2.re);
           }
+#pragma unroll
+          for (int f = 0; f < NCF; ++f) {
+            float t1[2 * UC], t2[2 * UC];
+            load_run<2 * UC, true>(row1 + cx_at(f, 0), t1);
+            load_run<2 * UC, true>(row2 + cx_at(f, 0), t2);
+#pragma unroll
+            for (int x = 0; x < UC; ++x) {
+              n1.cr[f * UC + x] = t1[2 * x]; n1.ci[f * UC + x] = t1[2 * x + 1];
+              n2.cr[f * UC + x] = t2[2 * x]; n2.ci[f * UC + x] = t2[2 * x + 1];
+            }
+          }
+        } else {
+#pragma unroll
+          for (int x = 0; x < NR; ++x) {
+            n1.re[x] = row1[real_at(x)];
+            n2.re[x] = row2[real_at(x)];
+          }
+#pragma unroll
+          for (int f = 0; f < NCF; ++f)
+#pragma unroll
+            for (int x = 0; x < UC; ++x) {
+              const int at = cx_at(f, x);
+              n1.cr[f * UC + x] = row1[at]; n1.ci[f * UC + x] = row1[at + 1];
+              n2.cr[f * UC + x] = row2[at]; n2.ci[f * UC + x] = row2[at + 1];
+            }
         }
 #pragma unroll
         for (int tt = 0; tt < TT; ++tt) {
@@ -410,9 +427,10 @@ int make_lat_plan(const int64_t* desc_host, int F, int H, int D, int L, LatPlan&
   }
   P.d_head = P.a0 + 2 * P.ac * P.n_cf;
   P.pitch = P.d_head + ((8 - P.d_head % 16) + 16) % 16;  // pitch = 8 (mod 16) floats
+  // aligned: every lane owns full runs (a0 = NR * L, ac = UC * L) and every run starts on a 16-byte boundary
   const int nr = (P.a0 + L - 1) / L, uc = (P.ac + L - 1) / L;
-  P.aligned = (P.a0 % 4 == 0) && ((2 * P.ac) % 4 == 0) && (nr % 4 == 0 || nr == 0) && ((2 * uc) % 4 == 0 || uc == 0) &&
-              (P.a0 % (nr ? nr : 1) == 0) && (P.ac % (uc ? uc : 1) == 0);
+  P.aligned = (P.a0 == nr * L) && (P.ac == uc * L) && (P.a0 % 4 == 0) && (P.ac % 2 == 0) &&
+              (nr == 0 || nr == 1 || nr == 2 || nr == 4) && (uc == 0 || uc == 1 || uc == 2 || uc == 4);
   return GM_OK;
 }
 
@@ -459,7 +477,7 @@ int launch_lattice(const LatCall& c, const int64_t* desc_host, int F, int rows, 
   const int nr = (a.plan.a0 + L - 1) / L, uc = (a.plan.ac + L - 1) / L, ncf = a.plan.n_cf;
 #define GM_LAT_CASE(NR_, NCF_, UC_)                                                                 \
   if (nr <= NR_ && ncf <= NCF_ && uc <= UC_) {                                                      \
-    if (a.plan.aligned && nr == NR_ && uc == UC_) return go(lattice_kernel<S, NR_, NCF_, UC_, TT, MODE, true>); \
+    if (a.plan.aligned && nr == NR_ && uc == UC_ && ncf == NCF_) return go(lattice_kernel<S, NR_, NCF_, UC_, TT, MODE, true>); \
     return go(lattice_kernel<S, NR_, NCF_, UC_, TT, MODE, false>);                                   \
   }
   GM_LAT_CASE(1, 2, 1)
