@@ -39,6 +39,7 @@ sys.path.insert(0, str(ROOT))
 
 HEADLINE = dict(nlat=256, nlon=512, radius_rows=3, batch=8, heads=4, head_type={0: 16, 1: 16, 2: 16})
 SMALL = dict(nlat=64, nlon=128, radius_rows=3, batch=2, heads=4, head_type={0: 16, 1: 16, 2: 16})
+MID = dict(nlat=128, nlon=256, radius_rows=3, batch=4, heads=4, head_type={0: 16, 1: 16, 2: 16})  # profiling size: > L2, < 1 GB
 L2_BYTES = 126 * 1024 * 1024
 
 
@@ -49,7 +50,7 @@ def parse() -> argparse.Namespace:
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--dtype", choices=["bf16", "f32"], default="bf16")
     p.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    p.add_argument("--workload", choices=["headline", "small"], default="headline")
+    p.add_argument("--workload", choices=["headline", "mid", "small"], default="headline")
     p.add_argument("--kernel", choices=["lattice", "csr"], default="lattice",
                    help="lattice: compact-table fast path (default); csr: general per-edge-table kernels")
     p.add_argument("--no-cpu-baseline", action="store_true")
@@ -388,7 +389,7 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
 
 def main() -> None:
     args = parse()
-    cfg = HEADLINE if args.workload == "headline" else SMALL
+    cfg = {"headline": HEADLINE, "mid": MID, "small": SMALL}[args.workload]
     if args.impl == "reference":
         run_reference(args, cfg)
     else:
