@@ -33,6 +33,7 @@ namespace {
 
 constexpr int LAT_MAX_CF = 4;   // complex frequencies per head
 constexpr int LAT_THREADS = 128;
+constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
 enum { MODE_FWD = 0, MODE_BWD_T = 1, MODE_BWD_S = 2 };
 
 // A head's layout: optionally a_0 scalar copies, then n_cf complex frequencies of a_c copies each.
@@ -43,6 +44,7 @@ struct LatPlan {
   int cf_off[LAT_MAX_CF];     // flat offset of each complex frequency's block (all heads)
   int cf_order[LAT_MAX_CF];   // its frequency n >= 1
   int aligned;                // 1: every run a lane reads from shared memory starts on a 16-byte boundary
+  int stage_vec;              // 1: every head segment starts / ends on a 16-byte boundary of the stored element type
 };
 
 template <typename S>
@@ -179,24 +181,68 @@ __global__ void __launch_bounds__(LAT_THREADS) lattice_kernel(LatArgs<S> a) {
     for (int p0 = 0; p0 < window; p0 += SC) {
       const int np = min(SC, window - p0);
       __syncthreads();
-      // stage np neighbour rows (the head's columns of both fields) as fp32: one warp per row, lanes over columns
-      for (int p = warp; p < np; p += LAT_THREADS / 32) {
-        const int64_t nb = (nrow0 + wrap(c0 + lo + p0 + p, a.nlon)) * a.D;
-        for (int c = lane; c < P.d_head; c += 32) {
-          int g;
-          if (c < P.a0) {
-            g = P.real_off + h * P.a0 + c;
-          } else {
-            const int f = (c - P.a0) / (2 * P.ac);
-            g = P.cf_off[f] + 2 * h * P.ac + (c - P.a0 - 2 * P.ac * f);
-          }
-          s1[p * pitch + c] = ld<float>(a.f1 + nb + g);
-          s2[p * pitch + c] = ld<float>(a.f2 + nb + g);
+      // stage np neighbour rows (the head's columns of both fields) as fp32
+      if (P.stage_vec) {
+        // 16-byte global loads: EV elements per vector, V vectors per row; a lane keeps one vector slot for every row
+        constexpr int EV = 16 / (int)sizeof(S);
+        const int V = P.d_head / EV;
+        const int lanes_per_row = V <= 8 ? 8 : (V <= 16 ? 16 : 32);
+        const int rows_per_pass = (32 / lanes_per_row) * (LAT_THREADS / 32);
+        const int sub = lane / lanes_per_row, vec = lane % lanes_per_row;
+        const int c = vec * EV;  // head-local column of the vector
+        int g = 0;
+        if (c < P.a0) {
+          g = P.real_off + h * P.a0 + c;
+        } else if (P.ac > 0) {
+          const int f = min((c - P.a0) / (2 * P.ac), P.n_cf - 1);
+          g = P.cf_off[f] + 2 * h * P.ac + (c - P.a0 - 2 * P.ac * f);
         }
-        if (MODE == MODE_BWD_S && lane == 0) {
-          const int64_t nn = (nrow0 + wrap(c0 + lo + p0 + p, a.nlon)) * a.H + h;
-          sstat[2 * p] = a.lse[nn];
-          sstat[2 * p + 1] = a.delta[nn];
+        for (int pp = warp * (32 / lanes_per_row) + sub; pp < np; pp += rows_per_pass) {
+          if (vec < V) {
+            const int64_t nb = (nrow0 + wrap(c0 + lo + p0 + pp, a.nlon)) * a.D + g;
+            const uint4 raw1 = __ldg(reinterpret_cast<const uint4*>(a.f1 + nb));
+            const uint4 raw2 = __ldg(reinterpret_cast<const uint4*>(a.f2 + nb));
+            float* d1 = s1 + pp * pitch + c;
+            float* d2 = s2 + pp * pitch + c;
+            if constexpr (sizeof(S) == 4) {
+              *reinterpret_cast<uint4*>(d1) = raw1;
+              *reinterpret_cast<uint4*>(d2) = raw2;
+            } else {  // 8 bf16 -> 8 floats: a bf16 is the upper half of the fp32 with the same value
+              const unsigned w1[4] = {raw1.x, raw1.y, raw1.z, raw1.w}, w2[4] = {raw2.x, raw2.y, raw2.z, raw2.w};
+#pragma unroll
+              for (int x = 0; x < 4; x += 2) {
+                *reinterpret_cast<float4*>(d1 + 2 * x) = make_float4(__uint_as_float(w1[x] << 16), __uint_as_float(w1[x] & 0xffff0000u),
+                                                                     __uint_as_float(w1[x + 1] << 16), __uint_as_float(w1[x + 1] & 0xffff0000u));
+                *reinterpret_cast<float4*>(d2 + 2 * x) = make_float4(__uint_as_float(w2[x] << 16), __uint_as_float(w2[x] & 0xffff0000u),
+                                                                     __uint_as_float(w2[x + 1] << 16), __uint_as_float(w2[x + 1] & 0xffff0000u));
+              }
+            }
+          }
+          if (MODE == MODE_BWD_S && vec == 0) {
+            const int64_t nn = (nrow0 + wrap(c0 + lo + p0 + pp, a.nlon)) * a.H + h;
+            sstat[2 * pp] = a.lse[nn];
+            sstat[2 * pp + 1] = a.delta[nn];
+          }
+        }
+      } else {
+        for (int p = warp; p < np; p += LAT_THREADS / 32) {
+          const int64_t nb = (nrow0 + wrap(c0 + lo + p0 + p, a.nlon)) * a.D;
+          for (int c = lane; c < P.d_head; c += 32) {
+            int g;
+            if (c < P.a0) {
+              g = P.real_off + h * P.a0 + c;
+            } else {
+              const int f = (c - P.a0) / (2 * P.ac);
+              g = P.cf_off[f] + 2 * h * P.ac + (c - P.a0 - 2 * P.ac * f);
+            }
+            s1[p * pitch + c] = ld<float>(a.f1 + nb + g);
+            s2[p * pitch + c] = ld<float>(a.f2 + nb + g);
+          }
+          if (MODE == MODE_BWD_S && lane == 0) {
+            const int64_t nn = (nrow0 + wrap(c0 + lo + p0 + p, a.nlon)) * a.H + h;
+            sstat[2 * p] = a.lse[nn];
+            sstat[2 * p + 1] = a.delta[nn];
+          }
         }
       }
       __syncthreads();
@@ -287,11 +333,12 @@ __global__ void __launch_bounds__(LAT_THREADS) lattice_kernel(LatArgs<S> a) {
             part += __shfl_xor_sync(0xffffffffu, part, o);
             if (MODE != MODE_FWD) dpart += __shfl_xor_sync(0xffffffffu, dpart, o);
           }
+          // logits are kept in base 2 (scale and bias carry log2 e), so the exponentials are single ex2 instructions
           const float bias = valid ? __ldg(e + 2 * a.NORD) : -INFINITY;
-          const float logit = a.scale * part + bias;
+          const float logit = LOG2E * (a.scale * part + bias);
           if (MODE == MODE_FWD) {
             if (logit > m[tt]) {
-              const float corr = expf(m[tt] - logit);
+              const float corr = exp2f(m[tt] - logit);
               l[tt] *= corr;
 #pragma unroll
               for (int s = 0; s < NR; ++s) acc1[tt].re[s] *= corr;
@@ -299,7 +346,7 @@ __global__ void __launch_bounds__(LAT_THREADS) lattice_kernel(LatArgs<S> a) {
               for (int s = 0; s < NC; ++s) { acc1[tt].cr[s] *= corr; acc1[tt].ci[s] *= corr; }
               m[tt] = logit;
             }
-            const float pr = expf(logit - m[tt]);  // exp(-inf) = 0 for masked or out-of-window pairs
+            const float pr = exp2f(logit - m[tt]);  // 2^(-inf) = 0 for masked or out-of-window pairs
             l[tt] += pr;
 #pragma unroll
             for (int s = 0; s < NR; ++s) acc1[tt].re[s] += pr * n2.re[s];
@@ -316,7 +363,7 @@ __global__ void __launch_bounds__(LAT_THREADS) lattice_kernel(LatArgs<S> a) {
           } else {
             const float lse = MODE == MODE_BWD_T ? own_lse[tt] : sstat[2 * pl];
             const float delta = MODE == MODE_BWD_T ? own_delta[tt] : sstat[2 * pl + 1];
-            const float pr = valid ? expf(logit - lse) : 0.f;
+            const float pr = valid ? exp2f(logit - LOG2E * lse) : 0.f;
             const float ds = a.scale * pr * (dpart - delta);
 #pragma unroll
             for (int s = 0; s < NR; ++s) {
@@ -374,7 +421,7 @@ __global__ void __launch_bounds__(LAT_THREADS) lattice_kernel(LatArgs<S> a) {
           st<S>(a.r2 + g + 1, acc2[tt].ci[s]);
         }
       }
-    if (MODE == MODE_FWD && ls == 0) a.lse_out[node * a.H + h] = l[tt] > 0.f ? m[tt] + logf(l[tt]) : -INFINITY;
+    if (MODE == MODE_FWD && ls == 0) a.lse_out[node * a.H + h] = l[tt] > 0.f ? (m[tt] + log2f(l[tt])) * LN2 : -INFINITY;
   }
 }
 
@@ -458,6 +505,13 @@ int launch_lattice(const LatCall& c, const int64_t* desc_host, int F, int rows, 
   a.lse = c.lse; a.delta = c.delta; a.r1 = (S*)c.r1; a.r2 = (S*)c.r2; a.lse_out = c.lse_out;
   a.win_cnt = c.win_cnt; a.win_lo = c.win_lo; a.win_off = c.win_off; a.entries = c.entries; a.row_order = c.row_order;
   a.rows = rows; a.nlon = nlon; a.D = D; a.H = H; a.W = W; a.ES = ES; a.NORD = NORD; a.scale = (float)scale;
+  {
+    const int ev = 16 / (int)sizeof(S);  // elements per 16-byte vector
+    bool ok = D % ev == 0 && a.plan.a0 % ev == 0 && (2 * a.plan.ac) % ev == 0 && a.plan.real_off % ev == 0 && a.plan.pitch % 4 == 0;
+    for (int f = 0; f < a.plan.n_cf; ++f) ok = ok && a.plan.cf_off[f] % ev == 0;
+    for (const void* ptr : {c.f1, c.f2}) ok = ok && (reinterpret_cast<uintptr_t>(ptr) % 16 == 0);
+    a.plan.stage_vec = ok ? 1 : 0;
+  }
   constexpr int TT = 2;
   const int TL = (LAT_THREADS / L) * TT;
   const int tiles = (nlon + TL - 1) / TL;
