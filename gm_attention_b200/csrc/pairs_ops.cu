@@ -1,0 +1,224 @@
+// The fused pair term of a steerable kernel, per edge -- the reference
+// extension's forward / backward (src/gm_attention/nn/fused/pairs_cpu.cpp:88-136,
+// arithmetic src/gm_attention/nn/fused/pairs.h:201-365):
+//
+//   out(e) += post(e) * f( M(e) (pre(e) u~(e)) ),   M(e) = W h(e) + b  (B x A, formed in registers)
+//
+// u~ = u or conj(u) (u real or complex), pre / post unit phases, post also
+// carries the real per-edge scale, f = identity or real part.  The backward
+// recomputes M, accumulates grad_u and grad_hidden in place and writes this
+// term's coefficient gradient grad_k (width, n_edges), coefficient-major.
+//
+// One thread per edge.  The input side (A <= 16) and the trunk (T <= 16) are
+// unrolled to their bounds with predicates so that every per-edge vector stays
+// in registers; the output side (B) is a runtime loop.  W and b are read
+// through the read-only path: every thread of a warp reads the same address.
+#include "common.cuh"
+
+namespace gmb {
+namespace {
+
+constexpr int PMAX = 16;
+enum { MATRIX_COMPLEX = 1, U_REAL = 2, CONJ_U = 4, OUT_REAL = 8 };
+
+template <typename T>
+struct PArgs {
+  int64_t n_edges;
+  int a, b, trunk, flags;
+  const T *hidden, *weight, *bias, *u, *pre, *post, *scale;
+  T* out;
+  const T* grad_out;
+  T *grad_u, *grad_hidden, *grad_k;
+};
+
+template <typename T>
+__device__ __forceinline__ void load_edge(const PArgs<T>& p, int64_t e, T (&h)[PMAX], T (&ur)[PMAX], T (&ui)[PMAX], T& s, T& pr, T& pi, T& qr, T& qi) {
+#pragma unroll
+  for (int k = 0; k < PMAX; ++k) h[k] = k < p.trunk ? p.hidden[e * p.trunk + k] : T(0);
+  pr = p.pre ? p.pre[2 * e] : T(1);
+  pi = p.pre ? p.pre[2 * e + 1] : T(0);
+  s = p.scale ? p.scale[e] : T(1);
+  qr = (p.post ? p.post[2 * e] : T(1)) * s;
+  qi = (p.post ? p.post[2 * e + 1] : T(0)) * s;
+#pragma unroll
+  for (int x = 0; x < PMAX; ++x) {
+    ur[x] = ui[x] = T(0);
+    if (x < p.a) {
+      T re, im;
+      if (p.flags & U_REAL) {
+        re = p.u[e * p.a + x];
+        im = T(0);
+      } else {
+        re = p.u[2 * (e * p.a + x)];
+        im = p.u[2 * (e * p.a + x) + 1];
+        if (p.flags & CONJ_U) im = -im;
+      }
+      ur[x] = pr * re - pi * im;  // uu = pre * u~
+      ui[x] = pr * im + pi * re;
+    }
+  }
+}
+
+// M_idx = <W rows, h> + b
+template <typename T>
+__device__ __forceinline__ void entry(const PArgs<T>& p, int idx, const T (&h)[PMAX], T& mr, T& mi) {
+  if (p.flags & MATRIX_COMPLEX) {
+    mr = p.bias ? __ldg(p.bias + 2 * idx) : T(0);
+    mi = p.bias ? __ldg(p.bias + 2 * idx + 1) : T(0);
+    const T* wr = p.weight + (int64_t)(2 * idx) * p.trunk;
+    const T* wi = wr + p.trunk;
+#pragma unroll
+    for (int k = 0; k < PMAX; ++k)
+      if (k < p.trunk) {
+        mr += __ldg(wr + k) * h[k];
+        mi += __ldg(wi + k) * h[k];
+      }
+  } else {
+    mr = p.bias ? __ldg(p.bias + idx) : T(0);
+    mi = T(0);
+    const T* w = p.weight + (int64_t)idx * p.trunk;
+#pragma unroll
+    for (int k = 0; k < PMAX; ++k)
+      if (k < p.trunk) mr += __ldg(w + k) * h[k];
+  }
+}
+
+template <typename T>
+__global__ void pairs_forward_kernel(PArgs<T> p) {
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < p.n_edges; e += (int64_t)gridDim.x * blockDim.x) {
+    T h[PMAX], ur[PMAX], ui[PMAX], s, pr, pi, qr, qi;
+    load_edge(p, e, h, ur, ui, s, pr, pi, qr, qi);
+    for (int bi = 0; bi < p.b; ++bi) {
+      T accr = T(0), acci = T(0);
+#pragma unroll
+      for (int x = 0; x < PMAX; ++x)
+        if (x < p.a) {
+          T mr, mi;
+          entry(p, bi * p.a + x, h, mr, mi);
+          accr += mr * ur[x] - mi * ui[x];
+          acci += mr * ui[x] + mi * ur[x];
+        }
+      if (p.flags & OUT_REAL) {
+        p.out[e * p.b + bi] += accr * s;
+      } else {
+        p.out[2 * (e * p.b + bi)] += qr * accr - qi * acci;
+        p.out[2 * (e * p.b + bi) + 1] += qr * acci + qi * accr;
+      }
+    }
+  }
+}
+
+template <typename T>
+__global__ void pairs_backward_kernel(PArgs<T> p) {
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < p.n_edges; e += (int64_t)gridDim.x * blockDim.x) {
+    T h[PMAX], ur[PMAX], ui[PMAX], s, pr, pi, qr, qi;
+    load_edge(p, e, h, ur, ui, s, pr, pi, qr, qi);
+    T gur[PMAX], gui[PMAX], gh[PMAX];
+#pragma unroll
+    for (int x = 0; x < PMAX; ++x) gur[x] = gui[x] = gh[x] = T(0);
+    for (int bi = 0; bi < p.b; ++bi) {
+      // gq = dL/dq for q = M uu: conj(post) g, or (g s, 0) for a real output
+      T gqr, gqi;
+      if (p.flags & OUT_REAL) {
+        gqr = p.grad_out[e * p.b + bi] * s;
+        gqi = T(0);
+      } else {
+        const T gr = p.grad_out[2 * (e * p.b + bi)], gi = p.grad_out[2 * (e * p.b + bi) + 1];
+        gqr = qr * gr + qi * gi;
+        gqi = qr * gi - qi * gr;
+      }
+#pragma unroll
+      for (int x = 0; x < PMAX; ++x)
+        if (x < p.a) {
+          const int idx = bi * p.a + x;
+          const T gmr = gqr * ur[x] + gqi * ui[x], gmi = gqi * ur[x] - gqr * ui[x];  // gm = gq conj(uu)
+          T mr, mi;
+          entry(p, idx, h, mr, mi);
+          gur[x] += mr * gqr + mi * gqi;  // guu += conj(m) gq
+          gui[x] += mr * gqi - mi * gqr;
+          if (p.flags & MATRIX_COMPLEX) {
+            const T* wr = p.weight + (int64_t)(2 * idx) * p.trunk;
+            const T* wi = wr + p.trunk;
+#pragma unroll
+            for (int k = 0; k < PMAX; ++k)
+              if (k < p.trunk) gh[k] += __ldg(wr + k) * gmr + __ldg(wi + k) * gmi;
+            p.grad_k[(int64_t)(2 * idx) * p.n_edges + e] = gmr;
+            p.grad_k[(int64_t)(2 * idx + 1) * p.n_edges + e] = gmi;
+          } else {
+            const T* w = p.weight + (int64_t)idx * p.trunk;
+#pragma unroll
+            for (int k = 0; k < PMAX; ++k)
+              if (k < p.trunk) gh[k] += __ldg(w + k) * gmr;
+            p.grad_k[(int64_t)idx * p.n_edges + e] = gmr;
+          }
+        }
+    }
+    // through uu = pre * u~ (and u~ = conj(u), or u real)
+#pragma unroll
+    for (int x = 0; x < PMAX; ++x)
+      if (x < p.a) {
+        const T gr = pr * gur[x] + pi * gui[x];  // conj(pre) guu
+        T gi = pr * gui[x] - pi * gur[x];
+        if (p.flags & U_REAL) {
+          p.grad_u[e * p.a + x] += gr;
+        } else {
+          if (p.flags & CONJ_U) gi = -gi;
+          p.grad_u[2 * (e * p.a + x)] += gr;
+          p.grad_u[2 * (e * p.a + x) + 1] += gi;
+        }
+      }
+#pragma unroll
+    for (int k = 0; k < PMAX; ++k)
+      if (k < p.trunk) p.grad_hidden[e * p.trunk + k] += gh[k];
+  }
+}
+
+int check_pairs(int64_t n_edges, int a, int b, int trunk, int flags, int dtype, const void* hidden, const void* weight, const void* u) {
+  GM_REQUIRE(n_edges >= 0, GM_ERR_ARGUMENT, "gm_pairs: negative size");
+  GM_REQUIRE(a >= 1 && a <= PMAX && b >= 1 && b <= PMAX, GM_ERR_ARGUMENT, "gm_pairs: block dimensions must be in 1..16");
+  GM_REQUIRE(trunk >= 1 && trunk <= PMAX, GM_ERR_ARGUMENT, "gm_pairs: trunk width must be in 1..16");
+  GM_REQUIRE(flags >= 0 && flags < 16, GM_ERR_ARGUMENT, "gm_pairs: unknown flags");
+  GM_REQUIRE(dtype == GM_F32 || dtype == GM_F64, GM_ERR_UNSUPPORTED, "gm_pairs: dtype must be float32 or float64");
+  if (n_edges == 0) return GM_OK;
+  GM_REQUIRE(hidden && weight && u, GM_ERR_ARGUMENT, "gm_pairs: null pointer");
+  return GM_OK;
+}
+
+}  // namespace
+}  // namespace gmb
+
+using namespace gmb;
+
+extern "C" int gm_pairs_forward(const void* hidden, const void* weight, const void* bias, const void* u, const void* pre,
+                                const void* post, const void* scale, void* out, int64_t n_edges, int a, int b, int trunk, int flags,
+                                int dtype, void* stream) {
+  int status = check_pairs(n_edges, a, b, trunk, flags, dtype, hidden, weight, u);
+  if (status != GM_OK || n_edges == 0) return status;
+  GM_REQUIRE(out, GM_ERR_ARGUMENT, "gm_pairs_forward: null out");
+  auto run = [&](auto tag) {
+    using T = decltype(tag);
+    PArgs<T> p{n_edges, a, b, trunk, flags, (const T*)hidden, (const T*)weight, (const T*)bias, (const T*)u, (const T*)pre,
+               (const T*)post, (const T*)scale, (T*)out, nullptr, nullptr, nullptr, nullptr};
+    const unsigned blocks = (unsigned)((n_edges + 127) / 128 < 148 * 32 ? (n_edges + 127) / 128 : 148 * 32);
+    pairs_forward_kernel<T><<<blocks, 128, 0, (cudaStream_t)stream>>>(p);
+    return launch_status("gm_pairs_forward");
+  };
+  return dtype == GM_F32 ? run(float()) : run(double());
+}
+
+extern "C" int gm_pairs_backward(const void* hidden, const void* weight, const void* bias, const void* u, const void* pre,
+                                 const void* post, const void* scale, const void* grad_out, void* grad_u, void* grad_hidden,
+                                 void* grad_k, int64_t n_edges, int a, int b, int trunk, int flags, int dtype, void* stream) {
+  int status = check_pairs(n_edges, a, b, trunk, flags, dtype, hidden, weight, u);
+  if (status != GM_OK || n_edges == 0) return status;
+  GM_REQUIRE(grad_out && grad_u && grad_hidden && grad_k, GM_ERR_ARGUMENT, "gm_pairs_backward: null pointer");
+  auto run = [&](auto tag) {
+    using T = decltype(tag);
+    PArgs<T> p{n_edges, a, b, trunk, flags, (const T*)hidden, (const T*)weight, (const T*)bias, (const T*)u, (const T*)pre,
+               (const T*)post, (const T*)scale, nullptr, (const T*)grad_out, (T*)grad_u, (T*)grad_hidden, (T*)grad_k};
+    const unsigned blocks = (unsigned)((n_edges + 127) / 128 < 148 * 32 ? (n_edges + 127) / 128 : 148 * 32);
+    pairs_backward_kernel<T><<<blocks, 128, 0, (cudaStream_t)stream>>>(p);
+    return launch_status("gm_pairs_backward");
+  };
+  return dtype == GM_F32 ? run(float()) : run(double());
+}

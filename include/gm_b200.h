@@ -212,6 +212,62 @@ int gm_lattice_attention_backward(const void* dout, const void* q, const void* k
                                   const int64_t* desc_host, int F, int rows, int nlon, int64_t batch, int D, int H, int W, int ES,
                                   int NORD, double scale, int dtype, void* dq, void* dk, void* dv, float* delta, void* stream);
 
+/* ------------------------------------------------------------------------
+ * Factored steerable kernel (drop-in for the reference extension's forward /
+ * aggregate / backward / backward_aggregated: factored_cpu.cpp:77-219,
+ * arithmetic factored.h:118-347).
+ *
+ *   h          (n_edges, k - 1)       trunk features; h~ = (1, h)
+ *   zc         (n_nodes, k, wc, 2), zr (n_nodes, k, wr)   node-side mixes
+ *   angular, transport (n_edges, n_f, 2); rho (n_edges)
+ *   desc       (n_blocks, 8) int32    rows (kind, z_off, b_m, ang, trn, power, out_off, take_real),
+ *                                     sorted by out_off
+ *   order (n_edges), group_ptr (n_groups + 1), group_source (n_groups) int64:
+ *              the edges sorted by source, each source's run, the sources
+ *   out / rows (n_edges, d_out)
+ * gm_factored_backward: g is (n_edges, d_out), or -- the aggregated form, when
+ * `target` is non-NULL -- (n_targets, d_out) read through target[e] and scaled
+ * by weights[e], with dweights[e] = <g[target[e]], rows[e]> also written.
+ * dh (n_edges, k - 1) is written; dzc, dzr are written for every source that has
+ * edges (zero them first: nodes without edges keep zero).
+ * The packed width 2 wc + wr is bounded by k * (2 wc + wr) <= 8192 (the
+ * reference stops at 320).  dtype: GM_F32 or GM_F64.
+ * ------------------------------------------------------------------------ */
+int gm_factored_forward(const void* h, const void* zc, const void* zr, const void* angular, const void* transport,
+                        const void* rho, const int32_t* desc, const int64_t* source, const int64_t* order,
+                        const int64_t* group_ptr, const int64_t* group_source, int64_t n_edges, int64_t n_groups, int k, int wc,
+                        int wr, int n_f, int n_blocks, int d_out, int dtype, void* out, void* stream);
+
+int gm_factored_aggregate(const void* rows, const void* weights, const int64_t* row_ptr, int64_t n_targets, int64_t n_edges,
+                          int d_out, int dtype, void* out, void* stream);
+
+int gm_factored_backward(const void* g, const int64_t* target, const void* weights, const void* rows, const void* h,
+                         const void* zc, const void* zr, const void* angular, const void* transport, const void* rho,
+                         const int32_t* desc, const int64_t* source, const int64_t* order, const int64_t* group_ptr,
+                         const int64_t* group_source, int64_t n_edges, int64_t n_groups, int k, int wc, int wr, int n_f,
+                         int n_blocks, int d_out, int dtype, void* dh, void* dzc, void* dzr, void* dweights, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Pair term of the general steerable kernel (drop-in for the reference
+ * extension's forward / backward: pairs_cpu.cpp:88-136, arithmetic
+ * pairs.h:201-365).  out(e) += post(e) f(M(e) (pre(e) u~(e))), M = W h(e) + b.
+ *
+ *   hidden (n_edges, trunk); weight (width, trunk), bias (width) or NULL,
+ *       width = (MATRIX_COMPLEX ? 2 : 1) * a * b
+ *   u      (n_edges, a) real (U_REAL) or (n_edges, a, 2) complex
+ *   pre, post (n_edges, 2) complex or NULL; scale (n_edges) or NULL
+ *   out    (n_edges, b) real (OUT_REAL) or (n_edges, b, 2); ACCUMULATED
+ *   grad_u, grad_hidden: ACCUMULATED in place; grad_k (width, n_edges) written
+ *   flags: MATRIX_COMPLEX = 1, U_REAL = 2, CONJ_U = 4, OUT_REAL = 8; a, b, trunk in 1..16
+ * dtype: GM_F32 or GM_F64.
+ * ------------------------------------------------------------------------ */
+int gm_pairs_forward(const void* hidden, const void* weight, const void* bias, const void* u, const void* pre, const void* post,
+                     const void* scale, void* out, int64_t n_edges, int a, int b, int trunk, int flags, int dtype, void* stream);
+
+int gm_pairs_backward(const void* hidden, const void* weight, const void* bias, const void* u, const void* pre, const void* post,
+                      const void* scale, const void* grad_out, void* grad_u, void* grad_hidden, void* grad_k, int64_t n_edges,
+                      int a, int b, int trunk, int flags, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
