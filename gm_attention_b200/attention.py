@@ -16,6 +16,7 @@ bfloat16 (bf16 storage, fp32 arithmetic; the tables are then float32).
 from __future__ import annotations
 
 import ctypes
+import os
 from dataclasses import dataclass
 from typing import Any
 
@@ -269,18 +270,39 @@ def _check_lattice(q: Tensor, k: Tensor, v: Tensor, t: LatticeTables) -> tuple[t
     return device, q.shape[0] // n
 
 
-def lattice_attention_forward(q: Tensor, k: Tensor, v: Tensor, t: LatticeTables) -> tuple[Tensor, Tensor]:
+def tensor_core_layout_supported(rows: tuple[tuple[int, int, int, int, int], ...]) -> bool:
+    """Head layouts of the tensor-core lattice kernels: an optional scalar block of <= 16 copies and one
+    to three complex frequencies sharing a multiplicity <= 16 (the instantiated combinations)."""
+    scalar = [a for n, a, *_ in rows if n == 0]
+    mult = {a for n, a, *_ in rows if n > 0}
+    n_cf = sum(1 for n, *_ in rows if n > 0)
+    if len(scalar) > 1 or len(mult) != 1 or (scalar and scalar[0] > 16) or next(iter(mult)) > 16:
+        return False
+    ksc = 2 if next(iter(mult)) > 8 else 1
+    return (bool(scalar), n_cf, ksc) in {(True, 2, 2), (True, 2, 1), (True, 3, 1), (True, 1, 2), (True, 1, 1), (False, 2, 1)}
+
+
+#: "auto": bf16 node fields take the tensor-core kernels when the head layout allows; "0": never
+TENSOR_CORES = os.environ.get("GM_LATTICE_TENSOR_CORES", "auto")
+
+
+def lattice_attention_forward(q: Tensor, k: Tensor, v: Tensor, t: LatticeTables, tensor_cores: bool | None = None) -> tuple[Tensor, Tensor]:
     device, batch = _check_lattice(q, k, v, t)
+    if tensor_cores is None:
+        tensor_cores = TENSOR_CORES != "0" and q.dtype == torch.bfloat16 and tensor_core_layout_supported(t.desc_rows)
     full = t.row_order.numel() == t.rows
     out = torch.empty_like(q) if full else torch.zeros_like(q)
     lse = torch.empty((q.shape[0], t.heads), dtype=torch.float32, device=device) if full else \
         torch.full((q.shape[0], t.heads), float("-inf"), dtype=torch.float32, device=device)
     desc = t.host_descriptor()
+    common = (_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(t.win_cnt), _lib.ptr(t.win_lo), _lib.ptr(t.win_off), _lib.ptr(t.entries),
+              _lib.ptr(t.row_order), t.row_order.numel(), ctypes.addressof(desc), len(t.desc_rows), t.rows, t.nlon, batch, q.shape[1],
+              t.heads, t.halo, t.entry_stride, t.orders, float(t.scale))
     with torch.cuda.device(device):
-        _lib.call("gm_lattice_attention_forward", _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(t.win_cnt), _lib.ptr(t.win_lo),
-                  _lib.ptr(t.win_off), _lib.ptr(t.entries), _lib.ptr(t.row_order), t.row_order.numel(), ctypes.addressof(desc),
-                  len(t.desc_rows), t.rows, t.nlon, batch, q.shape[1], t.heads, t.halo, t.entry_stride, t.orders, float(t.scale),
-                  _lib.dtype_code(q.dtype), _lib.ptr(out), _lib.ptr(lse), _lib.stream(device))
+        if tensor_cores:
+            _lib.call("gm_lattice_attention_forward_tc", *common, _lib.ptr(out), _lib.ptr(lse), _lib.stream(device))
+        else:
+            _lib.call("gm_lattice_attention_forward", *common, _lib.dtype_code(q.dtype), _lib.ptr(out), _lib.ptr(lse), _lib.stream(device))
     return out, lse
 
 

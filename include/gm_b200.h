@@ -268,6 +268,20 @@ int gm_pairs_backward(const void* hidden, const void* weight, const void* bias, 
                       const void* scale, const void* grad_out, void* grad_u, void* grad_hidden, void* grad_k, int64_t n_edges,
                       int a, int b, int trunk, int flags, int dtype, void* stream);
 
+/* ------------------------------------------------------------------------
+ * Tensor-core variants of the lattice fast path for bf16 node fields (same
+ * tables, same results within bf16 rounding of the attention weights): the
+ * per-frequency Gram blocks and the (alpha o tau) V sums run as m16n8k16 bf16
+ * matrix products on 16 x 16 (target, source) tiles of the longitude band.
+ * Head layouts: an optional scalar block of <= 16 copies and up to three complex
+ * frequencies sharing one multiplicity <= 16; otherwise GM_ERR_UNSUPPORTED (use
+ * gm_lattice_attention_forward).
+ * ------------------------------------------------------------------------ */
+int gm_lattice_attention_forward_tc(const void* q, const void* k, const void* v, const int* win_cnt, const int* win_lo,
+                                    const int* win_off, const float* entries, const int* row_order, int n_order_rows,
+                                    const int64_t* desc_host, int F, int rows, int nlon, int64_t batch, int D, int H, int W, int ES,
+                                    int NORD, double scale, void* out, float* lse, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

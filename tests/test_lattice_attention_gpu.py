@@ -111,3 +111,27 @@ def test_lattice_through_autograd_and_unsupported_layout():
     rows = tuple(tuple(int(x) for x in row) for row in odd.desc)
     assert not lattice_layout_supported(rows)
     assert lattice_layout_supported(lat.desc_rows)
+
+
+TC_CASES = [CASES[0], CASES[1], CASES[2], CASES[3], CASES[4], (8, 16, 2 * math.pi / 8, {1: 6, 2: 6}, 1, "hard", 2)]
+
+
+@pytest.mark.parametrize("case", TC_CASES)
+def test_tensor_core_forward_bf16(case):
+    """mma.sync Gram / value tiles against the oracle (2e-2 of the output's magnitude) and against the FMA
+    lattice kernel on the same bf16 inputs (they differ only by the bf16 rounding of the attention weights)."""
+    from gm_attention_b200.attention import lattice_attention_forward, tensor_core_layout_supported
+
+    batch = case[6]
+    c = make_case(*case[:5], dtype=np.float32, window=case[5])
+    rounded = [torch.from_numpy(x).bfloat16() for x in seeded((batch * c.n_nodes, c.width), 57, np.float32, 3)]
+    q, k, v = (x.float().numpy() for x in rounded)
+    want = O.attention_forward(q, k, v, c.transport, c.bias, c.inside, c.desc, c.row_ptr, c.source, c.heads, c.scale, batch)
+    _, lat = tables_for(c)
+    assert tensor_core_layout_supported(lat.desc_rows)
+    Q, K, V = (x.cuda() for x in rounded)
+    out_tc, lse_tc = lattice_attention_forward(Q, K, V, lat, tensor_cores=True)
+    out_fma, lse_fma = lattice_attention_forward(Q, K, V, lat, tensor_cores=False)
+    assert rel_err(out_tc.float().cpu().numpy(), want) < 2e-2
+    assert rel_err(out_tc.float().cpu().numpy(), out_fma.float().cpu().numpy()) < 2e-2
+    assert_close(lse_tc.cpu().numpy(), lse_fma.cpu().numpy(), 1e-4, 1e-4, "lse")
