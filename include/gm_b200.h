@@ -277,6 +277,13 @@ int gm_pairs_backward(const void* hidden, const void* weight, const void* bias, 
  * frequencies sharing one multiplicity <= 16; otherwise GM_ERR_UNSUPPORTED (use
  * gm_lattice_attention_forward).
  * ------------------------------------------------------------------------ */
+int gm_lattice_attention_backward_tc(const void* dout, const void* q, const void* k, const void* v, const void* out, const float* lse,
+                                     const int* win_cnt, const int* win_lo, const int* win_off, const float* entries,
+                                     const int* row_order, int n_order_rows, const int* t_win_cnt, const int* t_win_lo,
+                                     const int* t_win_off, const float* t_entries, const int* t_row_order, int t_n_order_rows,
+                                     const int64_t* desc_host, int F, int rows, int nlon, int64_t batch, int D, int H, int W, int ES,
+                                     int NORD, double scale, void* dq, void* dk, void* dv, float* delta, void* stream);
+
 int gm_lattice_attention_forward_tc(const void* q, const void* k, const void* v, const int* win_cnt, const int* win_lo,
                                     const int* win_off, const float* entries, const int* row_order, int n_order_rows,
                                     const int64_t* desc_host, int F, int rows, int nlon, int64_t batch, int D, int H, int W, int ES,

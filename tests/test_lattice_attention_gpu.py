@@ -135,3 +135,24 @@ def test_tensor_core_forward_bf16(case):
     assert rel_err(out_tc.float().cpu().numpy(), want) < 2e-2
     assert rel_err(out_tc.float().cpu().numpy(), out_fma.float().cpu().numpy()) < 2e-2
     assert_close(lse_tc.cpu().numpy(), lse_fma.cpu().numpy(), 1e-4, 1e-4, "lse")
+
+
+@pytest.mark.parametrize("case", TC_CASES)
+def test_tensor_core_backward_bf16(case):
+    """Both backward passes on tensor cores against the oracle (fp32 on the bf16-rounded inputs, 2e-2 of each
+    gradient's magnitude); reruns are bit-identical (no atomics)."""
+    from gm_attention_b200.attention import lattice_attention_backward, lattice_attention_forward
+
+    batch = case[6]
+    c = make_case(*case[:5], dtype=np.float32, window=case[5])
+    rounded = [torch.from_numpy(x).bfloat16() for x in seeded((batch * c.n_nodes, c.width), 58, np.float32, 4)]
+    q, k, v, g = (x.float().numpy() for x in rounded)
+    grads = O.attention_backward(g, q, k, v, c.transport, c.bias, c.inside, c.desc, c.row_ptr, c.source, c.heads, c.scale, batch)
+    _, lat = tables_for(c)
+    Q, K, V, G = (x.cuda() for x in rounded)
+    out, lse = lattice_attention_forward(Q, K, V, lat, tensor_cores=True)
+    got = lattice_attention_backward(G, Q, K, V, out, lse, lat, tensor_cores=True)
+    again = lattice_attention_backward(G, Q, K, V, out, lse, lat, tensor_cores=True)
+    for name, a, b, a2 in zip(("dq", "dk", "dv"), got, grads, again):
+        assert rel_err(a.float().cpu().numpy(), b) < 2e-2, name
+        assert torch.equal(a, a2), name
