@@ -44,6 +44,7 @@ constexpr int TC_THREADS = 128;
 constexpr int TC_TL = 64;  // targets per CTA
 constexpr float TC_LOG2E = 1.4426950408889634f, TC_LN2 = 0.6931471805599453f;
 constexpr int TC_MAX_CF = 3;
+constexpr int TC_MAX_WIN = 33;  // 2 W + 1 neighbour rows at most
 
 struct TcPlan {
   int a0, ac, n_cf;
@@ -257,17 +258,25 @@ __global__ void __launch_bounds__(TC_THREADS) lattice_tc_kernel(TcArgs a) {
   }
   float m_a = -1e30f, m_b = -1e30f, l_a = 0.f, l_b = 0.f;  // forward: running max (base-2 logits), partial row sums
 
-  // ---- the walk: stages = (neighbour row, chunk of its window), produced in order
+  // ---- the walk: stages = (neighbour row, chunk of its window), produced in order.  The owner row's window
+  // table (2W + 1 row pairs) is read once into shared memory so that stepping to the next stage costs no global load.
+  __shared__ int win_s[3 * TC_MAX_WIN];
+  for (int x = threadIdx.x; x < 2 * a.W + 1; x += TC_THREADS) {
+    const int widx = row * (2 * a.W + 1) + x;
+    win_s[3 * x] = a.win_cnt[widx];
+    win_s[3 * x + 1] = a.win_lo[widx];
+    win_s[3 * x + 2] = a.win_off[widx];
+  }
+  __syncthreads();
   auto first_chunk_of_row = [&](TcStage& s, int dj) -> bool {  // set s to chunk 0 of the first non-empty row pair >= dj
     for (; dj <= a.W; ++dj) {
       const int j = row + dj;
       if (j < 0 || j >= a.rows) continue;
-      const int widx = row * (2 * a.W + 1) + dj + a.W;
-      const int cnt = a.win_cnt[widx];
+      const int cnt = win_s[3 * (dj + a.W)];
       if (cnt == 0) continue;
-      s.dj = dj; s.p0 = 0; s.cnt = cnt; s.lo = a.win_lo[widx]; s.window = TC_TL + cnt - 1;
+      s.dj = dj; s.p0 = 0; s.cnt = cnt; s.lo = win_s[3 * (dj + a.W) + 1]; s.window = TC_TL + cnt - 1;
       s.nrow0 = (b * a.rows + j) * (int64_t)a.nlon;
-      s.ent = a.entries + (size_t)a.win_off[widx] * 8;
+      s.ent = a.entries + (size_t)win_s[3 * (dj + a.W) + 2] * 8;
       return true;
     }
     return false;
@@ -571,6 +580,7 @@ int fill_tc_args(TcArgs& a, const int64_t* desc_host, int F, int rows, int nlon,
   GM_REQUIRE(rows >= 1 && nlon >= 1 && batch >= 1 && D >= 1 && H >= 1 && H <= 65535 && batch <= 65535, GM_ERR_ARGUMENT,
              "gm_lattice_attention (tensor cores): bad sizes");
   GM_REQUIRE(W >= 0 && NORD >= 0, GM_ERR_ARGUMENT, "gm_lattice_attention (tensor cores): bad table sizes");
+  GM_REQUIRE(2 * W + 1 <= TC_MAX_WIN, GM_ERR_UNSUPPORTED, "gm_lattice_attention (tensor cores): neighbourhoods span more than %d lattice rows", TC_MAX_WIN);
   GM_REQUIRE(ES == 8 && 2 * NORD + 1 <= 8, GM_ERR_UNSUPPORTED, "gm_lattice_attention (tensor cores): entries must be 8 floats wide (orders <= 3)");
   GM_REQUIRE(desc_host, GM_ERR_ARGUMENT, "gm_lattice_attention (tensor cores): null descriptor");
   int status = make_tc_plan(desc_host, F, H, D, a.plan);
