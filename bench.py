@@ -328,17 +328,24 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
     e2e = None
     if not args.no_e2e:
         outs_host = [torch.empty(shape, dtype=dtype).pin_memory() for _ in range(4)]
-        def e2e_step():
-            dev = [h.to(device, non_blocking=True) for h in host]
-            qq, kk, vv, gg = dev
-            if halo is not None:
+        if halo is None:
+            # host-resident fields through the public host API: sample chunks pipelined over three streams
+            from gm_attention_b200.attention import HostPipeline
+            pipeline = HostPipeline(tables, batch, D, dtype, device, chunk=1)
+            host_flat = [x.view(batch * n_ext, D) for x in host]
+            outs_flat = [x.view(batch * n_ext, D) for x in outs_host]
+            def e2e_step():
+                pipeline.run(*host_flat, *outs_flat)
+        else:
+            def e2e_step():
+                dev = [x.to(device, non_blocking=True) for x in host]
+                qq, kk, vv, gg = dev
                 halo.fill_halos(kk, vv)
-            out, lse = attention_forward(flat(qq), flat(kk), flat(vv), tables)
-            dq, dk, dv = attention_backward(flat(gg), flat(qq), flat(kk), flat(vv), out, lse, tables)
-            if halo is not None:
+                out, lse = attention_forward(flat(qq), flat(kk), flat(vv), tables)
+                dq, dk, dv = attention_backward(flat(gg), flat(qq), flat(kk), flat(vv), out, lse, tables)
                 halo.reduce_halos(dk.view(shape), dv.view(shape))
-            for dst, src in zip(outs_host, (out, dq, dk, dv)):
-                dst.copy_(src.view(shape), non_blocking=True)
+                for dst, src in zip(outs_host, (out, dq, dk, dv)):
+                    dst.copy_(src.view(shape), non_blocking=True)
         for _ in range(2):
             e2e_step()
         barrier()

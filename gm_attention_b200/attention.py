@@ -329,3 +329,61 @@ def lattice_attention_backward(dout: Tensor, q: Tensor, k: Tensor, v: Tensor, ou
         else:
             _lib.call("gm_lattice_attention_backward", *common, _lib.dtype_code(q.dtype), *outputs)
     return dq, dk, dv
+
+
+# ----------------------------------------------------------------------------- host-resident fields
+
+class HostPipeline:
+    """Forward + backward of the fused layer for fields that live in (pinned) HOST memory.
+
+    Samples share the geometry and are otherwise independent, so the batch is cut
+    into chunks of samples and three CUDA streams run concurrently: chunk ``i + 1``
+    is copied host -> device while chunk ``i`` is computed and the results of chunk
+    ``i - 1`` are copied device -> host.  Device staging buffers are allocated once
+    (two chunks deep) and reused across calls."""
+
+    def __init__(self, tables: Any, batch: int, width: int, dtype: torch.dtype, device: torch.device, chunk: int = 1) -> None:
+        self.tables, self.batch, self.chunk, self.device = tables, batch, chunk, device
+        n = (tables.rows * tables.nlon) if isinstance(tables, LatticeTables) else tables.n_nodes
+        self.n_nodes = n
+        shape = (chunk * n, width)
+        self.inputs = [[torch.empty(shape, dtype=dtype, device=device) for _ in range(4)] for _ in range(2)]
+        self.streams = [torch.cuda.Stream(device) for _ in range(3)]  # h2d, compute, d2h
+        self.lattice = isinstance(tables, LatticeTables)
+
+    def run(self, q: Tensor, k: Tensor, v: Tensor, dout: Tensor, out: Tensor, dq: Tensor, dk: Tensor, dv: Tensor) -> None:
+        """All arguments are host tensors ``(batch * n_nodes, D)`` (pinned for overlap); the last four are written."""
+        fwd = lattice_attention_forward if self.lattice else attention_forward
+        bwd = lattice_attention_backward if self.lattice else attention_backward
+        h2d, comp, d2h = self.streams
+        rows = self.chunk * self.n_nodes
+        n_chunks = self.batch // self.chunk
+        main = torch.cuda.current_stream(self.device)
+        for s in self.streams:
+            s.wait_stream(main)
+        loaded = [torch.cuda.Event() for _ in range(n_chunks)]
+        computed = [torch.cuda.Event() for _ in range(n_chunks)]
+        stored = [torch.cuda.Event() for _ in range(n_chunks)]
+        results: list[tuple[Tensor, ...]] = [()] * n_chunks
+        for i in range(n_chunks):
+            sl = slice(i * rows, (i + 1) * rows)
+            slot = self.inputs[i % 2]
+            with torch.cuda.stream(h2d):
+                if i >= 2:
+                    h2d.wait_event(computed[i - 2])  # the slot's previous occupant has been consumed
+                for dst, src in zip(slot, (q, k, v, dout)):
+                    dst.copy_(src[sl], non_blocking=True)
+                loaded[i].record(h2d)
+            with torch.cuda.stream(comp):
+                comp.wait_event(loaded[i])
+                o, lse = fwd(slot[0], slot[1], slot[2], self.tables)
+                results[i] = (o, *bwd(slot[3], slot[0], slot[1], slot[2], o, lse, self.tables))
+                computed[i].record(comp)
+            with torch.cuda.stream(d2h):
+                d2h.wait_event(computed[i])
+                for dst, src in zip((out, dq, dk, dv), results[i]):
+                    dst[sl].copy_(src, non_blocking=True)
+                    src.record_stream(d2h)
+                stored[i].record(d2h)
+        for s in self.streams:
+            main.wait_stream(s)
