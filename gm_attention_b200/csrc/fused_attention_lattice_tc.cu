@@ -217,7 +217,7 @@ struct TcStage {
 };
 
 template <int KS0, int NCF, int KSC, int MODE>
-__global__ void __launch_bounds__(TC_THREADS) lattice_tc_kernel(TcArgs a) {
+__global__ void __launch_bounds__(TC_THREADS, MODE == TC_BWD_S ? 2 : 3) lattice_tc_kernel(TcArgs a) {
   constexpr int KQ = KS0 + NCF * KSC, DP = 16 * KQ, CH = DP / 8, PITCH = (CH % 2 == 0 ? CH + 1 : CH) * 8, NT = 2 * KQ;
   constexpr int NF = NCF > 0 ? NCF : 1;
   constexpr bool FWD = MODE == TC_FWD, PASS_S = MODE == TC_BWD_S;
@@ -241,6 +241,7 @@ __global__ void __launch_bounds__(TC_THREADS) lattice_tc_kernel(TcArgs a) {
   const int64_t node0 = (b * a.rows + row) * (int64_t)a.nlon;
   const int tl_a = 16 * warp + g, tl_b = tl_a + 8;  // the two owner rows this thread sees in every fragment
   const float cscale = a.scale * TC_LOG2E;
+  const bool orders_12 = NCF == 2 && P.n_cf == 2 && P.cf_order[0] == 1 && P.cf_order[1] == 2;
 
   unsigned f1[KQ][4], f2[FWD ? 1 : KQ][4];
   load_owner_fragments<KS0, NCF, KSC>(P, a.own1, node0, c0, a.nlon, a.D, h, tl_a, tl_b, c, f1);
@@ -285,43 +286,55 @@ __global__ void __launch_bounds__(TC_THREADS) lattice_tc_kernel(TcArgs a) {
     if (s.p0 + SC < s.window) { s.p0 += SC; return true; }
     return first_chunk_of_row(s, s.dj + 1);
   };
+  // staging slots: thread -> (row within a pass, 16-byte chunk); the chunk's flat column is fixed per thread
+  constexpr int ROWS_PER_PASS = TC_THREADS / CH;
+  const int st_row = threadIdx.x / CH, st_ch = threadIdx.x - st_row * CH;
+  const int st_g0 = flat_column<KS0, NCF, KSC>(P, h, 8 * st_ch), st_g7 = flat_column<KS0, NCF, KSC>(P, h, 8 * st_ch + 7);
+  const bool st_active = st_row < ROWS_PER_PASS;
+  const bool st_whole = st_g0 >= 0 && st_g7 == st_g0 + 7 && (a.D % 8 == 0) && (st_g0 % 8 == 0);  // one aligned 16-byte chunk of real columns
+  const bool st_pad = st_g0 < 0 && st_g7 < 0 && flat_column<KS0, NCF, KSC>(P, h, 8 * st_ch + 3) < 0;  // all padding (stays zero)
+  // zero both buffers once: rows beyond a window and padding columns are never written again and must be finite
+  for (size_t x = threadIdx.x; x < 2 * buf_bytes / 16; x += TC_THREADS) reinterpret_cast<uint4*>(smem_raw)[x] = make_uint4(0, 0, 0, 0);
+  __syncthreads();
   auto issue = [&](const TcStage& s, int buf) {  // asynchronous copies of one stage into buffer `buf`
     __nv_bfloat16* d1 = tile1(buf);
     __nv_bfloat16* d2 = tile2(buf);
-    for (int idx = threadIdx.x; idx < SC * CH; idx += TC_THREADS) {
-      const int pl = idx / CH, ch = idx - pl * CH;
-      const int64_t nb = (s.nrow0 + tc_wrap(c0 + s.lo + s.p0 + pl, a.nlon)) * a.D;
-      const int g0 = flat_column<KS0, NCF, KSC>(P, h, 8 * ch), g7 = flat_column<KS0, NCF, KSC>(P, h, 8 * ch + 7);
-      const bool inside = s.p0 + pl < s.window;
-      if (!inside || g0 < 0 || (g7 == g0 + 7 && ((nb + g0) % 8 == 0))) {  // whole 16-byte chunk, or zeros (padding / beyond the window)
-        const int bytes = (inside && g0 >= 0) ? 16 : 0;
-        const int64_t at = bytes ? nb + g0 : 0;
-        cp_async16(d1 + pl * PITCH + 8 * ch, a.nb1 + at, bytes);
-        cp_async16(d2 + pl * PITCH + 8 * ch, a.nb2 + at, bytes);
-      } else {  // a chunk that straddles padding or is misaligned: element by element (visible after the barrier)
-        unsigned short u1[8], u2[8];
+    const int n_rows = min(SC, s.window - s.p0);
+    if (st_active && !st_pad) {
+      int lon = tc_wrap(c0 + s.lo + s.p0 + st_row, a.nlon);
+      const int step = ROWS_PER_PASS % a.nlon;
+      for (int pl = st_row; pl < n_rows; pl += ROWS_PER_PASS) {
+        const int64_t nb = (s.nrow0 + lon) * a.D;
+        if (st_whole) {
+          cp_async16(d1 + pl * PITCH + 8 * st_ch, a.nb1 + nb + st_g0, 16);
+          cp_async16(d2 + pl * PITCH + 8 * st_ch, a.nb2 + nb + st_g0, 16);
+        } else {  // a chunk that straddles padding or is misaligned: element by element (visible after the barrier)
+          unsigned short u1[8], u2[8];
 #pragma unroll
-        for (int x = 0; x < 8; ++x) {
-          const int gx = flat_column<KS0, NCF, KSC>(P, h, 8 * ch + x);
-          u1[x] = gx >= 0 ? __bfloat16_as_ushort(a.nb1[nb + gx]) : (unsigned short)0;
-          u2[x] = gx >= 0 ? __bfloat16_as_ushort(a.nb2[nb + gx]) : (unsigned short)0;
+          for (int x = 0; x < 8; ++x) {
+            const int gx = flat_column<KS0, NCF, KSC>(P, h, 8 * st_ch + x);
+            u1[x] = gx >= 0 ? __bfloat16_as_ushort(a.nb1[nb + gx]) : (unsigned short)0;
+            u2[x] = gx >= 0 ? __bfloat16_as_ushort(a.nb2[nb + gx]) : (unsigned short)0;
+          }
+          *reinterpret_cast<uint4*>(d1 + pl * PITCH + 8 * st_ch) =
+              make_uint4(u1[0] | (u1[1] << 16), u1[2] | (u1[3] << 16), u1[4] | (u1[5] << 16), u1[6] | (u1[7] << 16));
+          *reinterpret_cast<uint4*>(d2 + pl * PITCH + 8 * st_ch) =
+              make_uint4(u2[0] | (u2[1] << 16), u2[2] | (u2[3] << 16), u2[4] | (u2[5] << 16), u2[6] | (u2[7] << 16));
         }
-        *reinterpret_cast<uint4*>(d1 + pl * PITCH + 8 * ch) =
-            make_uint4(u1[0] | (u1[1] << 16), u1[2] | (u1[3] << 16), u1[4] | (u1[5] << 16), u1[6] | (u1[7] << 16));
-        *reinterpret_cast<uint4*>(d2 + pl * PITCH + 8 * ch) =
-            make_uint4(u2[0] | (u2[1] << 16), u2[2] | (u2[3] << 16), u2[4] | (u2[5] << 16), u2[6] | (u2[7] << 16));
+        lon += step;
+        if (lon >= a.nlon) lon -= a.nlon;
       }
     }
     // table entries of the offsets x = p - tl the chunk can meet (clamped: validity is decided from x itself)
     float* de = entry(buf);
-    for (int idx = threadIdx.x; idx < 2 * (SC + TC_TL); idx += TC_THREADS) {
+    for (int idx = threadIdx.x; idx < 2 * (n_rows + TC_TL - 1); idx += TC_THREADS) {
       const int xi = idx >> 1, part = idx & 1;
       const int x = min(max(xi + s.p0 - (TC_TL - 1), 0), s.cnt - 1);
       cp_async16(de + 8 * xi + 4 * part, s.ent + (size_t)x * 8 + 4 * part, 16);
     }
     if constexpr (PASS_S) {
       float* ds = stats(buf);
-      for (int idx = threadIdx.x; idx < 2 * SC; idx += TC_THREADS) {
+      for (int idx = threadIdx.x; idx < 2 * n_rows; idx += TC_THREADS) {
         const int pl = idx >> 1, which = idx & 1;
         const int64_t nn = (s.nrow0 + tc_wrap(c0 + s.lo + s.p0 + pl, a.nlon)) * a.H + h;
         cp_async4(ds + 2 * pl + which, (which ? a.delta : a.lse) + nn, 4);
@@ -360,6 +373,18 @@ __global__ void __launch_bounds__(TC_THREADS) lattice_tc_kernel(TcArgs a) {
       float mx_a = m_a, mx_b = m_b;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
+        if (half == 1 && p + 8 >= p_hi) {  // the upper 8 positions are beyond every owner's window (warp-uniform): no work
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            lg[1][x] = -INFINITY;
+#pragma unroll
+            for (int f = 0; f < NCF; ++f) tr[f][1][x] = ti[f][1][x] = 0.f;
+          }
+          xa[2] = xa[3] = ya[2] = ya[3] = 0u;
+#pragma unroll
+          for (int f = 0; f < NCF; ++f) xar[f][2] = xar[f][3] = xai[f][2] = xai[f][3] = yar[f][2] = yar[f][3] = yai[f][2] = yai[f][3] = 0u;
+          continue;
+        }
         float s0[4], sr[NF][4], si[NF][4], h0[4], hr[NF][4], hi[NF][4];
         gram_half<KS0, NCF, KSC, !PASS_S>(f1, t1, PITCH, pl + 8 * half, lane, s0, sr, si);
         if constexpr (!FWD) gram_half<KS0, NCF, KSC, !PASS_S>(f2, t2, PITCH, pl + 8 * half, lane, h0, hr, hi);
@@ -371,13 +396,23 @@ __global__ void __launch_bounds__(TC_THREADS) lattice_tc_kernel(TcArgs a) {
           const int xi = pos - tl + (TC_TL - 1);                    // staged entry of the offset x = p - tl
           const bool valid = (unsigned)(p0 + pos - tl) < (unsigned)cnt;
           float sum = s0[x], dal = FWD ? 0.f : h0[x];
+          float tau[2 * NF];
+          if (NCF == 2 && orders_12) {  // the usual case, frequencies 1 and 2: their phases are the entry's first 16 bytes
+            const float4 t = *reinterpret_cast<const float4*>(e_s + 8 * xi);
+            tau[0] = t.x; tau[1] = t.y; tau[2] = t.z; tau[3] = t.w;
+          } else {
+#pragma unroll
+            for (int f = 0; f < NCF; ++f) {
+              const float2 t = *reinterpret_cast<const float2*>(e_s + 8 * xi + 2 * (P.cf_order[f < P.n_cf ? f : 0] - 1));
+              tau[2 * f] = t.x; tau[2 * f + 1] = t.y;
+            }
+          }
 #pragma unroll
           for (int f = 0; f < NCF; ++f) {
-            const float2 t = *reinterpret_cast<const float2*>(e_s + 8 * xi + 2 * (P.cf_order[f < P.n_cf ? f : 0] - 1));
-            tr[f][half][x] = t.x;
-            ti[f][half][x] = t.y;
-            sum += t.x * sr[f][x] - t.y * si[f][x];
-            if constexpr (!FWD) dal += t.x * hr[f][x] - t.y * hi[f][x];
+            tr[f][half][x] = tau[2 * f];
+            ti[f][half][x] = tau[2 * f + 1];
+            sum += tau[2 * f] * sr[f][x] - tau[2 * f + 1] * si[f][x];
+            if constexpr (!FWD) dal += tau[2 * f] * hr[f][x] - tau[2 * f + 1] * hi[f][x];
           }
           const float logit = valid ? TC_LOG2E * e_s[8 * xi + 2 * a.NORD] + cscale * sum : -INFINITY;  // -inf: outside the window
           if constexpr (FWD) {
@@ -419,15 +454,17 @@ __global__ void __launch_bounds__(TC_THREADS) lattice_tc_kernel(TcArgs a) {
         mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
         mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
         mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
-        const float corr_a = exp2f(m_a - mx_a), corr_b = exp2f(m_b - mx_b);
-        m_a = mx_a;
-        m_b = mx_b;
-        l_a *= corr_a;
-        l_b *= corr_b;
+        if (__any_sync(0xffffffffu, mx_a != m_a || mx_b != m_b)) {  // some row's maximum moved: rescale what was summed so far
+          const float corr_a = exp2f(m_a - mx_a), corr_b = exp2f(m_b - mx_b);
+          m_a = mx_a;
+          m_b = mx_b;
+          l_a *= corr_a;
+          l_b *= corr_b;
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          acc1[nt][0] *= corr_a; acc1[nt][1] *= corr_a;
-          acc1[nt][2] *= corr_b; acc1[nt][3] *= corr_b;
+          for (int nt = 0; nt < NT; ++nt) {
+            acc1[nt][0] *= corr_a; acc1[nt][1] *= corr_a;
+            acc1[nt][2] *= corr_b; acc1[nt][3] *= corr_b;
+          }
         }
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
