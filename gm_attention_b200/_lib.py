@@ -35,6 +35,7 @@ SIGNATURES: dict[str, list[Any]] = {
     "gm_lattice_attention_forward": [_P] * 8 + [_I, _P, _I, _I, _I, _L, _I, _I, _I, _I, _I, _D, _I, _P, _P, _P],
     "gm_lattice_attention_forward_tc": [_P] * 8 + [_I, _P, _I, _I, _I, _L, _I, _I, _I, _I, _I, _D, _P, _P, _P],
     "gm_lattice_attention_backward_tc": [_P] * 11 + [_I] + [_P] * 5 + [_I, _P, _I, _I, _I, _L, _I, _I, _I, _I, _I, _D, _P, _P, _P, _P, _P],
+    "gm_lattice_attention_backward_tc_passes": [_P] * 11 + [_I] + [_P] * 5 + [_I, _P, _I, _I, _I, _L, _I, _I, _I, _I, _I, _D, _P, _P, _P, _P, _I, _P],
     "gm_lattice_attention_backward": [_P] * 11 + [_I] + [_P] * 5 + [_I, _P, _I, _I, _I, _L, _I, _I, _I, _I, _I, _D, _I, _P, _P, _P, _P, _P],
     "gm_factored_forward": [_P] * 11 + [_L, _L, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "gm_factored_aggregate": [_P, _P, _P, _L, _L, _I, _I, _P, _P],

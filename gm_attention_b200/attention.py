@@ -307,15 +307,20 @@ def lattice_attention_forward(q: Tensor, k: Tensor, v: Tensor, t: LatticeTables,
 
 
 def lattice_attention_backward(dout: Tensor, q: Tensor, k: Tensor, v: Tensor, out: Tensor, lse: Tensor, t: LatticeTables,
-                               tensor_cores: bool | None = None) -> tuple[Tensor, Tensor, Tensor]:
+                               tensor_cores: bool | None = None, passes: int = 7, workspace: tuple | None = None) -> tuple[Tensor, Tensor, Tensor]:
+    """``(dq, dk, dv)``.  ``passes`` (tensor-core path only) selects Delta (1), the target-major pass (2) and the
+    source-major pass (4) for timing them separately; ``workspace = (dq, dk, dv, delta)`` reuses buffers of an earlier call."""
     device, batch = _check_lattice(q, k, v, t)
     if tensor_cores is None:
         tensor_cores = TENSOR_CORES != "0" and q.dtype == torch.bfloat16 and tensor_core_layout_supported(t.desc_rows)
     dout = dout.contiguous()
     alloc = torch.empty_like if t.row_order.numel() == t.rows else torch.zeros_like
     alloc_t = torch.empty_like if t.t_row_order.numel() == t.rows else torch.zeros_like
-    dq, dk, dv = alloc(q), alloc_t(q), alloc_t(q)
-    delta = torch.empty((q.shape[0], t.heads), dtype=torch.float32, device=device)
+    if workspace is not None:
+        dq, dk, dv, delta = workspace
+    else:
+        dq, dk, dv = alloc(q), alloc_t(q), alloc_t(q)
+        delta = torch.empty((q.shape[0], t.heads), dtype=torch.float32, device=device)
     desc = t.host_descriptor()
     common = (_lib.ptr(dout), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(lse), _lib.ptr(t.win_cnt), _lib.ptr(t.win_lo),
               _lib.ptr(t.win_off), _lib.ptr(t.entries), _lib.ptr(t.row_order), t.row_order.numel(), _lib.ptr(t.t_win_cnt),
@@ -325,7 +330,7 @@ def lattice_attention_backward(dout: Tensor, q: Tensor, k: Tensor, v: Tensor, ou
     outputs = (_lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(delta), _lib.stream(device))
     with torch.cuda.device(device):
         if tensor_cores:
-            _lib.call("gm_lattice_attention_backward_tc", *common, *outputs)
+            _lib.call("gm_lattice_attention_backward_tc_passes", *common, *outputs[:4], int(passes), outputs[4])
         else:
             _lib.call("gm_lattice_attention_backward", *common, _lib.dtype_code(q.dtype), *outputs)
     return dq, dk, dv

@@ -558,6 +558,35 @@ __global__ void tc_delta_kernel(const __nv_bfloat16* __restrict__ dout, const __
   if (lane == 0) delta[node * H + h] = acc;
 }
 
+// Same, one warp per node with 16-byte loads: every 8-column chunk of the row belongs to one head (host-checked).
+__global__ void tc_delta_vec_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ out, float* __restrict__ delta,
+                                    int64_t n_nodes, int D, int H, TcPlan P) {
+  const int lane = threadIdx.x & 31;
+  const int64_t node = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (node >= n_nodes) return;
+  float part[2] = {0.f, 0.f};
+  int head[2] = {-1, -1};
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int col = 8 * (lane + 32 * r);
+    if (col >= D) continue;
+    if (P.a0 > 0 && col >= P.real_off && col < P.real_off + H * P.a0) head[r] = (col - P.real_off) / P.a0;
+    for (int f = 0; f < P.n_cf; ++f)
+      if (col >= P.cf_off[f] && col < P.cf_off[f] + 2 * H * P.ac) head[r] = (col - P.cf_off[f]) / (2 * P.ac);
+    if (head[r] < 0) continue;
+    const uint4 a = __ldg(reinterpret_cast<const uint4*>(dout + node * D + col));
+    const uint4 b = __ldg(reinterpret_cast<const uint4*>(out + node * D + col));
+    const unsigned wa[4] = {a.x, a.y, a.z, a.w}, wb[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int x = 0; x < 4; ++x)
+      part[r] += __uint_as_float(wa[x] << 16) * __uint_as_float(wb[x] << 16) + __uint_as_float(wa[x] & 0xffff0000u) * __uint_as_float(wb[x] & 0xffff0000u);
+  }
+  for (int h = 0; h < H; ++h) {
+    const float v = warp_sum((head[0] == h ? part[0] : 0.f) + (head[1] == h ? part[1] : 0.f));
+    if (lane == 0) delta[node * H + h] = v;
+  }
+}
+
 int make_tc_plan(const int64_t* desc_host, int F, int H, int D, TcPlan& P) {
   P = TcPlan{};
   GM_REQUIRE(F >= 1 && F <= TC_MAX_CF + 1, GM_ERR_UNSUPPORTED, "gm_lattice_attention (tensor cores): at most %d frequencies", TC_MAX_CF + 1);
@@ -649,6 +678,15 @@ extern "C" int gm_lattice_attention_forward_tc(const void* q, const void* k, con
   return dispatch_tc<TC_FWD>(a, n_order_rows, batch, (cudaStream_t)stream);
 }
 
+extern "C" int gm_lattice_attention_backward_tc_passes(const void* dout, const void* q, const void* k, const void* v, const void* out,
+                                                       const float* lse, const int* win_cnt, const int* win_lo, const int* win_off,
+                                                       const float* entries, const int* row_order, int n_order_rows,
+                                                       const int* t_win_cnt, const int* t_win_lo, const int* t_win_off,
+                                                       const float* t_entries, const int* t_row_order, int t_n_order_rows,
+                                                       const int64_t* desc_host, int F, int rows, int nlon, int64_t batch, int D, int H,
+                                                       int W, int ES, int NORD, double scale, void* dq, void* dk, void* dv, float* delta,
+                                                       int passes, void* stream);
+
 extern "C" int gm_lattice_attention_backward_tc(const void* dout, const void* q, const void* k, const void* v, const void* out,
                                                 const float* lse, const int* win_cnt, const int* win_lo, const int* win_off,
                                                 const float* entries, const int* row_order, int n_order_rows, const int* t_win_cnt,
@@ -656,6 +694,21 @@ extern "C" int gm_lattice_attention_backward_tc(const void* dout, const void* q,
                                                 const int* t_row_order, int t_n_order_rows, const int64_t* desc_host, int F, int rows,
                                                 int nlon, int64_t batch, int D, int H, int W, int ES, int NORD, double scale, void* dq,
                                                 void* dk, void* dv, float* delta, void* stream) {
+  return gm_lattice_attention_backward_tc_passes(dout, q, k, v, out, lse, win_cnt, win_lo, win_off, entries, row_order, n_order_rows,
+                                                 t_win_cnt, t_win_lo, t_win_off, t_entries, t_row_order, t_n_order_rows, desc_host, F, rows,
+                                                 nlon, batch, D, H, W, ES, NORD, scale, dq, dk, dv, delta, 7, stream);
+}
+
+// passes: bit 0 = Delta, bit 1 = the target-major pass (dq), bit 2 = the source-major pass (dk, dv).  Running a
+// subset is for timing the passes separately; pass T and pass S read the Delta an earlier call left in `delta`.
+extern "C" int gm_lattice_attention_backward_tc_passes(const void* dout, const void* q, const void* k, const void* v, const void* out,
+                                                       const float* lse, const int* win_cnt, const int* win_lo, const int* win_off,
+                                                       const float* entries, const int* row_order, int n_order_rows,
+                                                       const int* t_win_cnt, const int* t_win_lo, const int* t_win_off,
+                                                       const float* t_entries, const int* t_row_order, int t_n_order_rows,
+                                                       const int64_t* desc_host, int F, int rows, int nlon, int64_t batch, int D, int H,
+                                                       int W, int ES, int NORD, double scale, void* dq, void* dk, void* dv, float* delta,
+                                                       int passes, void* stream) {
   using B = __nv_bfloat16;
   cudaStream_t cs = (cudaStream_t)stream;
   TcArgs a{};
@@ -665,17 +718,24 @@ extern "C" int gm_lattice_attention_backward_tc(const void* dout, const void* q,
                  t_win_off && t_entries && t_row_order && dq && dk && dv && delta,
              GM_ERR_ARGUMENT, "gm_lattice_attention_backward_tc: null pointer");
   const int64_t n_nodes = batch * rows * (int64_t)nlon;
-  tc_delta_kernel<<<(unsigned)((n_nodes * H + 7) / 8), 256, 0, cs>>>((const B*)dout, (const B*)out, delta, n_nodes, D, H, a.plan);
+  bool chunked = D % 8 == 0 && D <= 512 && a.plan.a0 % 8 == 0 && (2 * a.plan.ac) % 8 == 0 && a.plan.real_off % 8 == 0 &&
+                 reinterpret_cast<uintptr_t>(dout) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
+  for (int f = 0; f < a.plan.n_cf; ++f) chunked = chunked && a.plan.cf_off[f] % 8 == 0;
+  if (!(passes & 1)) {
+  } else if (chunked)
+    tc_delta_vec_kernel<<<(unsigned)((n_nodes + 7) / 8), 256, 0, cs>>>((const B*)dout, (const B*)out, delta, n_nodes, D, H, a.plan);
+  else
+    tc_delta_kernel<<<(unsigned)((n_nodes * H + 7) / 8), 256, 0, cs>>>((const B*)dout, (const B*)out, delta, n_nodes, D, H, a.plan);
   status = launch_status("gm_lattice_attention_backward_tc (delta)");
   if (status != GM_OK) return status;
   a.lse = lse; a.delta = delta;
-  if (n_order_rows > 0) {
+  if (n_order_rows > 0 && (passes & 2)) {
     a.own1 = (const B*)q; a.own2 = (const B*)dout; a.nb1 = (const B*)k; a.nb2 = (const B*)v; a.res1 = (B*)dq; a.res2 = nullptr;
     a.win_cnt = win_cnt; a.win_lo = win_lo; a.win_off = win_off; a.entries = entries; a.row_order = row_order;
     status = dispatch_tc<TC_BWD_T>(a, n_order_rows, batch, cs);
     if (status != GM_OK) return status;
   }
-  if (t_n_order_rows > 0) {
+  if (t_n_order_rows > 0 && (passes & 4)) {
     a.own1 = (const B*)k; a.own2 = (const B*)v; a.nb1 = (const B*)q; a.nb2 = (const B*)dout; a.res1 = (B*)dk; a.res2 = (B*)dv;
     a.win_cnt = t_win_cnt; a.win_lo = t_win_lo; a.win_off = t_win_off; a.entries = t_entries; a.row_order = t_row_order;
     status = dispatch_tc<TC_BWD_S>(a, t_n_order_rows, batch, cs);

@@ -284,6 +284,16 @@ int gm_lattice_attention_backward_tc(const void* dout, const void* q, const void
                                      const int64_t* desc_host, int F, int rows, int nlon, int64_t batch, int D, int H, int W, int ES,
                                      int NORD, double scale, void* dq, void* dk, void* dv, float* delta, void* stream);
 
+/* The same with a pass mask (bit 0: Delta = <dO, O>; bit 1: target-major pass -> dq; bit 2: source-major pass ->
+ * dk, dv), for timing the passes one by one; passes 2 and 4 read the Delta an earlier call left in `delta`. */
+int gm_lattice_attention_backward_tc_passes(const void* dout, const void* q, const void* k, const void* v, const void* out,
+                                            const float* lse, const int* win_cnt, const int* win_lo, const int* win_off,
+                                            const float* entries, const int* row_order, int n_order_rows, const int* t_win_cnt,
+                                            const int* t_win_lo, const int* t_win_off, const float* t_entries, const int* t_row_order,
+                                            int t_n_order_rows, const int64_t* desc_host, int F, int rows, int nlon, int64_t batch,
+                                            int D, int H, int W, int ES, int NORD, double scale, void* dq, void* dk, void* dv,
+                                            float* delta, int passes, void* stream);
+
 int gm_lattice_attention_forward_tc(const void* q, const void* k, const void* v, const int* win_cnt, const int* win_lo,
                                     const int* win_off, const float* entries, const int* row_order, int n_order_rows,
                                     const int64_t* desc_host, int F, int rows, int nlon, int64_t batch, int D, int H, int W, int ES,
