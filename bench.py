@@ -208,9 +208,9 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
     from gm_attention_b200.attention import (AttentionTables, attention_backward, attention_forward, build_lattice_tables,
                                              lattice_attention_backward, lattice_attention_forward)
     from gm_attention_b200.fields import FieldType
-    from gm_attention_b200.geometry import SphericalLattice, compute_edge_geometry, midpoint_lattice
+    from gm_attention_b200.geometry import midpoint_lattice
     from gm_attention_b200.nn import fused_attention as fa
-    from gm_attention_b200.parallel import BandPlan, HaloExchanger
+    from gm_attention_b200.parallel import BandPlan, HaloExchanger, band_geometry, row_degrees
 
     _lib.lib()
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -231,31 +231,14 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
     # ---- resident geometry (built once, on the device; not timed)
     lattice = midpoint_lattice(nlat, nlon, device)
     w = lattice.band(radius)
-    lo_c, hi_c = lattice.candidate_ranges(radius)
-    row_edges = None
     if world > 1:
-        # per-row degrees from a count-only pass over column 0 of every row
-        deg = torch.empty(nlat * nlon, dtype=torch.int64, device=device)
-        _lib.call("gm_geometry_count", _lib.ptr(lattice.nodes), nlat * nlon, _lib.ptr(lo_c), _lib.ptr(hi_c), radius, _lib.ptr(deg),
-                  _lib.stream(device))
-        row_degree = deg.reshape(nlat, nlon)[:, 0].tolist()
-        plan = BandPlan.balanced(nlat, nlon, w, row_degree, world)
+        plan = BandPlan.balanced(nlat, nlon, w, row_degrees(lattice, radius), world)
     else:
         plan = BandPlan(nlat, nlon, w, (0, nlat))
     lo, hi = plan.owned(rank)
     elo, ehi = plan.extended(rank)
     rows_ext = ehi - elo
-    # the rank's node set: its extended rows; halo targets examine no candidates (degree 0)
-    sel = slice(elo * nlon, ehi * nlon)
-    sub = SphericalLattice(rows_ext, nlon, lattice.theta[elo:ehi], lattice.nodes[sel].contiguous(),
-                           lattice.quadrature_weights[sel].contiguous(), lattice.frames[sel].contiguous())
-    c_lo, c_hi = (lo_c[sel] - elo * nlon).clone(), (hi_c[sel] - elo * nlon).clamp_max(rows_ext * nlon).clone()
-    c_lo.clamp_min_(0)
-    owned_mask = torch.zeros(rows_ext, dtype=torch.bool, device=device)
-    owned_mask[lo - elo: hi - elo] = True
-    owned_nodes = owned_mask.repeat_interleave(nlon)
-    c_hi = torch.where(owned_nodes, c_hi, c_lo)
-    edges = compute_edge_geometry(sub, sub.frames, radius, max_frequency=2, dtype=torch.float32, candidates=(c_lo, c_hi))
+    edges = band_geometry(lattice, plan, rank, radius, max_frequency=2, dtype=torch.float32)
     geo = fa.geometry(edges, radius, "hard", torch.float32)
     owner = type("Layer", (), {})()
     p = fa._plan(owner, attn, full, heads)

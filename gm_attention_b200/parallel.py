@@ -160,3 +160,38 @@ class HaloExchanger:
         for g in grads:
             g[:, : self.lo - self.elo].zero_()
             g[:, self.hi - self.elo:].zero_()
+
+
+def band_geometry(lattice, plan: BandPlan, rank: int, radius: float, *, max_frequency: int = 4, dtype: torch.dtype = torch.float32):
+    """The neighbourhood geometry one rank keeps resident: nodes = its extended rows (band + halo),
+    edges = those whose TARGET lies in the band (halo rows examine no candidates and get degree 0),
+    node indices relative to the extended rows.  Built on the rank's own device."""
+    from gm_attention_b200.geometry import SphericalLattice, compute_edge_geometry
+
+    nlon = lattice.nlon
+    lo, hi = plan.owned(rank)
+    elo, ehi = plan.extended(rank)
+    rows_ext = ehi - elo
+    sel = slice(elo * nlon, ehi * nlon)
+    sub = SphericalLattice(rows_ext, nlon, lattice.theta[elo:ehi], lattice.nodes[sel].contiguous(),
+                           lattice.quadrature_weights[sel].contiguous(), lattice.frames[sel].contiguous())
+    c_lo, c_hi = lattice.candidate_ranges(radius)
+    c_lo = (c_lo[sel] - elo * nlon).clamp_min(0)
+    c_hi = (c_hi[sel] - elo * nlon).clamp_max(rows_ext * nlon)
+    owned = torch.zeros(rows_ext, dtype=torch.bool, device=lattice.nodes.device)
+    owned[lo - elo: hi - elo] = True
+    c_hi = torch.where(owned.repeat_interleave(nlon), c_hi, c_lo)
+    return compute_edge_geometry(sub, sub.frames, radius, max_frequency=max_frequency, dtype=dtype, candidates=(c_lo.contiguous(), c_hi.contiguous()))
+
+
+def row_degrees(lattice, radius: float) -> list[int]:
+    """Neighbours per node of every lattice row (independent of longitude), from a count-only pass."""
+    from gm_attention_b200 import _lib
+
+    device = lattice.nodes.device
+    n = lattice.n_nodes
+    lo, hi = lattice.candidate_ranges(radius)
+    degree = torch.empty(n, dtype=torch.int64, device=device)
+    with torch.cuda.device(device):
+        _lib.call("gm_geometry_count", _lib.ptr(lattice.nodes), n, _lib.ptr(lo), _lib.ptr(hi), float(radius), _lib.ptr(degree), _lib.stream(device))
+    return degree.reshape(lattice.nlat, lattice.nlon)[:, 0].tolist()

@@ -1,0 +1,89 @@
+"""Latitude-band sharding on real GPUs (NCCL, one process per GPU): the sharded fused layer with halo exchange
+against the unsharded layer on one GPU.  Needs at least two GPUs; skipped otherwise."""
+
+from __future__ import annotations
+
+import math
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank(rank: int, world: int, port: int, out_dir: str) -> None:
+    import torch.distributed as dist
+
+    from gm_attention_b200.attention import AttentionTables, build_lattice_tables, lattice_attention_backward, lattice_attention_forward
+    from gm_attention_b200.fields import FieldType
+    from gm_attention_b200.geometry import compute_edge_geometry, midpoint_lattice
+    from gm_attention_b200.nn import fused_attention as fa
+    from gm_attention_b200.parallel import BandPlan, HaloExchanger, band_geometry, row_degrees
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    try:
+        nlat, nlon, batch, heads = 24, 48, 2, 4
+        radius = 3 * math.pi / nlat
+        attn = FieldType({0: 16, 1: 16, 2: 16})
+        full = attn.scaled(heads)
+        D = full.dimension
+        owner = type("Layer", (), {})()
+        rows = fa._plan(owner, attn, full, heads).rows
+        scale = 1.0 / math.sqrt(attn.dimension)
+        lattice = midpoint_lattice(nlat, nlon, device)
+        plan = BandPlan.balanced(nlat, nlon, lattice.band(radius), row_degrees(lattice, radius), world)
+        lo, hi = plan.owned(rank)
+        elo, ehi = plan.extended(rank)
+
+        def tables_of(edges, n_rows):
+            g = fa.geometry(edges, radius, "hard", torch.float32)
+            general = AttentionTables(g.transport, g.bias, g.inside, g.row_ptr, g.source, rows, heads, scale)
+            return build_lattice_tables(general, n_rows, nlon, rows, heads, scale)
+
+        local = tables_of(band_geometry(lattice, plan, rank, radius, max_frequency=2), ehi - elo)
+        gen = torch.Generator().manual_seed(7)
+        fields = [torch.randn(batch, nlat, nlon, D, generator=gen).to(device) for _ in range(4)]  # same on every rank
+        q, k, v, g = (f[:, elo:ehi].contiguous() for f in fields)
+        k[:, : lo - elo] = float("nan"); k[:, hi - elo:] = float("nan")  # halos must come from the owners
+        v[:, : lo - elo] = float("nan"); v[:, hi - elo:] = float("nan")
+        halo = HaloExchanger(plan, rank)
+        halo.fill_halos(k, v)
+        flat = lambda t: t.reshape(-1, D)
+        out, lse = lattice_attention_forward(flat(q), flat(k), flat(v), local, tensor_cores=False)
+        dq, dk, dv = lattice_attention_backward(flat(g), flat(q), flat(k), flat(v), out, lse, local, tensor_cores=False)
+        shape = (batch, ehi - elo, nlon, D)
+        dk, dv = dk.view(shape), dv.view(shape)
+        halo.reduce_halos(dk, dv)
+        # unsharded on this GPU
+        whole = tables_of(compute_edge_geometry(lattice, lattice.frames, radius, max_frequency=2, dtype=torch.float32), nlat)
+        Q, K, V, G = (flat(f.contiguous()) for f in fields)
+        want_out, want_lse = lattice_attention_forward(Q, K, V, whole, tensor_cores=False)
+        want = [want_out, *lattice_attention_backward(G, Q, K, V, want_out, want_lse, whole, tensor_cores=False)]
+        own = slice(lo - elo, hi - elo)
+        for name, got, ref in zip(("out", "dq", "dk", "dv"), (out.view(shape), dq.view(shape), dk, dv), want):
+            ref = ref.view(batch, nlat, nlon, D)[:, lo:hi]
+            err = float((got[:, own] - ref).abs().max() / ref.abs().max().clamp_min(1.0))
+            assert err < 1e-5, f"rank {rank} {name}: {err}"
+        open(os.path.join(out_dir, f"ok{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sharded_layer_on_gpus(tmp_path):
+    import torch.multiprocessing as mp
+
+    world = min(torch.cuda.device_count(), 4)
+    mp.spawn(_rank, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert sorted(os.listdir(tmp_path)) == [f"ok{r}" for r in range(world)]
