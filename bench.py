@@ -50,7 +50,10 @@ def parse() -> argparse.Namespace:
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--dtype", choices=["bf16", "f32"], default="bf16")
     p.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    p.add_argument("--workload", choices=["headline", "mid", "small"], default="headline")
+    p.add_argument("--workload", choices=["headline", "mid", "small", "ops"], default="headline",
+                   help="headline (default): the BASELINE workload; mid / small: profiling and smoke sizes; "
+                        "ops: times every op-level entry point (scores+softmax, depthwise conv, factored kernel, pair term) "
+                        "against its own interface bytes and prints one JSON object")
     p.add_argument("--kernel", choices=["lattice", "csr"], default="lattice",
                    help="lattice: compact-table fast path (default); csr: general per-edge-table kernels")
     p.add_argument("--no-cpu-baseline", action="store_true")
@@ -403,8 +406,117 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
         dist.destroy_process_group()
 
 
+def run_ops(args: argparse.Namespace) -> None:
+    """Per-op timings of the drop-in entry points on a 128 x 256 lattice (radius 3 pi / 128, ~3.0 M edges), fp32:
+    achieved GB/s of each op's own interface bytes (inputs + outputs, each byte once), CUDA events, 3 warm-up + 10 timed."""
+    import numpy as np
+    import torch
+
+    from gm_attention_b200.fields import FieldType
+    from gm_attention_b200.geometry import compute_edge_geometry, midpoint_lattice
+    from gm_attention_b200.nn import fused_attention as fa
+    from gm_attention_b200.nn import fused_factored as ff
+    from gm_attention_b200.nn import fused_pairs as fp
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    nlat, nlon = 128, 256
+    radius = 3 * math.pi / nlat
+    lattice = midpoint_lattice(nlat, nlon, dev)
+    edges = compute_edge_geometry(lattice, lattice.frames, radius, max_frequency=4, dtype=torch.float32)
+    geo = fa.geometry(edges, radius, "hard", torch.float32)
+    n, e = nlat * nlon, edges.n_edges
+    gen = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *shape: torch.randn(*shape, generator=gen, device=dev, dtype=torch.float32)
+    peak = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())["hbm_gbs"] if (ROOT / "MEASURED_PEAKS.json").exists() else 6650.0
+    results = {}
+
+    def timed(name: str, fn, nbytes: int) -> None:
+        for _ in range(3):
+            fn()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(10)]
+        for a, b in ev:
+            a.record(); fn(); b.record()
+        torch.cuda.synchronize()
+        ms = statistics.mean(a.elapsed_time(b) for a, b in ev)
+        results[name] = {"ms": ms, "interface_bytes": nbytes, "GB/s": nbytes / ms / 1e6, "frac_of_hbm_peak": nbytes / ms / 1e6 / peak,
+                         "edges_per_s": e / (ms * 1e-3)}
+
+    # scores + softmax: 4 heads of 8 x (m = 0..3), D = 224 (BASELINE config 2 layout)
+    heads, attn = 4, FieldType({0: 8, 1: 8, 2: 8, 3: 8})
+    owner = type("Layer", (), {})()
+    p = fa._plan(owner, attn, attn.scaled(heads), heads)
+    desc = fa.descriptors(owner, p, dev)
+    D = p.width
+    q, k = rnd(n, D), rnd(n, D)
+    ext = fa.extension(True)
+    sm = (geo.transport, geo.bias, geo.inside, desc, geo.row_ptr, geo.source, heads, 1.0 / math.sqrt(attn.dimension), geo.max_degree)
+    alpha = ext.softmax_forward(q, k, *sm[:6], *sm[6:])
+    dalpha = rnd(e, heads)
+    tab = e * (geo.transport.shape[1] * 2 * 4 + 4 + 1 + 8) + (n + 1) * 8
+    timed("softmax_forward", lambda: ext.softmax_forward(q, k, *sm), 2 * n * D * 4 + tab + e * heads * 4)
+    timed("softmax_backward", lambda: ext.softmax_backward(dalpha, q, k, *sm[:6], alpha, *sm[6:]), 4 * n * D * 4 + tab + 2 * e * heads * 4)
+    del q, k, alpha, dalpha
+    # depthwise conv: 16 x (m = 0, 1, 2): D = 80, a0 = 16, W = 128
+    conv_type = FieldType({0: 16, 1: 16, 2: 16})
+    owner2 = type("Layer", (), {})()
+    p2 = fa._plan(owner2, conv_type, conv_type, 1)
+    desc2 = fa.descriptors(owner2, p2, dev)
+    v, g = rnd(n, p2.width), rnd(n, p2.width)
+    rc, cc = rnd(e, p2.a_0), rnd(e, p2.complex_width)
+    cv = (rc, cc, geo.transport, geo.angular, geo.rho, geo.weights, desc2, geo.row_ptr, geo.source, p2.a_0, p2.complex_width)
+    coeff = e * (p2.a_0 + p2.complex_width) * 4
+    tab2 = e * (2 * geo.transport.shape[1] * 2 * 4 + 8 + 8) + (n + 1) * 8
+    timed("conv_forward", lambda: ext.conv_forward(v, *cv), 2 * n * p2.width * 4 + coeff + tab2)
+    timed("conv_backward", lambda: ext.conv_backward(g, v, *cv), 3 * n * p2.width * 4 + 2 * coeff + tab2)
+    del rc, cc, v, g
+    # factored value kernel {8, 8, 8} -> {4, 4, 4}, trunk 16 (BASELINE config 1 value kernel: 13 blocks, wc 48, wr 4)
+    tin, tout, kk = {0: 8, 1: 8, 2: 8}, {0: 4, 1: 4, 2: 4}, 17
+    blocks, powers = [(0, 0, "real")], {}
+    for a_n in sorted(tin):
+        for m in sorted(tout):
+            if a_n == 0 and m == 0:
+                continue
+            blocks.append((a_n, m, "linear")); powers[(a_n, m, "linear")] = abs(m - a_n)
+            if a_n and m:
+                blocks.append((a_n, m, "antilinear")); powers[(a_n, m, "antilinear")] = m + a_n
+    fplan = ff.plan_blocks(blocks, FieldType(tout), powers)
+    fdesc = torch.tensor([b.row() for b in fplan.blocks], dtype=torch.int32, device=dev)
+    h, zc, zr = rnd(e, kk - 1), rnd(n, kk, fplan.wc, 2), rnd(n, kk, fplan.wr)
+    order, gptr, gsrc = ff.source_groups(geo.source)
+    fext = ff.extension(True)
+    fa_args = (h, zc, zr, geo.angular, geo.transport, geo.rho, fdesc, geo.source, order, gptr, gsrc)
+    rows = fext.forward(*fa_args, fplan.d_out, fplan.max_bm)
+    grow = rnd(e, fplan.d_out)
+    zbytes = n * kk * (2 * fplan.wc + fplan.wr) * 4
+    ftab = e * (2 * geo.transport.shape[1] * 2 * 4 + 4 + 8 + 8)
+    timed("factored_forward", lambda: fext.forward(*fa_args, fplan.d_out, fplan.max_bm), e * (kk - 1) * 4 + zbytes + ftab + e * fplan.d_out * 4)
+    timed("factored_aggregate", lambda: fext.aggregate(rows, geo.weights, geo.row_ptr), e * (fplan.d_out + 1) * 4 + n * fplan.d_out * 4)
+    timed("factored_backward", lambda: fext.backward(grow, *fa_args), 2 * e * (kk - 1) * 4 + 2 * zbytes + ftab + e * fplan.d_out * 4)
+    del h, zc, zr, rows, grow
+    # pair term 8 -> 8 linear block, trunk 16, complex matrix
+    a_, b_, t_ = 8, 8, 16
+    pext = fp.extension()
+    hidden, weight, bias = rnd(e, t_), rnd(2 * a_ * b_, t_), rnd(2 * a_ * b_)
+    u = torch.view_as_complex(rnd(e, a_, 2))
+    pre, post = geo.angular[:, 1].contiguous(), geo.angular[:, 2].contiguous()
+    pre_c, post_c = torch.view_as_complex(pre), torch.view_as_complex(post)
+    out = torch.view_as_complex(torch.zeros(e, b_, 2, device=dev))
+    timed("pairs_forward", lambda: pext.forward(hidden, weight, bias, u, pre_c, post_c, geo.rho, out, a_, b_, 1),
+          e * (t_ + 2 * a_ + 4 + 1 + 4 * b_) * 4)
+    gu, gh, gk = torch.zeros_like(u), torch.zeros_like(hidden), torch.empty(2 * a_ * b_, e, device=dev)
+    gout = torch.view_as_complex(rnd(e, b_, 2))
+    timed("pairs_backward", lambda: pext.backward(hidden, weight, bias, u, pre_c, post_c, geo.rho, gout, gu, gh, gk, a_, b_, 1),
+          e * (3 * t_ + 6 * a_ + 4 + 1 + 2 * b_ + 2 * a_ * b_) * 4)
+    print(json.dumps({"workload": f"op-level entry points, {nlat}x{nlon} lattice, radius 3pi/{nlat}, {e} edges, fp32", "hbm_peak_GB/s": peak,
+                      "ops": results}))
+
+
 def main() -> None:
     args = parse()
+    if args.workload == "ops":
+        run_ops(args)
+        return
     cfg = {"headline": HEADLINE, "mid": MID, "small": SMALL}[args.workload]
     if args.impl == "reference":
         run_reference(args, cfg)
