@@ -213,7 +213,8 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
     from gm_attention_b200.fields import FieldType
     from gm_attention_b200.geometry import midpoint_lattice
     from gm_attention_b200.nn import fused_attention as fa
-    from gm_attention_b200.parallel import BandPlan, HaloExchanger, band_geometry, row_degrees
+    from gm_attention_b200.parallel import (BandPlan, HaloExchanger, band_geometry, row_degrees, row_pair_counts,
+                                            tensor_core_row_cost)
 
     _lib.lib()
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -235,7 +236,11 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
     lattice = midpoint_lattice(nlat, nlon, device)
     w = lattice.band(radius)
     if world > 1:
-        plan = BandPlan.balanced(nlat, nlon, w, row_degrees(lattice, radius), world)
+        if args.kernel == "lattice" and args.dtype == "bf16":  # balance the kernels' cost model, not the raw edge count
+            row_cost = tensor_core_row_cost(row_pair_counts(lattice, radius))
+        else:
+            row_cost = row_degrees(lattice, radius)
+        plan = BandPlan.balanced(nlat, nlon, w, row_cost, world)
     else:
         plan = BandPlan(nlat, nlon, w, (0, nlat))
     lo, hi = plan.owned(rank)

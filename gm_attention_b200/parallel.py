@@ -97,7 +97,8 @@ class BandPlan:
         return (lo, hi) if lo < hi else None
 
     @staticmethod
-    def balanced(nlat: int, nlon: int, halo: int, row_degree: list[int], world: int) -> BandPlan:
+    def balanced(nlat: int, nlon: int, halo: int, row_degree: list[int] | list[float], world: int) -> BandPlan:
+        """Bands of (nearly) equal total ``row_degree`` -- edges per node of each row, or any per-row cost."""
         return BandPlan(nlat, nlon, halo, tuple(balanced_cuts([d * nlon for d in row_degree], world)))
 
     def load(self, row_degree: list[int]) -> list[int]:
@@ -195,3 +196,39 @@ def row_degrees(lattice, radius: float) -> list[int]:
     with torch.cuda.device(device):
         _lib.call("gm_geometry_count", _lib.ptr(lattice.nodes), n, _lib.ptr(lo), _lib.ptr(hi), float(radius), _lib.ptr(degree), _lib.stream(device))
     return degree.reshape(lattice.nlat, lattice.nlon)[:, 0].tolist()
+
+
+def row_pair_counts(lattice, radius: float) -> Tensor:
+    """``(nlat, 2 W + 1)``: neighbours a node of row ``i`` has in row ``i + dj`` (0 where the row does not exist),
+    from count-only passes restricted to one source row each."""
+    from gm_attention_b200 import _lib
+
+    device = lattice.nodes.device
+    nlat, nlon, w = lattice.nlat, lattice.nlon, lattice.band(radius)
+    rows = torch.arange(nlat, device=device)
+    counts = torch.zeros(nlat, 2 * w + 1, dtype=torch.int64, device=device)
+    degree = torch.empty(nlat * nlon, dtype=torch.int64, device=device)
+    with torch.cuda.device(device):
+        for dj in range(-w, w + 1):
+            src = rows + dj
+            ok = (src >= 0) & (src < nlat)
+            lo = (src.clamp(0, nlat - 1) * nlon)
+            hi = torch.where(ok, lo + nlon, lo)
+            lo_n, hi_n = lo.repeat_interleave(nlon).contiguous(), hi.repeat_interleave(nlon).contiguous()
+            _lib.call("gm_geometry_count", _lib.ptr(lattice.nodes), nlat * nlon, _lib.ptr(lo_n), _lib.ptr(hi_n), float(radius),
+                      _lib.ptr(degree), _lib.stream(device))
+            counts[:, dj + w] = degree.reshape(nlat, nlon)[:, 0]
+    return counts
+
+
+def tensor_core_row_cost(pair_counts: Tensor) -> list[float]:
+    """Relative cost of one lattice row under the tensor-core lattice kernels.  A warp owns 16 consecutive owners and
+    walks, for every neighbour row, the 15 + cnt positions their windows cover: Gram + elementwise work per 8 positions,
+    softmax + value accumulation per 16, plus a fixed cost per staged row pair.  Narrow equatorial windows therefore cost
+    several times more PER EDGE than whole-row polar windows, which an edge-count balance ignores."""
+    cnt = pair_counts.to(torch.float64)
+    present = cnt > 0
+    halves = torch.ceil((15 + cnt) / 8)
+    steps = torch.ceil((15 + cnt) / 16)
+    cost = torch.where(present, 150.0 * halves + 115.0 * steps + 150.0, torch.zeros_like(cnt))
+    return cost.sum(1).tolist()
