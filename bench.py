@@ -341,6 +341,28 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
     else:
         per_pass = None
 
+    # ---- the same layer with fp32 node fields (FMA lattice kernels), for the record: 3 timed steps, N = 1 only
+    f32_line = None
+    if world == 1 and args.dtype == "bf16" and args.kernel == "lattice" and not args.no_e2e:
+        q32, k32, v32, g32 = (flat(x).float() for x in (q, k, v, g))
+        for _ in range(2):
+            o32, l32 = attention_forward(q32, k32, v32, tables)
+            attention_backward(g32, q32, k32, v32, o32, l32, tables)
+        torch.cuda.synchronize()
+        ev32 = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        ev32[0].record()
+        for _ in range(3):
+            o32, l32 = attention_forward(q32, k32, v32, tables)
+        ev32[1].record()
+        for _ in range(3):
+            attention_backward(g32, q32, k32, v32, o32, l32, tables)
+        ev32[2].record()
+        torch.cuda.synchronize()
+        f_ms, b_ms = ev32[0].elapsed_time(ev32[1]) / 3, ev32[1].elapsed_time(ev32[2]) / 3
+        f32_line = {"dtype": "f32", "fwd_ms": f_ms, "bwd_ms": b_ms, "value": total_edges / ((f_ms + b_ms) * 1e-3), "unit": "edges/s",
+                    "hbm_frac": (12 * n_rows_local * D * 4 + 2 * n_rows_local * heads * 4) / ((f_ms + b_ms) * 1e-3) / 1e9 / 6548.2}
+        del q32, k32, v32, g32, o32, l32
+
     # ---- end to end from pinned host buffers (copies inside the timed region)
     e2e = None
     if not args.no_e2e:
@@ -403,6 +425,7 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
             "gpu_launches": args.steps * launches,
             "clocks": clocks.summary(),
             "e2e": e2e,
+            "other_dtypes": f32_line,
         }
         if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = {k: val for k, val in cpu_layer_rate(cfg).items() if k != "seconds"}

@@ -116,6 +116,7 @@ __global__ void __launch_bounds__(LAT_THREADS) lattice_kernel(LatArgs<S> a) {
   float* s1 = smem;
   float* s2 = smem + (size_t)SC * pitch;
   float* sstat = s2 + (size_t)SC * pitch;  // (SC, 2): lse, delta of the staged rows (pass S)
+  float* sent = sstat + 2 * (size_t)SC;     // (SC + TL, ES): table entries of the offsets a chunk can meet
 
   // The lane's runs: scalars u = ls * NR + x (valid below a0), complex copies u = ls * UC + x (valid below ac,
   // frequency below n_cf).  An invalid slot keeps zero owner values, reads a clamped (valid, finite) staged
@@ -245,6 +246,12 @@ __global__ void __launch_bounds__(LAT_THREADS) lattice_kernel(LatArgs<S> a) {
           }
         }
       }
+      // the table entries of the offsets x = p - (tile offset) this chunk can meet, clamped (validity is decided from x)
+      for (int idx = threadIdx.x; idx < (np + TL) * a.ES; idx += LAT_THREADS) {
+        const int xi = idx / a.ES, w = idx - xi * a.ES;
+        const int x = min(max(xi + p0 - (TL - 1), 0), cnt - 1);
+        sent[idx] = __ldg(ent + (size_t)x * a.ES + w);
+      }
       __syncthreads();
       // Owner tt of pair `group` sits at tile offset q0 + tt and reads positions p = q0 + tt + x, x in [0, cnt).
       // The walk is over r = p - q0, the SAME r for every lane of the warp (the shuffles below need all 32
@@ -294,7 +301,7 @@ __global__ void __launch_bounds__(LAT_THREADS) lattice_kernel(LatArgs<S> a) {
         for (int tt = 0; tt < TT; ++tt) {
           const int x = r - tt;
           const bool valid = staged && own_ok[tt] && x >= 0 && x < cnt;
-          const float* e = ent + (size_t)(valid ? x : 0) * a.ES;
+          const float* e = sent + (size_t)(valid ? (p - p0) - (q0 + tt) + (TL - 1) : 0) * a.ES;
           float tr[NCF > 0 ? NCF : 1], ti[NCF > 0 ? NCF : 1];
           float part = 0.f, dpart = 0.f;
 #pragma unroll
@@ -305,8 +312,8 @@ __global__ void __launch_bounds__(LAT_THREADS) lattice_kernel(LatArgs<S> a) {
 #pragma unroll
           for (int f = 0; f < NCF; ++f) {
             const int n = P.cf_order[f < P.n_cf ? f : 0];
-            tr[f] = __ldg(e + 2 * (n - 1));
-            ti[f] = __ldg(e + 2 * (n - 1) + 1);
+            tr[f] = e[2 * (n - 1)];
+            ti[f] = e[2 * (n - 1) + 1];
             // G = sum over copies of conj(q) k  (q on the owner side in passes FWD / T, on the neighbour side in pass S)
             float gr = 0.f, gi = 0.f, hr = 0.f, hi = 0.f;
 #pragma unroll
@@ -334,7 +341,7 @@ __global__ void __launch_bounds__(LAT_THREADS) lattice_kernel(LatArgs<S> a) {
             if (MODE != MODE_FWD) dpart += __shfl_xor_sync(0xffffffffu, dpart, o);
           }
           // logits are kept in base 2 (scale and bias carry log2 e), so the exponentials are single ex2 instructions
-          const float bias = valid ? __ldg(e + 2 * a.NORD) : -INFINITY;
+          const float bias = valid ? e[2 * a.NORD] : -INFINITY;
           const float logit = LOG2E * (a.scale * part + bias);
           if (MODE == MODE_FWD) {
             if (logit > m[tt]) {
@@ -516,11 +523,11 @@ int launch_lattice(const LatCall& c, const int64_t* desc_host, int F, int rows, 
   const int TL = (LAT_THREADS / L) * TT;
   const int tiles = (nlon + TL - 1) / TL;
   // rows staged per chunk: what ~48 KiB of shared memory hold (two fields + stats), at least TL + 8
-  int SC = (48 * 1024) / ((2 * a.plan.pitch + 2) * (int)sizeof(float));
+  int SC = (44 * 1024) / ((2 * a.plan.pitch + 2 + ES) * (int)sizeof(float));
   if (SC < TL + 8) SC = TL + 8;
   if (SC > nlon + TL) SC = nlon + TL;
   a.SC = SC;
-  const size_t smem = (size_t)SC * (2 * a.plan.pitch + 2) * sizeof(float);
+  const size_t smem = ((size_t)SC * (2 * a.plan.pitch + 2) + (size_t)(SC + TL) * ES) * sizeof(float);
   dim3 grid((unsigned)(c.n_order_rows * tiles), (unsigned)H, (unsigned)batch);
   auto go = [&](auto kernel) {
     int st = allow_smem(kernel, smem, "gm_lattice_attention");
