@@ -41,7 +41,8 @@ MODULES = {
 
 
 def default_reference() -> Path:
-    return Path(os.environ.get("GM_REFERENCE_ROOT", "/root/reference"))
+    """``$GM_REFERENCE_ROOT``, else a checkout named ``reference`` next to this repository."""
+    return Path(os.environ.get("GM_REFERENCE_ROOT", str(HERE.parent.parent / "reference")))
 
 
 def compile_one(name: str, source: Path, force: bool) -> Path:

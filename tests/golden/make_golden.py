@@ -1,8 +1,8 @@
 """Generate the golden fixtures under ``tests/golden/`` by running the reference.
 
-Run where a checkout of masonfaldet/gm-attention is mounted (default
-``/root/reference``) and ``oracle/_ref`` has been built (``python
-oracle/build_ref.py``)::
+Run where a checkout of masonfaldet/gm-attention is mounted (``$GM_REFERENCE_ROOT``,
+default: a directory ``reference`` next to this repository) and ``oracle/_ref``
+has been built (``python oracle/build_ref.py``)::
 
     python tests/golden/make_golden.py
 
@@ -36,7 +36,7 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 REPO = HERE.parent.parent
-REFERENCE = Path(os.environ.get("GM_REFERENCE_ROOT", "/root/reference"))
+REFERENCE = Path(os.environ.get("GM_REFERENCE_ROOT", str(REPO.parent / "reference")))
 sys.path.insert(0, str(REFERENCE / "src"))
 sys.path.insert(0, str(REPO))
 
