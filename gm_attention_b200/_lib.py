@@ -15,7 +15,7 @@ from typing import Any
 import torch
 
 LIBRARY = Path(__file__).resolve().parent / "libgmb200.so"
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 GM_F32, GM_F64, GM_BF16 = 0, 1, 2
 _DTYPES = {torch.float32: GM_F32, torch.float64: GM_F64, torch.bfloat16: GM_BF16}
@@ -24,7 +24,7 @@ _P, _I, _L, _D = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_double
 
 #: name -> argument ctypes, in the order of include/gm_b200.h
 SIGNATURES: dict[str, list[Any]] = {
-    "gm_softmax_forward": [_P] * 8 + [_L, _L, _I, _I, _I, _I, _D, _L, _I, _P, _P],
+    "gm_softmax_forward": [_P] * 8 + [_L, _L, _I, _I, _I, _I, _D, _L, _I, _I, _P, _P],
     "gm_softmax_backward": [_P] * 10 + [_L, _L, _I, _I, _I, _I, _D, _L, _I, _P, _P, _P],
     "gm_conv_forward": [_P] * 10 + [_L, _L, _I, _I, _I, _I, _I, _I, _P, _P],
     "gm_conv_backward": [_P] * 11 + [_L, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P],

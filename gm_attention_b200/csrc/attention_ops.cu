@@ -133,6 +133,77 @@ __global__ void __launch_bounds__(SM_THREADS) softmax_forward_kernel(SoftmaxArgs
   }
 }
 
+
+// Scores + softmax with the lanes of a warp split into H head groups (H a power of two): one warp per target,
+// a group of L = 32 / H lanes owns a head and each lane the copies u = s, s + L, ... of every frequency (at most
+// R per frequency).  Per edge every lane reads its own columns of k_j (the groups together read the whole row once),
+// the group reduces with log2(L) xor-shuffles, and all H logits of the edge appear at once.  The raw logits go to
+// alpha, the row is then normalised in place by the same warp (masked edges never enter the shift or the sum).
+template <typename T, int R>
+__global__ void __launch_bounds__(128) softmax_forward_grouped_kernel(SoftmaxArgs<T> a) {
+  const int lane = threadIdx.x & 31;
+  const int64_t i = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (i >= a.n_nodes) return;
+  const int L = 32 / a.H, h = lane / L, s = lane % L;
+  int col[MAX_F][R], order[MAX_F];
+  T qr[MAX_F][R], qi[MAX_F][R];
+#pragma unroll
+  for (int f = 0; f < MAX_F; ++f) {
+    order[f] = -1;
+#pragma unroll
+    for (int r = 0; r < R; ++r) { col[f][r] = -1; qr[f][r] = qi[f][r] = T(0); }
+    if (f < a.F) {
+      const int n = (int)a.desc[f * DESC], a_n = (int)a.desc[f * DESC + 1], off = (int)a.desc[f * DESC + 2];
+      order[f] = n;
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const int u = s + L * r;
+        if (u < a_n) {
+          col[f][r] = off + (n == 0 ? 1 : 2) * (h * a_n + u);
+          qr[f][r] = a.q[i * a.D + col[f][r]];
+          if (n != 0) qi[f][r] = a.q[i * a.D + col[f][r] + 1];
+        }
+      }
+    }
+  }
+  const int64_t e0 = a.row_ptr[i], e1 = a.row_ptr[i + 1];
+  T m = neg_inf<T>();
+  for (int64_t e = e0; e < e1; ++e) {
+    const T* k_j = a.k + a.source[e] * a.D;
+    const T* tau = a.transport + e * a.orders * 2;
+    T part = T(0);
+#pragma unroll
+    for (int f = 0; f < MAX_F; ++f) {
+      if (order[f] < 0) continue;
+      const T tr = order[f] ? tau[2 * order[f]] : T(1), ti = order[f] ? tau[2 * order[f] + 1] : T(0);
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        if (col[f][r] < 0) continue;
+        if (order[f] == 0) {
+          part += qr[f][r] * k_j[col[f][r]];
+        } else {
+          const T kr = k_j[col[f][r]], ki = k_j[col[f][r] + 1];
+          part += qr[f][r] * (tr * kr - ti * ki) + qi[f][r] * (tr * ki + ti * kr);
+        }
+      }
+    }
+    for (int o = L >> 1; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    const T lw = a.scale * part + a.bias[e];
+    if (a.inside[e] && lw > m) m = lw;
+    if (s == 0) a.alpha[e * a.H + h] = lw;
+  }
+  __syncwarp();
+  // normalise: the group's lanes stride the row's edges for their head
+  T sum = T(0);
+  for (int64_t e = e0 + s; e < e1; e += L) {
+    const T u = a.inside[e] ? gm_exp(a.alpha[e * a.H + h] - m) : T(0);
+    a.alpha[e * a.H + h] = u;
+    sum += u;
+  }
+  for (int o = L >> 1; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  for (int64_t e = e0 + s; e < e1; e += L) a.alpha[e * a.H + h] /= sum;
+}
+
 template <typename T>
 __global__ void softmax_backward_kernel(SoftmaxArgs<T> a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -298,7 +369,16 @@ int column_threads(int D) {
 int grid_for(int64_t n_nodes) { return (int)(n_nodes < (int64_t)1 << 30 ? n_nodes : (int64_t)1 << 30); }
 
 template <typename T>
-int softmax_forward_t(SoftmaxArgs<T> a, int64_t deg_max, cudaStream_t stream) {
+int softmax_forward_t(SoftmaxArgs<T> a, int64_t deg_max, int max_mult, cudaStream_t stream) {
+  // head-group kernel when the heads split a warp evenly and every lane owns at most 4 copies per frequency
+  if ((a.H == 1 || a.H == 2 || a.H == 4 || a.H == 8) && max_mult > 0 && max_mult <= 4 * (32 / a.H)) {
+    const int per_lane = (max_mult + 32 / a.H - 1) / (32 / a.H);
+    const unsigned blocks = (unsigned)((a.n_nodes + 3) / 4);
+    if (per_lane <= 1) softmax_forward_grouped_kernel<T, 1><<<blocks, 128, 0, stream>>>(a);
+    else if (per_lane <= 2) softmax_forward_grouped_kernel<T, 2><<<blocks, 128, 0, stream>>>(a);
+    else softmax_forward_grouped_kernel<T, 4><<<blocks, 128, 0, stream>>>(a);
+    return launch_status("gm_softmax_forward");
+  }
   // Logits in shared memory when the largest neighbourhood fits ~96 KiB; else kept in alpha.
   const size_t budget = 96 * 1024;
   size_t want = (size_t)deg_max * a.H;
@@ -341,7 +421,7 @@ using namespace gmb;
 extern "C" int gm_softmax_forward(const void* q, const void* k, const void* transport, const void* bias,
                                   const uint8_t* inside, const int64_t* desc, const int64_t* row_ptr,
                                   const int64_t* source, int64_t n_nodes, int64_t n_edges, int D, int F, int orders,
-                                  int H, double scale, int64_t deg_max, int dtype, void* alpha, void* stream) {
+                                  int H, double scale, int64_t deg_max, int max_mult, int dtype, void* alpha, void* stream) {
   int status = check_softmax(q, k, transport, bias, inside, desc, row_ptr, source, n_nodes, n_edges, D, F, orders, H, dtype);
   if (status != GM_OK || n_nodes == 0 || n_edges == 0) return status;
   GM_REQUIRE(alpha, GM_ERR_ARGUMENT, "gm_softmax_forward: null alpha");
@@ -352,7 +432,7 @@ extern "C" int gm_softmax_forward(const void* q, const void* k, const void* tran
     a.q = (const T*)q; a.k = (const T*)k; a.transport = (const T*)transport; a.bias = (const T*)bias;
     a.inside = inside; a.desc = desc; a.row_ptr = row_ptr; a.source = source; a.alpha = (T*)alpha;
     a.n_nodes = n_nodes; a.D = D; a.F = F; a.orders = orders; a.H = H; a.scale = (T)scale;
-    return softmax_forward_t<T>(a, deg_max, (cudaStream_t)stream);
+    return softmax_forward_t<T>(a, deg_max, max_mult, (cudaStream_t)stream);
   };
   return dtype == GM_F32 ? run(float()) : run(double());
 }

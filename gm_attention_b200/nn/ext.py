@@ -30,6 +30,23 @@ class AttentionExtension:
 
     with_cuda = True
 
+    def __init__(self) -> None:
+        #: largest multiplicity of a descriptor tensor, read back from the device once per tensor
+        self._max_mult: dict[tuple[int, int], tuple[object, int]] = {}
+
+    def _largest_multiplicity(self, desc: Tensor) -> int:
+        key = (desc.data_ptr(), desc.size(0))
+        hit = self._max_mult.get(key)
+        if hit is not None and hit[0]() is desc:
+            return hit[1]
+        import weakref
+
+        value = int(desc[:, 1].max()) if desc.size(0) else 0
+        if len(self._max_mult) > 256:
+            self._max_mult.clear()
+        self._max_mult[key] = (weakref.ref(desc), value)
+        return value
+
     # -- depthwise convolution -------------------------------------------------
     @staticmethod
     def _check_conv(v: Tensor, rc: Tensor, cc: Tensor, transport: Tensor, angular: Tensor, rho: Tensor, weights: Tensor,
@@ -115,8 +132,8 @@ class AttentionExtension:
         with torch.cuda.device(device):
             _lib.call("gm_softmax_forward", _lib.ptr(q), _lib.ptr(k), _lib.ptr(transport), _lib.ptr(bias), _lib.ptr(inside),
                       _lib.ptr(desc), _lib.ptr(row_ptr), _lib.ptr(source), q.size(0), source.size(0), q.size(1), desc.size(0),
-                      transport.size(1), int(heads), float(scale), int(deg_max), _lib.dtype_code(q.dtype), _lib.ptr(alpha),
-                      _lib.stream(device))
+                      transport.size(1), int(heads), float(scale), int(deg_max), self._largest_multiplicity(desc),
+                      _lib.dtype_code(q.dtype), _lib.ptr(alpha), _lib.stream(device))
         return alpha
 
     def softmax_backward(self, dalpha: Tensor, q: Tensor, k: Tensor, transport: Tensor, bias: Tensor, inside: Tensor, desc: Tensor,

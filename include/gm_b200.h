@@ -54,12 +54,14 @@ const char* gm_last_error(void);
  *   alpha       (n_edges, H)            out
  *   dq          (n_nodes, D)            out (written)
  *   dk          (n_nodes, D)            out, ACCUMULATED (zero it first)
+ *   max_mult    the largest a_n among desc's rows if the host knows it (desc lives on the device), else 0:
+ *               lets the forward pick the kernel that splits a warp's lanes over the heads
  * dtype: GM_F32 or GM_F64.
  * ------------------------------------------------------------------------ */
 int gm_softmax_forward(const void* q, const void* k, const void* transport, const void* bias, const uint8_t* inside,
                        const int64_t* desc, const int64_t* row_ptr, const int64_t* source, int64_t n_nodes,
-                       int64_t n_edges, int D, int F, int orders, int H, double scale, int64_t deg_max, int dtype,
-                       void* alpha, void* stream);
+                       int64_t n_edges, int D, int F, int orders, int H, double scale, int64_t deg_max, int max_mult,
+                       int dtype, void* alpha, void* stream);
 
 int gm_softmax_backward(const void* dalpha, const void* q, const void* k, const void* transport, const void* bias,
                         const uint8_t* inside, const int64_t* desc, const int64_t* row_ptr, const int64_t* source,

@@ -58,12 +58,12 @@ def test_bad_arguments_are_refused_without_a_gpu(library):
     fn = library.gm_softmax_forward
     fn.restype = ctypes.c_int
     P, I, L, D = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_double
-    fn.argtypes = [P] * 8 + [L, L, I, I, I, I, D, L, I, P, P]
-    status = fn(None, None, None, None, None, None, None, None, 4, 4, 8, 1, 1, 99, 1.0, 1, 0, None, None)
+    fn.argtypes = [P] * 8 + [L, L, I, I, I, I, D, L, I, I, P, P]
+    status = fn(None, None, None, None, None, None, None, None, 4, 4, 8, 1, 1, 99, 1.0, 1, 0, 0, None, None)
     assert status == -1
     library.gm_last_error.restype = ctypes.c_char_p
     assert b"heads" in library.gm_last_error()
-    status = fn(None, None, None, None, None, None, None, None, 4, 4, 8, 1, 1, 2, 1.0, 1, 7, None, None)
+    status = fn(None, None, None, None, None, None, None, None, 4, 4, 8, 1, 1, 2, 1.0, 1, 0, 7, None, None)
     assert status == -2
 
 
