@@ -367,10 +367,11 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
     e2e = None
     if not args.no_e2e:
         outs_host = [torch.empty(shape, dtype=dtype).pin_memory() for _ in range(4)]
-        if halo is None:
+        if args.kernel == "lattice":
             # host-resident fields through the public host API: sample chunks pipelined over three streams
+            # (with latitude bands, every chunk's halos are exchanged inside the pipeline)
             from gm_attention_b200.attention import HostPipeline
-            pipeline = HostPipeline(tables, batch, D, dtype, device, chunk=1)
+            pipeline = HostPipeline(tables, batch, D, dtype, device, chunk=1, halo=halo)
             host_flat = [x.view(batch * n_ext, D) for x in host]
             outs_flat = [x.view(batch * n_ext, D) for x in outs_host]
             def e2e_step():
@@ -379,10 +380,12 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
             def e2e_step():
                 dev = [x.to(device, non_blocking=True) for x in host]
                 qq, kk, vv, gg = dev
-                halo.fill_halos(kk, vv)
+                if halo is not None:
+                    halo.fill_halos(kk, vv)
                 out, lse = attention_forward(flat(qq), flat(kk), flat(vv), tables)
                 dq, dk, dv = attention_backward(flat(gg), flat(qq), flat(kk), flat(vv), out, lse, tables)
-                halo.reduce_halos(dk.view(shape), dv.view(shape))
+                if halo is not None:
+                    halo.reduce_halos(dk.view(shape), dv.view(shape))
                 for dst, src in zip(outs_host, (out, dq, dk, dv)):
                     dst.copy_(src.view(shape), non_blocking=True)
         for _ in range(2):

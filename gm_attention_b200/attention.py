@@ -347,8 +347,12 @@ class HostPipeline:
     ``i - 1`` are copied device -> host.  Device staging buffers are allocated once
     (two chunks deep) and reused across calls."""
 
-    def __init__(self, tables: Any, batch: int, width: int, dtype: torch.dtype, device: torch.device, chunk: int = 1) -> None:
-        self.tables, self.batch, self.chunk, self.device = tables, batch, chunk, device
+    def __init__(self, tables: Any, batch: int, width: int, dtype: torch.dtype, device: torch.device, chunk: int = 1,
+                 halo: Any = None) -> None:
+        """``halo``: a :class:`gm_attention_b200.parallel.HaloExchanger` when the lattice is sharded into latitude
+        bands: every chunk's key / value halos are filled before its forward and its dk / dv halo sums are handed
+        back after its backward, on the compute stream (all ranks walk the chunks in the same order)."""
+        self.tables, self.batch, self.chunk, self.device, self.halo = tables, batch, chunk, device, halo
         n = (tables.rows * tables.nlon) if isinstance(tables, LatticeTables) else tables.n_nodes
         self.n_nodes = n
         shape = (chunk * n, width)
@@ -381,8 +385,14 @@ class HostPipeline:
                 loaded[i].record(h2d)
             with torch.cuda.stream(comp):
                 comp.wait_event(loaded[i])
+                if self.halo is not None:
+                    banded = (self.chunk, self.tables.rows, self.tables.nlon, slot[1].shape[1])
+                    self.halo.fill_halos(slot[1].view(banded), slot[2].view(banded))
                 o, lse = fwd(slot[0], slot[1], slot[2], self.tables)
-                results[i] = (o, *bwd(slot[3], slot[0], slot[1], slot[2], o, lse, self.tables))
+                grads = bwd(slot[3], slot[0], slot[1], slot[2], o, lse, self.tables)
+                if self.halo is not None:
+                    self.halo.reduce_halos(grads[1].view(banded), grads[2].view(banded))
+                results[i] = (o, *grads)
                 computed[i].record(comp)
             with torch.cuda.stream(d2h):
                 d2h.wait_event(computed[i])
