@@ -161,22 +161,66 @@ def workload_config(cfg: dict, args: argparse.Namespace, world: int) -> dict:
 # ----------------------------------------------------------------------------- GPU arm
 
 class ClockSampler:
+    """Samples SM clock and clock-event reasons of one GPU while a timed region runs (read-only NVML queries from a
+    thread, every few milliseconds; ``nvidia-smi -lms`` as the fallback when NVML cannot be loaded)."""
+
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
-    def __init__(self, index: int) -> None:
-        self.index, self.proc = index, None
+    def __init__(self, index: int, uuid: str | None = None) -> None:
+        self.index, self.uuid, self.proc, self.thread = index, uuid, None, None
+        self.samples: list[tuple[float, int]] = []  # (SM MHz, reason mask)
+        self.sm_max = None
+        self.source = None
+
+    def _nvml_loop(self, nv, handle) -> None:
+        while not self._stop.is_set():
+            try:
+                self.samples.append((float(nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)), int(nv.nvmlDeviceGetCurrentClocksEventReasons(handle))))
+            except Exception:  # noqa: BLE001  (a failed query is a missing sample)
+                pass
+            self._stop.wait(0.004)
 
     def __enter__(self):
         try:
+            import threading
+
+            import pynvml as nv
+
+            nv.nvmlInit()
+            handle = None
+            if self.uuid:
+                try:
+                    handle = nv.nvmlDeviceGetHandleByUUID(self.uuid.encode() if hasattr(self.uuid, "encode") else self.uuid)
+                except Exception:  # noqa: BLE001
+                    handle = None
+            if handle is None:
+                handle = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.sm_max = float(nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM))
+            self._masks = [nv.nvmlClocksEventReasonHwSlowdown, nv.nvmlClocksEventReasonHwThermalSlowdown,
+                           nv.nvmlClocksEventReasonSwThermalSlowdown, nv.nvmlClocksEventReasonSwPowerCap]
+            self._stop = threading.Event()
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, handle), daemon=True)
+            self.thread.start()
+            self.source = "nvml"
+            return self
+        except Exception:  # noqa: BLE001  (no NVML binding: fall back to the command-line tool)
+            self.thread = None
+        try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20",
                                           "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.source = "nvidia-smi"
         except OSError:
             self.proc = None
         return self
 
     def __exit__(self, *exc):
         self.rows = []
+        if self.thread is not None:
+            self._stop.set()
+            self.thread.join(timeout=2)
+            return
         if self.proc is None:
             return
         self.proc.terminate()
@@ -191,15 +235,19 @@ class ClockSampler:
                 self.rows.append(parts)
 
     def summary(self) -> dict:
+        if self.thread is not None and self.samples:
+            sm = sorted(s[0] for s in self.samples)
+            reasons = [n for n, m in zip(self.NAMES, self._masks) if any(s[1] & m for s in self.samples)]
+            busy = sm[len(sm) // 2:] or sm  # upper half = samples under load
+            return {"sm_mhz": statistics.median(busy), "sm_max_mhz": self.sm_max, "reasons": reasons, "samples": len(sm), "source": "nvml"}
         rows = getattr(self, "rows", [])
         if not rows:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
         sm = [float(r[1]) for r in rows if r[1].replace(".", "").isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(r[5 + i].lower().startswith("active") for r in rows)]
+        reasons = [n for i, n in enumerate(self.NAMES) if any(r[5 + i].lower().startswith("active") for r in rows)]
         busy = sorted(sm)[len(sm) // 2:] or sm  # upper half = samples under load
         return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": float(rows[0][2]), "reasons": reasons,
-                "samples": len(rows)}
+                "samples": len(rows), "source": "nvidia-smi"}
 
 
 def run_ours(args: argparse.Namespace, cfg: dict) -> None:
@@ -295,7 +343,8 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
         step()
     barrier()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clocks:
+    gpu_uuid = getattr(torch.cuda.get_device_properties(local), "uuid", None)
+    with ClockSampler(local, f"GPU-{gpu_uuid}" if gpu_uuid is not None else None) as clocks:
         start.record()
         for s in range(args.steps):
             step(s)

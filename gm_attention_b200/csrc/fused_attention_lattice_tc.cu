@@ -22,12 +22,17 @@
 // One CTA = 64 owners (targets; sources in the backward's source-major pass) x one
 // head x one sample; a warp owns 16 of them.  The neighbour rows of one lattice
 // row and the table entries they need are copied into shared memory as raw bf16 /
-// fp32 with cp.async (row pitch an odd number of 16-byte chunks: conflict-free
-// ldmatrix), double-buffered: the copy of the next (row pair, chunk) runs while the
-// current one is consumed.  The pair-swapped value operand of the imaginary phase
-// part is made in registers (one shuffle per fragment register).  Tensor-core
-// instruction: mma.sync m16n8k16 (bf16 inputs, fp32 accumulate); fragments via
-// ldmatrix.
+// fp32, double-buffered: the copy of the next (row pair, chunk) runs while the
+// current one is consumed.  A staged field is one sub-tile per frequency block
+// (80 positions x 32 or 64 bytes) in the 32-byte / 64-byte shared-memory swizzle,
+// so that ldmatrix is conflict-free without padding and a whole sub-tile is ONE
+// TMA tensor copy (cp.async.bulk.tensor.3d over (column, longitude, sample * row),
+// completion on an mbarrier, issued by one thread).  Chunks that wrap the
+// longitude seam, and head layouts whose blocks are not exactly 16 / 32 columns,
+// are staged with per-thread cp.async into the same swizzled layout.  The
+// pair-swapped value operand of the imaginary phase part is made in registers
+// (one shuffle per fragment register).  Tensor-core instruction: mma.sync
+// m16n8k16 (bf16 inputs, fp32 accumulate); fragments via ldmatrix.
 //
 // Backward, two deterministic passes (no atomics):
 //   pass T: owners = targets.  Gram blocks of (q, k) and of (dO, v) give the logits and d alpha;
@@ -35,6 +40,9 @@
 //   pass S: owners = SOURCES, neighbours = the targets that see them (transposed tables, their lse / Delta
 //           staged with them).  Same Gram blocks with the roles swapped, then (ds o conj tau) Q -> dk and
 //           (p o conj tau) dO -> dv.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
 #include "common.cuh"
 
 namespace gmb {
@@ -45,6 +53,11 @@ constexpr int TC_TL = 64;  // targets per CTA
 constexpr float TC_LOG2E = 1.4426950408889634f, TC_LN2 = 0.6931471805599453f;
 constexpr int TC_MAX_CF = 3;
 constexpr int TC_MAX_WIN = 33;  // 2 W + 1 neighbour rows at most
+constexpr int TC_SC = 80;       // staged positions per chunk: 64 owners + a window of up to 17 fit one chunk
+constexpr unsigned TC_WAIT_LIMIT = 1u << 22;  // polls of a copy barrier before the kernel gives up on it
+
+// set when a wait on a TMA completion barrier ran out (never expected; the results of that launch are invalid)
+__device__ int g_tc_wait_expired;
 
 struct TcPlan {
   int a0, ac, n_cf;
@@ -63,9 +76,11 @@ struct TcArgs {
   const float* entries;               // (n_entries, 8): (cos, sin) of orders 1..NORD, bias at 2 NORD
   const int* row_order;
   int rows, nlon, D, H, W, NORD;
-  int SC;  // staged positions per chunk (multiple of 16)
+  int use_tma;  // the neighbours' fields have tensor maps (exact 16 / 32-column blocks, aligned, nlon >= TC_SC)
   float scale;
   TcPlan plan;
+  // tensor maps over the neighbours' fields as (D, nlon, batch * rows): [field][0 = 16-column box, 1 = complex-block box]
+  alignas(64) CUtensorMap maps[2][2];
 };
 
 enum { TC_FWD = 0, TC_BWD_T = 1, TC_BWD_S = 2 };
@@ -88,6 +103,39 @@ __device__ __forceinline__ void ldsm_x4_trans(unsigned (&r)[4], const void* p) {
   const unsigned addr = (unsigned)__cvta_generic_to_shared(p);
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
+__device__ __forceinline__ void ldsm_x2(unsigned (&r)[2], const void* p) {
+  const unsigned addr = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+// ---- TMA + mbarrier (single CTA; no multicast)
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"((unsigned)__cvta_generic_to_shared(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"((unsigned)__cvta_generic_to_shared(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
+  unsigned done;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(done) : "r"((unsigned)__cvta_generic_to_shared(bar)), "r"(parity) : "memory");
+  return done != 0;
+}
+// bounded wait: gives up after TC_WAIT_LIMIT polls and records it
+__device__ __forceinline__ void mbar_wait(unsigned long long* bar, unsigned parity) {
+  for (unsigned tries = 0; tries < TC_WAIT_LIMIT; ++tries) {
+    if (mbar_try_wait(bar, parity)) return;
+    if (tries > 64) __nanosleep(64);
+  }
+  atomicOr(&g_tc_wait_expired, 1);
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, unsigned long long* bar, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
+               ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(reinterpret_cast<unsigned long long>(map)),
+                 "r"((unsigned)__cvta_generic_to_shared(bar)), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
+
 // 16-byte asynchronous copy global -> shared; src_bytes = 0 writes zeros
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, int src_bytes) {
   const unsigned addr = (unsigned)__cvta_generic_to_shared(dst);
@@ -141,64 +189,97 @@ __device__ __forceinline__ void load_owner_fragments(const TcPlan& P, const __nv
     }
 }
 
-// Gram blocks of 16 owners x 8 staged rows (prow0 .. prow0 + 7): g0 (scalar block), gr / gi per complex frequency.
-// OWNER_IS_Q: owners carry q, staged rows k (imaginary part against (k_im, -k_re)); otherwise owners carry k,
-// staged rows q (imaginary part against (-q_im, q_re)).  Same for (dO, v).
+// Shared-memory layout of one staged field: a sub-tile per frequency block, TC_SC rows each.  The scalar block's rows
+// are 32 bytes (16 columns), a complex frequency's rows 32 * KSC bytes.  16-byte chunk cb of row r sits at
+// r * pitch + 16 * (cb ^ s(r)), s(r) = (r >> 2) & 1 for 32-byte rows and (r >> 1) & 3 for 64-byte rows: the hardware's
+// 32-byte / 64-byte swizzle when the sub-tile starts on a 1024-byte boundary, and conflict-free for ldmatrix.
+template <int KS0, int NCF, int KSC>
+struct TcLayout {
+  static constexpr __host__ __device__ int align1k(int x) { return (x + 1023) / 1024 * 1024; }
+  static constexpr int REAL_PITCH = 32, CX_PITCH = 32 * KSC;
+  static constexpr int REAL_BYTES = KS0 ? align1k(TC_SC * REAL_PITCH) : 0;
+  static constexpr int CX_BYTES = align1k(TC_SC * CX_PITCH);
+  static constexpr int FIELD_BYTES = REAL_BYTES + NCF * CX_BYTES;
+  static constexpr int ENT_BYTES = (TC_SC + TC_TL) * 32;
+  static constexpr int BUFFER_BYTES = align1k(2 * FIELD_BYTES + ENT_BYTES + TC_SC * 8);  // with the (lse, Delta) pairs of pass S
+  static __device__ __forceinline__ int real_chunk(int r, int cb) { return r * REAL_PITCH + 16 * (cb ^ ((r >> 2) & 1)); }
+  static __device__ __forceinline__ int cx_chunk(int f, int r, int cb) {
+    return REAL_BYTES + f * CX_BYTES + r * CX_PITCH + 16 * (cb ^ (KSC == 2 ? (r >> 1) & 3 : (r >> 2) & 1));
+  }
+  // offset of padded head-local chunk ch (8 columns) of staged row r
+  static __device__ __forceinline__ int chunk(int r, int ch) {
+    if (ch < 2 * KS0) return real_chunk(r, ch);
+    const int cc = ch - 2 * KS0;
+    return cx_chunk(cc / (2 * KSC), r, cc % (2 * KSC));
+  }
+};
+
+// Gram blocks of 16 owners x 8 staged rows (prow0 .. prow0 + 7, prow0 a multiple of 8): g0 (scalar block), gr / gi per
+// complex frequency.  OWNER_IS_Q: owners carry q, staged rows k (imaginary part against (k_im, -k_re)); otherwise owners
+// carry k, staged rows q (imaginary part against (-q_im, q_re)).  Same for (dO, v).
 template <int KS0, int NCF, int KSC, bool OWNER_IS_Q>
-__device__ __forceinline__ void gram_half(const unsigned (&fa)[KS0 + NCF * KSC][4], const __nv_bfloat16* tile, int pitch, int prow0, int lane,
+__device__ __forceinline__ void gram_half(const unsigned (&fa)[KS0 + NCF * KSC][4], const unsigned char* tile, int prow0, int lane,
                                           float (&g0)[4], float (&gr)[NCF > 0 ? NCF : 1][4], float (&gi)[NCF > 0 ? NCF : 1][4]) {
-  constexpr int KQ = KS0 + NCF * KSC, DP = 16 * KQ;
+  using L = TcLayout<KS0, NCF, KSC>;
 #pragma unroll
   for (int x = 0; x < 4; ++x) {
     g0[x] = 0.f;
 #pragma unroll
     for (int f = 0; f < NCF; ++f) gr[f][x] = gi[f][x] = 0.f;
   }
+  const int mi = lane >> 3, row = prow0 + (lane & 7);  // one 8 x 8 matrix per 16-byte chunk: matrix mi <- chunk mi of the block
+  if constexpr (KS0 > 0) {
+    unsigned bf[2];
+    ldsm_x2(bf, tile + L::real_chunk(row, mi & 1));
+    mma_bf16(g0, fa[0], bf[0], bf[1]);
+  }
 #pragma unroll
-  for (int ks = 0; ks < KQ; ks += 2) {
+  for (int f = 0; f < NCF; ++f) {
     unsigned bf[4];
-    const int mi = lane >> 3, rr = lane & 7;  // matrices: (ks, k 0-7), (ks, k 8-15), (ks + 1, k 0-7), (ks + 1, k 8-15)
-    ldsm_x4(bf, tile + (prow0 + rr) * pitch + min(16 * ks + 8 * mi, DP - 8));
+    if constexpr (KSC == 2) {
+      ldsm_x4(bf, tile + L::cx_chunk(f, row, mi));
+    } else {
+      unsigned b2[2];
+      ldsm_x2(b2, tile + L::cx_chunk(f, row, mi & 1));
+      bf[0] = b2[0]; bf[1] = b2[1]; bf[2] = bf[3] = 0u;
+    }
 #pragma unroll
-    for (int sub = 0; sub < 2; ++sub) {
-      const int kk = ks + sub;
-      if (kk >= KQ) break;
+    for (int sub = 0; sub < KSC; ++sub) {
+      const int kk = KS0 + f * KSC + sub;
       const unsigned b0 = bf[2 * sub], b1 = bf[2 * sub + 1];
-      if (kk < KS0) {
-        mma_bf16(g0, fa[kk], b0, b1);
-      } else {
-        const int f = (kk - KS0) / KSC;
-        mma_bf16(gr[f], fa[kk], b0, b1);
-        if (OWNER_IS_Q) mma_bf16(gi[f], fa[kk], swap_neg(b0), swap_neg(b1));
-        else mma_bf16(gi[f], fa[kk], swap_neg_lo(b0), swap_neg_lo(b1));
-      }
+      mma_bf16(gr[f], fa[kk], b0, b1);
+      if (OWNER_IS_Q) mma_bf16(gi[f], fa[kk], swap_neg(b0), swap_neg(b1));
+      else mma_bf16(gi[f], fa[kk], swap_neg_lo(b0), swap_neg_lo(b1));
     }
   }
 }
 
-// acc (16 owners x padded head width) += A (16 owners x 16 staged rows) * tile with the phase parts: scalar
-// block a0 * tile; complex frequency f: ar[f] * tile + ai[f] * tile~, where tile~ holds each (re, im) pair as
-// (-im, re) [CONJ = false: multiplication by tau] or (im, -re) [CONJ = true: by conj tau].  tile~ is formed in
-// registers: the partner column of a B fragment lives in the lane 4 away.
+// acc (16 owners x padded head width) += A (16 owners x 16 staged rows pl .. pl + 15, pl a multiple of 16) * tile with
+// the phase parts: scalar block a0 * tile; complex frequency f: ar[f] * tile + ai[f] * tile~, where tile~ holds each
+// (re, im) pair as (-im, re) [CONJ = false: multiplication by tau] or (im, -re) [CONJ = true: by conj tau].  tile~ is
+// formed in registers: the partner column of a B fragment lives in the lane 4 away.
 template <int KS0, int NCF, int KSC, bool CONJ>
 __device__ __forceinline__ void accumulate_tiles(float (&acc)[2 * (KS0 + NCF * KSC)][4], const unsigned (&a0)[4],
                                                  const unsigned (&ar)[NCF > 0 ? NCF : 1][4], const unsigned (&ai)[NCF > 0 ? NCF : 1][4],
-                                                 const __nv_bfloat16* tile, int pitch, int pl, int lane) {
-  constexpr int NT = 2 * (KS0 + NCF * KSC);
+                                                 const unsigned char* tile, int pl, int lane) {
+  using L = TcLayout<KS0, NCF, KSC>;
   // this lane's column inside an n-tile is g = lane / 4: even = real part, odd = imaginary part
   const unsigned flip = (((lane >> 2) & 1) == (CONJ ? 1 : 0)) ? 0x80008000u : 0u;
-#pragma unroll
-  for (int nt = 0; nt < NT; nt += 2) {
-    const int mi = lane >> 3, rr = lane & 7;
-    const int prow = pl + 8 * (mi & 1) + rr, pcol = 8 * (nt + (mi >> 1));
+  const int mi = lane >> 3;
+  const int prow = pl + 8 * (mi & 1) + (lane & 7), cbl = mi >> 1;  // matrices: (rows 0-7, chunk), (rows 8-15, chunk), same for chunk + 1
+  if constexpr (KS0 > 0) {
     unsigned vf[4];
-    ldsm_x4_trans(vf, tile + prow * pitch + pcol);
-    if (nt < 2 * KS0) {
-      mma_bf16(acc[nt], a0, vf[0], vf[1]);
-      mma_bf16(acc[nt + 1], a0, vf[2], vf[3]);
-    } else {
-      const int f = (nt - 2 * KS0) / (2 * KSC);
-      unsigned wf[4];
+    ldsm_x4_trans(vf, tile + L::real_chunk(prow, cbl));
+    mma_bf16(acc[0], a0, vf[0], vf[1]);
+    mma_bf16(acc[1], a0, vf[2], vf[3]);
+  }
+#pragma unroll
+  for (int f = 0; f < NCF; ++f)
+#pragma unroll
+    for (int pair = 0; pair < KSC; ++pair) {
+      const int nt = 2 * KS0 + 2 * KSC * f + 2 * pair;
+      unsigned vf[4], wf[4];
+      ldsm_x4_trans(vf, tile + L::cx_chunk(f, prow, 2 * pair + cbl));
 #pragma unroll
       for (int x = 0; x < 4; ++x) wf[x] = __shfl_xor_sync(0xffffffffu, vf[x], 4) ^ flip;
       mma_bf16(acc[nt], ar[f], vf[0], vf[1]);
@@ -206,31 +287,34 @@ __device__ __forceinline__ void accumulate_tiles(float (&acc)[2 * (KS0 + NCF * K
       mma_bf16(acc[nt + 1], ar[f], vf[2], vf[3]);
       mma_bf16(acc[nt + 1], ai[f], wf[2], wf[3]);
     }
-  }
 }
 
 // One (row pair, chunk) of the walk over an owner row's neighbour rows.
 struct TcStage {
   int dj, p0, cnt, lo, window;
+  int z;  // sample * rows + neighbour row
   int64_t nrow0;
   const float* ent;
 };
 
 template <int KS0, int NCF, int KSC, int MODE>
-__global__ void __launch_bounds__(TC_THREADS, MODE == TC_BWD_S ? 2 : 3) lattice_tc_kernel(TcArgs a) {
-  constexpr int KQ = KS0 + NCF * KSC, DP = 16 * KQ, CH = DP / 8, PITCH = (CH % 2 == 0 ? CH + 1 : CH) * 8, NT = 2 * KQ;
+__global__ void __launch_bounds__(TC_THREADS, MODE == TC_BWD_S ? 2 : 3) lattice_tc_kernel(const __grid_constant__ TcArgs a) {
+  using L = TcLayout<KS0, NCF, KSC>;
+  constexpr int KQ = KS0 + NCF * KSC, CH = 2 * KQ, NT = 2 * KQ;
   constexpr int NF = NCF > 0 ? NCF : 1;
   constexpr bool FWD = MODE == TC_FWD, PASS_S = MODE == TC_BWD_S;
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int SC = TC_SC;
+  extern __shared__ __align__(1024) unsigned char smem_dyn[];
+  // swizzled sub-tiles must start on 1024-byte boundaries of the shared-memory window: align by hand (1 KB of slack is requested)
+  unsigned char* const smem_raw = smem_dyn + ((1024u - ((unsigned)__cvta_generic_to_shared(smem_dyn) & 1023u)) & 1023u);
+  __shared__ __align__(8) unsigned long long copy_bar[2];  // completion of the TMA copies into buffer 0 / 1
   const TcPlan& P = a.plan;
-  const int SC = a.SC;
-  // two buffers, each: tile 1 (SC, PITCH) bf16 | tile 2 | entries (SC + TC_TL, 8) fp32 | stats (SC, 2) fp32 (pass S)
-  const size_t tile_bytes = (size_t)SC * PITCH * 2, ent_bytes = (size_t)(SC + TC_TL) * 32, stat_bytes = PASS_S ? (size_t)SC * 8 : 0;
-  const size_t buf_bytes = 2 * tile_bytes + ent_bytes + stat_bytes;
-  auto tile1 = [&](int buf) { return reinterpret_cast<__nv_bfloat16*>(smem_raw + buf * buf_bytes); };
-  auto tile2 = [&](int buf) { return reinterpret_cast<__nv_bfloat16*>(smem_raw + buf * buf_bytes + tile_bytes); };
-  auto entry = [&](int buf) { return reinterpret_cast<float*>(smem_raw + buf * buf_bytes + 2 * tile_bytes); };
-  auto stats = [&](int buf) { return reinterpret_cast<float*>(smem_raw + buf * buf_bytes + 2 * tile_bytes + ent_bytes); };
+  // two buffers, each: field 1 sub-tiles | field 2 sub-tiles | entries (SC + TC_TL, 8) fp32 | stats (SC, 2) fp32 (pass S)
+  constexpr int buf_bytes = L::BUFFER_BYTES;
+  auto tile1 = [&](int buf) { return smem_raw + buf * buf_bytes; };
+  auto tile2 = [&](int buf) { return smem_raw + buf * buf_bytes + L::FIELD_BYTES; };
+  auto entry = [&](int buf) { return reinterpret_cast<float*>(smem_raw + buf * buf_bytes + 2 * L::FIELD_BYTES); };
+  auto stats = [&](int buf) { return reinterpret_cast<float*>(smem_raw + buf * buf_bytes + 2 * L::FIELD_BYTES + L::ENT_BYTES); };
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, c = lane & 3;
   const int tiles = (a.nlon + TC_TL - 1) / TC_TL;
@@ -276,7 +360,8 @@ __global__ void __launch_bounds__(TC_THREADS, MODE == TC_BWD_S ? 2 : 3) lattice_
       const int cnt = win_s[3 * (dj + a.W)];
       if (cnt == 0) continue;
       s.dj = dj; s.p0 = 0; s.cnt = cnt; s.lo = win_s[3 * (dj + a.W) + 1]; s.window = TC_TL + cnt - 1;
-      s.nrow0 = (b * a.rows + j) * (int64_t)a.nlon;
+      s.z = (int)(b * a.rows + j);
+      s.nrow0 = (int64_t)s.z * a.nlon;
       s.ent = a.entries + (size_t)win_s[3 * (dj + a.W) + 2] * 8;
       return true;
     }
@@ -286,7 +371,7 @@ __global__ void __launch_bounds__(TC_THREADS, MODE == TC_BWD_S ? 2 : 3) lattice_
     if (s.p0 + SC < s.window) { s.p0 += SC; return true; }
     return first_chunk_of_row(s, s.dj + 1);
   };
-  // staging slots: thread -> (row within a pass, 16-byte chunk); the chunk's flat column is fixed per thread
+  // per-thread staging slots of the cp.async path: thread -> (row within a pass, 16-byte chunk); the chunk's flat column is fixed
   constexpr int ROWS_PER_PASS = TC_THREADS / CH;
   const int st_row = threadIdx.x / CH, st_ch = threadIdx.x - st_row * CH;
   const int st_g0 = flat_column<KS0, NCF, KSC>(P, h, 8 * st_ch), st_g7 = flat_column<KS0, NCF, KSC>(P, h, 8 * st_ch + 7);
@@ -294,20 +379,48 @@ __global__ void __launch_bounds__(TC_THREADS, MODE == TC_BWD_S ? 2 : 3) lattice_
   const bool st_whole = st_g0 >= 0 && st_g7 == st_g0 + 7 && (a.D % 8 == 0) && (st_g0 % 8 == 0);  // one aligned 16-byte chunk of real columns
   const bool st_pad = st_g0 < 0 && st_g7 < 0 && flat_column<KS0, NCF, KSC>(P, h, 8 * st_ch + 3) < 0;  // all padding (stays zero)
   // zero both buffers once: rows beyond a window and padding columns are never written again and must be finite
-  for (size_t x = threadIdx.x; x < 2 * buf_bytes / 16; x += TC_THREADS) reinterpret_cast<uint4*>(smem_raw)[x] = make_uint4(0, 0, 0, 0);
+  for (int x = threadIdx.x; x < 2 * buf_bytes / 16; x += TC_THREADS) reinterpret_cast<uint4*>(smem_raw)[x] = make_uint4(0, 0, 0, 0);
+  if (threadIdx.x == 0) {
+    mbar_init(&copy_bar[0], 1);
+    mbar_init(&copy_bar[1], 1);
+    fence_mbar_init();
+  }
   __syncthreads();
+  // a stage goes through the tensor maps when its positions are consecutive longitudes (no wrap at the seam)
+  auto by_tma = [&](const TcStage& s) -> bool {
+    if (!a.use_tma) return false;
+    const int lon0 = tc_wrap(c0 + s.lo + s.p0, a.nlon);
+    return lon0 + min(SC, s.window - s.p0) <= a.nlon;
+  };
   auto issue = [&](const TcStage& s, int buf) {  // asynchronous copies of one stage into buffer `buf`
-    __nv_bfloat16* d1 = tile1(buf);
-    __nv_bfloat16* d2 = tile2(buf);
+    unsigned char* d1 = tile1(buf);
+    unsigned char* d2 = tile2(buf);
     const int n_rows = min(SC, s.window - s.p0);
-    if (st_active && !st_pad) {
+    if (by_tma(s)) {
+      if (threadIdx.x == 0) {
+        // the buffer was last touched through the generic proxy (zero fill, ldmatrix, fallback stores): order those first
+        fence_proxy_async();
+        const int lon0 = tc_wrap(c0 + s.lo + s.p0, a.nlon);
+        mbar_expect_tx(&copy_bar[buf], 2u * SC * (KS0 * L::REAL_PITCH + NCF * L::CX_PITCH));
+        if constexpr (KS0 > 0) {
+          tma_load_3d(d1, &a.maps[0][0], &copy_bar[buf], P.real_off + h * 16, lon0, s.z);
+          tma_load_3d(d2, &a.maps[1][0], &copy_bar[buf], P.real_off + h * 16, lon0, s.z);
+        }
+#pragma unroll
+        for (int f = 0; f < NCF; ++f) {
+          tma_load_3d(d1 + L::REAL_BYTES + f * L::CX_BYTES, &a.maps[0][1], &copy_bar[buf], P.cf_off[f] + h * 16 * KSC, lon0, s.z);
+          tma_load_3d(d2 + L::REAL_BYTES + f * L::CX_BYTES, &a.maps[1][1], &copy_bar[buf], P.cf_off[f] + h * 16 * KSC, lon0, s.z);
+        }
+      }
+    } else if (st_active && !st_pad) {
       int lon = tc_wrap(c0 + s.lo + s.p0 + st_row, a.nlon);
       const int step = ROWS_PER_PASS % a.nlon;
       for (int pl = st_row; pl < n_rows; pl += ROWS_PER_PASS) {
         const int64_t nb = (s.nrow0 + lon) * a.D;
+        const int off = L::chunk(pl, st_ch);
         if (st_whole) {
-          cp_async16(d1 + pl * PITCH + 8 * st_ch, a.nb1 + nb + st_g0, 16);
-          cp_async16(d2 + pl * PITCH + 8 * st_ch, a.nb2 + nb + st_g0, 16);
+          cp_async16(d1 + off, a.nb1 + nb + st_g0, 16);
+          cp_async16(d2 + off, a.nb2 + nb + st_g0, 16);
         } else {  // a chunk that straddles padding or is misaligned: element by element (visible after the barrier)
           unsigned short u1[8], u2[8];
 #pragma unroll
@@ -316,9 +429,9 @@ __global__ void __launch_bounds__(TC_THREADS, MODE == TC_BWD_S ? 2 : 3) lattice_
             u1[x] = gx >= 0 ? __bfloat16_as_ushort(a.nb1[nb + gx]) : (unsigned short)0;
             u2[x] = gx >= 0 ? __bfloat16_as_ushort(a.nb2[nb + gx]) : (unsigned short)0;
           }
-          *reinterpret_cast<uint4*>(d1 + pl * PITCH + 8 * st_ch) =
+          *reinterpret_cast<uint4*>(d1 + off) =
               make_uint4(u1[0] | (u1[1] << 16), u1[2] | (u1[3] << 16), u1[4] | (u1[5] << 16), u1[6] | (u1[7] << 16));
-          *reinterpret_cast<uint4*>(d2 + pl * PITCH + 8 * st_ch) =
+          *reinterpret_cast<uint4*>(d2 + off) =
               make_uint4(u2[0] | (u2[1] << 16), u2[2] | (u2[3] << 16), u2[4] | (u2[5] << 16), u2[6] | (u2[7] << 16));
         }
         lon += step;
@@ -346,6 +459,7 @@ __global__ void __launch_bounds__(TC_THREADS, MODE == TC_BWD_S ? 2 : 3) lattice_
   TcStage cur;
   bool have = first_chunk_of_row(cur, -a.W);
   int buf = 0;
+  unsigned parity = 0;  // bit b: the phase of copy_bar[b] the next TMA stage into buffer b completes
   if (have) issue(cur, 0);
   while (have) {
     TcStage nxt = cur;
@@ -356,9 +470,13 @@ __global__ void __launch_bounds__(TC_THREADS, MODE == TC_BWD_S ? 2 : 3) lattice_
     } else {
       cp_async_wait<0>();
     }
+    if (by_tma(cur)) {
+      mbar_wait(&copy_bar[buf], (parity >> buf) & 1u);
+      parity ^= 1u << buf;
+    }
     __syncthreads();
-    const __nv_bfloat16* t1 = tile1(buf);
-    const __nv_bfloat16* t2 = tile2(buf);
+    const unsigned char* t1 = tile1(buf);
+    const unsigned char* t2 = tile2(buf);
     const float* e_s = entry(buf);
     const float* stat_s = stats(buf);
     const int p0 = cur.p0, cnt = cur.cnt;
@@ -386,8 +504,8 @@ __global__ void __launch_bounds__(TC_THREADS, MODE == TC_BWD_S ? 2 : 3) lattice_
           continue;
         }
         float s0[4], sr[NF][4], si[NF][4], h0[4], hr[NF][4], hi[NF][4];
-        gram_half<KS0, NCF, KSC, !PASS_S>(f1, t1, PITCH, pl + 8 * half, lane, s0, sr, si);
-        if constexpr (!FWD) gram_half<KS0, NCF, KSC, !PASS_S>(f2, t2, PITCH, pl + 8 * half, lane, h0, hr, hi);
+        gram_half<KS0, NCF, KSC, !PASS_S>(f1, t1, pl + 8 * half, lane, s0, sr, si);
+        if constexpr (!FWD) gram_half<KS0, NCF, KSC, !PASS_S>(f2, t2, pl + 8 * half, lane, h0, hr, hi);
         float ds[4], pr[4];
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
@@ -484,12 +602,12 @@ __global__ void __launch_bounds__(TC_THREADS, MODE == TC_BWD_S ? 2 : 3) lattice_
             xai[f][2 * half + 1] = pack_bf16(pr[2] * ti[f][half][2], pr[3] * ti[f][half][3]);
           }
         }
-        accumulate_tiles<KS0, NCF, KSC, false>(acc1, xa, xar, xai, t2, PITCH, pl, lane);   // out += (p tau) v
+        accumulate_tiles<KS0, NCF, KSC, false>(acc1, xa, xar, xai, t2, pl, lane);   // out += (p tau) v
       } else if constexpr (!PASS_S) {
-        accumulate_tiles<KS0, NCF, KSC, false>(acc1, xa, xar, xai, t1, PITCH, pl, lane);   // dq += (ds tau) k
+        accumulate_tiles<KS0, NCF, KSC, false>(acc1, xa, xar, xai, t1, pl, lane);   // dq += (ds tau) k
       } else {
-        accumulate_tiles<KS0, NCF, KSC, true>(acc1, xa, xar, xai, t1, PITCH, pl, lane);    // dk += (ds conj tau) q
-        accumulate_tiles<KS0, NCF, KSC, true>(acc2, ya, yar, yai, t2, PITCH, pl, lane);    // dv += (p conj tau) dO
+        accumulate_tiles<KS0, NCF, KSC, true>(acc1, xa, xar, xai, t1, pl, lane);    // dk += (ds conj tau) q
+        accumulate_tiles<KS0, NCF, KSC, true>(acc2, ya, yar, yai, t2, pl, lane);    // dv += (p conj tau) dO
       }
     }
     __syncthreads();  // everyone is done with `buf` before the stage after next is copied into it
@@ -611,14 +729,58 @@ int make_tc_plan(const int64_t* desc_host, int F, int H, int D, TcPlan& P) {
   return GM_OK;
 }
 
+// GM_LATTICE_TMA=0 stages every chunk with per-thread copies (for comparing the two staging paths)
+bool tma_disabled() {
+  static const bool off = [] {
+    const char* v = getenv("GM_LATTICE_TMA");
+    return v && v[0] == '0';
+  }();
+  return off;
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link against the driver library)
+PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &res) != cudaSuccess || res != cudaDriverEntryPointSuccess)
+      sym = nullptr;
+    return reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(sym);
+  }();
+  return fn;
+}
+
+// Tensor map over one bf16 field seen as (D columns, nlon longitudes, batch * rows): boxes of `box_cols` columns x TC_SC
+// longitudes of one lattice row, written to shared memory in the swizzle that spans the box's rows.
+bool encode_field_map(CUtensorMap* map, const void* field, int D, int nlon, int64_t slabs, int box_cols) {
+  auto encode = tensor_map_encoder();
+  if (!encode) return false;
+  const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)nlon, (cuuint64_t)slabs};
+  const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)nlon * D * 2};
+  const cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)TC_SC, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUtensorMapSwizzle swz = box_cols == 16 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B;
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(field), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int KS0, int NCF, int KSC, int MODE>
 int launch_tc(TcArgs& a, int n_order_rows, int64_t batch, cudaStream_t stream) {
-  constexpr int KQ = KS0 + NCF * KSC, CH = 2 * KQ, PITCH = (CH % 2 == 0 ? CH + 1 : CH) * 8;
-  int SC = 80;  // 64 owners + a window of up to 17 fit one chunk; wider windows take several
-  if (SC > ((a.nlon + TC_TL + 15) / 16) * 16) SC = ((a.nlon + TC_TL + 15) / 16) * 16;
-  a.SC = SC;
-  const size_t buf = (size_t)SC * PITCH * 2 * 2 + (size_t)(SC + TC_TL) * 32 + (MODE == TC_BWD_S ? (size_t)SC * 8 : 0);
-  const size_t smem = 2 * buf;
+  using L = TcLayout<KS0, NCF, KSC>;
+  // TMA staging needs blocks of exactly 16 / 16 KSC columns starting on 16-byte boundaries, rows of a multiple of 16 bytes,
+  // and at least one chunk of longitudes; everything else is staged by the threads.
+  bool tma = !tma_disabled() && a.D % 8 == 0 && a.nlon >= TC_SC && batch * a.rows < (1ll << 31) && (KS0 == 0 || (a.plan.a0 == 16 && a.plan.real_off % 8 == 0)) &&
+             2 * a.plan.ac == 16 * KSC && reinterpret_cast<uintptr_t>(a.nb1) % 16 == 0 && reinterpret_cast<uintptr_t>(a.nb2) % 16 == 0;
+  for (int f = 0; f < a.plan.n_cf; ++f) tma = tma && a.plan.cf_off[f] % 8 == 0;
+  if (tma) {
+    const void* fields[2] = {a.nb1, a.nb2};
+    for (int x = 0; x < 2 && tma; ++x) {
+      if (KS0 > 0) tma = tma && encode_field_map(&a.maps[x][0], fields[x], a.D, a.nlon, batch * a.rows, 16);
+      tma = tma && encode_field_map(&a.maps[x][1], fields[x], a.D, a.nlon, batch * a.rows, 16 * KSC);
+    }
+  }
+  a.use_tma = tma ? 1 : 0;
+  const size_t smem = 2 * (size_t)L::BUFFER_BYTES + 1024;
   auto kernel = lattice_tc_kernel<KS0, NCF, KSC, MODE>;
   int st = allow_smem(kernel, smem, "gm_lattice_attention (tensor cores)");
   if (st != GM_OK) return st;
