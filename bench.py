@@ -56,6 +56,8 @@ def parse() -> argparse.Namespace:
                         "against its own interface bytes and prints one JSON object")
     p.add_argument("--kernel", choices=["lattice", "csr"], default="lattice",
                    help="lattice: compact-table fast path (default); csr: general per-edge-table kernels")
+    p.add_argument("--radius-rows", type=float, default=None,
+                   help="neighbourhood radius in lattice row spacings (default: the workload's own, 3); other values are for profiling")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
     return p.parse_args()
@@ -597,7 +599,9 @@ def main() -> None:
     if args.workload == "ops":
         run_ops(args)
         return
-    cfg = {"headline": HEADLINE, "mid": MID, "small": SMALL}[args.workload]
+    cfg = dict({"headline": HEADLINE, "mid": MID, "small": SMALL}[args.workload])
+    if args.radius_rows is not None:
+        cfg["radius_rows"] = args.radius_rows
     if args.impl == "reference":
         run_reference(args, cfg)
     else:

@@ -654,6 +654,601 @@ __global__ void __launch_bounds__(TC_THREADS, MODE == TC_BWD_S ? 2 : 3) lattice_
     }
 }
 
+// =====================================================================================================================
+// Owner-minor orientation.  The same layer with the roles of the two MMA dimensions exchanged: the staged neighbour
+// positions are the M dimension (16 per step) and a warp's owners the N dimension (8 per warp):
+//
+//   S^T   (16 positions x 8 owners)  = tile (positions x columns) * owners^T      A from shared memory, B loop-invariant registers
+//   out^T (16 columns   x 8 owners) += tile^T (columns x positions) * (P o tau)^T  A from shared memory (ldmatrix.trans), B = P^T
+//
+// * 8 owners see a window of 7 + cnt positions, so the narrow equatorial windows (cnt <= 9) take ONE step of 16
+//   positions instead of the two a 16-owner warp needs: ~1.5 x fewer computed pairs where most rows are.
+// * The imaginary Gram part uses a pre-swapped copy of the OWNERS' fragments (made once), not a per-step swap of the tile.
+// * The phase's imaginary part accumulates into a second accumulator set; the multiplication by i (the pair swap) is
+//   applied once in the epilogue, so the value tile is never swapped.
+// * Accumulators cover 8 owners: half the registers of the owner-major kernel, twice the warps per CTA.
+// * P (accumulator layout: position rows, owner columns) becomes a B operand with movmatrix (8 x 8 b16 transpose).
+// The result tile is transposed through shared memory for 16-byte stores.
+constexpr int TN_WARPS(int mode) { return 8; }
+constexpr int TN_ADV = 80;           // positions a chunk advances by
+constexpr int TN_ROWS = TN_ADV + 8;  // positions staged per chunk: a step of 16 may start 8 before the chunk's end
+
+template <int KS0, int NCF, int KSC, int TL>
+struct TnLayout {
+  static constexpr __host__ __device__ int align1k(int x) { return (x + 1023) / 1024 * 1024; }
+  static constexpr int REAL_PITCH = 32, CX_PITCH = 32 * KSC;
+  static constexpr int REAL_BYTES = KS0 ? align1k(TN_ROWS * REAL_PITCH) : 0;
+  static constexpr int CX_BYTES = align1k(TN_ROWS * CX_PITCH);
+  static constexpr int FIELD_BYTES = REAL_BYTES + NCF * CX_BYTES;
+  static constexpr int ENT_BYTES = (TN_ROWS + TL) * 32;
+  static constexpr int BUFFER_BYTES = align1k(2 * FIELD_BYTES + ENT_BYTES + TN_ROWS * 8);  // with the (lse, Delta) pairs of pass S
+  static constexpr int OUT_PITCH = 16 * (KS0 + NCF * KSC) + 8;  // result tile (owners x padded columns), bf16 elements per row
+  static __device__ __forceinline__ int real_chunk(int r, int cb) { return r * REAL_PITCH + 16 * (cb ^ ((r >> 2) & 1)); }
+  static __device__ __forceinline__ int cx_chunk(int f, int r, int cb) {
+    return REAL_BYTES + f * CX_BYTES + r * CX_PITCH + 16 * (cb ^ (KSC == 2 ? (r >> 1) & 3 : (r >> 2) & 1));
+  }
+  static __device__ __forceinline__ int chunk(int r, int ch) {
+    if (ch < 2 * KS0) return real_chunk(r, ch);
+    const int cc = ch - 2 * KS0;
+    return cx_chunk(cc / (2 * KSC), r, cc % (2 * KSC));
+  }
+};
+
+__device__ __forceinline__ unsigned movmatrix_trans(unsigned x) {
+  unsigned y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(y) : "r"(x));
+  return y;
+}
+__device__ __forceinline__ void mma_bf16_b2(float (&d)[4], const unsigned (&a)[4], const unsigned (&b)[2]) { mma_bf16(d, a, b[0], b[1]); }
+
+__device__ __forceinline__ void ldsm_x4_sa(unsigned (&r)[4], unsigned addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans_sa(unsigned (&r)[4], unsigned addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ float fast_exp2(float x) {  // ex2.approx: exp2(-inf) = 0, relative error ~2^-22
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Per-lane byte offsets of the ldmatrix rows inside a sub-tile, for a step starting at staged row 0.  A step starts on
+// a multiple of 8 rows, which leaves the swizzle term of a lane's row unchanged, so a step adds only pl * pitch.
+template <int KS0, int NCF, int KSC, int TL>
+struct TnLaneOffsets {
+  using L = TnLayout<KS0, NCF, KSC, TL>;
+  int g_real, g_cx[KSC];  // Gram A operand: matrices (rows 0-7, k 0-7), (rows 8-15, k 0-7), (rows 0-7, k 8-15), (rows 8-15, k 8-15)
+  int a_real, a_cx[KSC];  // accumulation A operand = tile^T: (cols 0-7, rows 0-7), (cols 8-15, rows 0-7), (cols 0-7, rows 8-15), (cols 8-15, rows 8-15)
+  __device__ __forceinline__ void init(int lane) {
+    const int mi = lane >> 3, rr = lane & 7;
+    g_real = L::real_chunk(8 * (mi & 1) + rr, mi >> 1);
+    a_real = L::real_chunk(8 * (mi >> 1) + rr, mi & 1);
+#pragma unroll
+    for (int sub = 0; sub < KSC; ++sub) {
+      g_cx[sub] = L::cx_chunk(0, 8 * (mi & 1) + rr, 2 * sub + (mi >> 1));
+      a_cx[sub] = L::cx_chunk(0, 8 * (mi >> 1) + rr, 2 * sub + (mi & 1));
+    }
+  }
+};
+
+// S^T blocks of 16 staged rows (pl .. pl + 15) x 8 owners: g0 (scalar block), gr / gi per complex frequency.
+// fb: the owners' fragments, fs: their pre-swapped copies for the imaginary part (complex k-steps only).
+// tile: shared-memory address of the staged field.
+template <int KS0, int NCF, int KSC, int TL>
+__device__ __forceinline__ void gram_step(const unsigned (&fb)[KS0 + NCF * KSC][2], const unsigned (&fs)[NCF * KSC > 0 ? NCF * KSC : 1][2],
+                                          unsigned tile, int pl, const TnLaneOffsets<KS0, NCF, KSC, TL>& lo, float (&g0)[4],
+                                          float (&gr)[NCF > 0 ? NCF : 1][4], float (&gi)[NCF > 0 ? NCF : 1][4]) {
+  using L = TnLayout<KS0, NCF, KSC, TL>;
+#pragma unroll
+  for (int x = 0; x < 4; ++x) {
+    g0[x] = 0.f;
+#pragma unroll
+    for (int f = 0; f < NCF; ++f) gr[f][x] = gi[f][x] = 0.f;
+  }
+  if constexpr (KS0 > 0) {
+    unsigned af[4];
+    ldsm_x4_sa(af, tile + pl * L::REAL_PITCH + lo.g_real);
+    mma_bf16_b2(g0, af, fb[0]);
+  }
+  const unsigned cx = tile + pl * L::CX_PITCH;
+#pragma unroll
+  for (int f = 0; f < NCF; ++f)
+#pragma unroll
+    for (int sub = 0; sub < KSC; ++sub) {
+      unsigned af[4];
+      ldsm_x4_sa(af, cx + lo.g_cx[sub] + f * L::CX_BYTES);
+      mma_bf16_b2(gr[f], af, fb[KS0 + f * KSC + sub]);
+      mma_bf16_b2(gi[f], af, fs[f * KSC + sub]);
+    }
+}
+
+// acc^T (padded head columns x 8 owners) += tile^T (columns x 16 staged rows pl .. pl + 15) * B, B = x0 for the scalar block,
+// xr[f] into the real-phase accumulators and xi[f] into the imaginary-phase accumulators of frequency f.
+template <int KS0, int NCF, int KSC, int TL>
+__device__ __forceinline__ void accumulate_step(float (&acc0)[4], float (&accr)[NCF * KSC > 0 ? NCF * KSC : 1][4], float (&acci)[NCF * KSC > 0 ? NCF * KSC : 1][4],
+                                                const unsigned (&x0)[2], const unsigned (&xr)[NCF > 0 ? NCF : 1][2], const unsigned (&xi)[NCF > 0 ? NCF : 1][2],
+                                                unsigned tile, int pl, const TnLaneOffsets<KS0, NCF, KSC, TL>& lo) {
+  using L = TnLayout<KS0, NCF, KSC, TL>;
+  if constexpr (KS0 > 0) {
+    unsigned af[4];
+    ldsm_x4_trans_sa(af, tile + pl * L::REAL_PITCH + lo.a_real);
+    mma_bf16_b2(acc0, af, x0);
+  }
+  const unsigned cx = tile + pl * L::CX_PITCH;
+#pragma unroll
+  for (int f = 0; f < NCF; ++f)
+#pragma unroll
+    for (int sub = 0; sub < KSC; ++sub) {
+      unsigned af[4];
+      ldsm_x4_trans_sa(af, cx + lo.a_cx[sub] + f * L::CX_BYTES);
+      mma_bf16_b2(accr[f * KSC + sub], af, xr[f]);
+      mma_bf16_b2(acci[f * KSC + sub], af, xi[f]);
+    }
+}
+
+// Flat column of the pair of padded head-local columns (col, col + 1) of k-step / m-tile `kt` (compile-time), col even in
+// 0 .. 14: first = flat column or -1 (padding), second likewise.  No division: the block is known at compile time.
+template <int KS0, int NCF, int KSC, int KT>
+__device__ __forceinline__ void flat_pair(const TcPlan& P, int h, int col, int& g0, int& g1) {
+  if constexpr (KT < KS0) {
+    const int cc = 16 * KT + col;
+    g0 = cc < P.a0 ? P.real_off + h * P.a0 + cc : -1;
+    g1 = cc + 1 < P.a0 ? P.real_off + h * P.a0 + cc + 1 : -1;
+  } else {
+    constexpr int F = (KT - KS0) / KSC, SUB = (KT - KS0) % KSC;
+    const int cc = 16 * SUB + col;
+    g0 = cc < 2 * P.ac ? P.cf_off[F] + 2 * h * P.ac + cc : -1;
+    g1 = g0 >= 0 ? g0 + 1 : -1;  // 2 ac is even: a (re, im) pair is never split
+  }
+}
+
+// B-operand fragments of one owner (column n = g of the warp's 8) for every k-step of the padded head layout
+template <int KS0, int NCF, int KSC, int KT = 0>
+__device__ __forceinline__ void load_owner_columns(const TcPlan& P, const __nv_bfloat16* src, bool present, bool words, int h, int c,
+                                                   unsigned (&fb)[KS0 + NCF * KSC][2]) {
+  if constexpr (KT < KS0 + NCF * KSC) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      int g0, g1;
+      flat_pair<KS0, NCF, KSC, KT>(P, h, 2 * c + 8 * r, g0, g1);
+      unsigned w = 0u;
+      if (present) {
+        if (words && g0 >= 0 && g1 == g0 + 1 && (g0 & 1) == 0) {
+          w = *reinterpret_cast<const unsigned*>(src + g0);
+        } else {
+          if (g0 >= 0) w = __bfloat16_as_ushort(src[g0]);
+          if (g1 >= 0) w |= (unsigned)__bfloat16_as_ushort(src[g1]) << 16;
+        }
+      }
+      fb[KT][r] = w;
+    }
+    load_owner_columns<KS0, NCF, KSC, KT + 1>(P, src, present, words, h, c, fb);
+  }
+}
+
+// One m-tile (16 head columns x 8 owners, accumulator layout) of a result -> global memory: transposed in registers
+// (movmatrix) so that a thread holds two adjacent columns of ONE owner (own_b): 4-byte stores.
+template <int KS0, int NCF, int KSC, int KT>
+__device__ __forceinline__ void store_tile(const TcPlan& P, __nv_bfloat16* dst, bool present, bool words, int h, int c, const float (&v)[4]) {
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const unsigned w = movmatrix_trans(pack_bf16(v[2 * r], v[2 * r + 1]));  // (owner own_b; columns 2c + 8r, 2c + 8r + 1)
+    int g0, g1;
+    flat_pair<KS0, NCF, KSC, KT>(P, h, 2 * c + 8 * r, g0, g1);
+    if (!present) continue;
+    if (words && g0 >= 0 && g1 == g0 + 1 && (g0 & 1) == 0) {
+      *reinterpret_cast<unsigned*>(dst + g0) = w;
+    } else {
+      if (g0 >= 0) dst[g0] = __ushort_as_bfloat16((unsigned short)(w & 0xffffu));
+      if (g1 >= 0) dst[g1] = __ushort_as_bfloat16((unsigned short)(w >> 16));
+    }
+  }
+}
+
+// combine the phase accumulators of every complex m-tile and store all m-tiles of one result
+template <int KS0, int NCF, int KSC, bool CONJ, int M = 0>
+__device__ __forceinline__ void store_result(const TcPlan& P, __nv_bfloat16* dst, bool present, bool words, int h, int g, int c, const float (&inv)[2],
+                                             const float (&acc0)[4], const float (&accr)[NCF * KSC > 0 ? NCF * KSC : 1][4],
+                                             const float (&acci)[NCF * KSC > 0 ? NCF * KSC : 1][4]) {
+  if constexpr (M == 0 && KS0 > 0) {
+    const float v[4] = {acc0[0] * inv[0], acc0[1] * inv[1], acc0[2] * inv[0], acc0[3] * inv[1]};
+    store_tile<KS0, NCF, KSC, 0>(P, dst, present, words, h, c, v);
+  }
+  if constexpr (M < NCF * KSC) {
+    // rows of an accumulator m-tile are head columns g, g + 8: even = real part, odd = imaginary part.
+    //   tau:      re = r_re - i_im,  im = r_im + i_re;      conj tau:  re = r_re + i_im,  im = r_im - i_re
+    const float sgn = ((g & 1) != 0) == CONJ ? -1.f : 1.f;
+    float v[4];
+#pragma unroll
+    for (int x = 0; x < 4; ++x) v[x] = (accr[M][x] + sgn * __shfl_xor_sync(0xffffffffu, acci[M][x], 4)) * inv[x & 1];
+    store_tile<KS0, NCF, KSC, KS0 + M>(P, dst, present, words, h, c, v);
+    store_result<KS0, NCF, KSC, CONJ, M + 1>(P, dst, present, words, h, g, c, inv, acc0, accr, acci);
+  }
+}
+
+// A neighbour row of the owner row's walk, prepared once per CTA
+struct TnRowPair {
+  int cnt, lo, z, lon_base;  // window width, first offset, sample * rows + neighbour row, longitude of position 0 (wrapped)
+  int ent_off, pad0, pad1, pad2;
+};
+
+template <int KS0, int NCF, int KSC, int MODE, int WARPS>
+__global__ void __launch_bounds__(32 * WARPS, MODE == TC_BWD_S ? 1 : 2) lattice_tn_kernel(const __grid_constant__ TcArgs a) {
+  constexpr int TL = 8 * WARPS, THREADS = 32 * WARPS;
+  using L = TnLayout<KS0, NCF, KSC, TL>;
+  constexpr int KQ = KS0 + NCF * KSC, CH = 2 * KQ, NCK = NCF * KSC > 0 ? NCF * KSC : 1;
+  constexpr int NF = NCF > 0 ? NCF : 1;
+  constexpr bool FWD = MODE == TC_FWD, PASS_S = MODE == TC_BWD_S;
+  extern __shared__ __align__(1024) unsigned char smem_dyn[];
+  // swizzled sub-tiles must start on 1024-byte boundaries of the shared-memory window: align by hand (1 KB of slack is requested)
+  unsigned char* const smem_raw = smem_dyn + ((1024u - ((unsigned)__cvta_generic_to_shared(smem_dyn) & 1023u)) & 1023u);
+  __shared__ __align__(8) unsigned long long copy_bar[2];  // completion of the TMA copies into buffer 0 / 1
+  __shared__ __align__(16) TnRowPair pairs_s[TC_MAX_WIN];
+  __shared__ int n_pairs_s;
+  const TcPlan& P = a.plan;
+  // two buffers, each: field 1 sub-tiles | field 2 sub-tiles | entries (TN_ROWS + TL, 8) fp32 | stats (TN_ROWS, 2) fp32 (pass S)
+  constexpr int buf_bytes = L::BUFFER_BYTES;
+  auto tile1 = [&](int buf) { return smem_raw + buf * buf_bytes; };
+  auto tile2 = [&](int buf) { return smem_raw + buf * buf_bytes + L::FIELD_BYTES; };
+  auto entry = [&](int buf) { return reinterpret_cast<float*>(smem_raw + buf * buf_bytes + 2 * L::FIELD_BYTES); };
+  auto stats = [&](int buf) { return reinterpret_cast<float*>(smem_raw + buf * buf_bytes + 2 * L::FIELD_BYTES + L::ENT_BYTES); };
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, c = lane & 3;
+  const int tiles = (a.nlon + TL - 1) / TL;
+  const int row = a.row_order[blockIdx.x / tiles];
+  const int c0 = (blockIdx.x % tiles) * TL;
+  const int h = blockIdx.y;
+  const int64_t b = blockIdx.z;
+  const int64_t node0 = (b * a.rows + row) * (int64_t)a.nlon;
+  const int own_b = 8 * warp + g;      // the owner whose column this thread holds in B fragments (and stores in the epilogue)
+  const int own_c = 8 * warp + 2 * c;  // the owners (own_c, own_c + 1) of this thread's accumulator columns
+  const float cscale = a.scale * TC_LOG2E;
+  const bool words = (a.D & 1) == 0;   // 4-byte accesses to (even column, next column) are aligned
+  TnLaneOffsets<KS0, NCF, KSC, TL> lane_off;
+  lane_off.init(lane);
+
+  // ---- the walk's row pairs, once per CTA: warp 0 compacts the non-empty ones (one lane per neighbour row)
+  if (warp == 0) {
+    int filled = 0;
+    for (int x0 = 0; x0 < 2 * a.W + 1; x0 += 32) {
+      const int x = x0 + lane, j = row + x - a.W;
+      int cnt = 0;
+      if (x < 2 * a.W + 1 && j >= 0 && j < a.rows) cnt = a.win_cnt[row * (2 * a.W + 1) + x];
+      const unsigned have = __ballot_sync(0xffffffffu, cnt > 0);
+      if (cnt > 0) {
+        const int widx = row * (2 * a.W + 1) + x;
+        TnRowPair rp;
+        rp.cnt = cnt;
+        rp.lo = a.win_lo[widx];
+        rp.z = (int)(b * a.rows + j);
+        rp.lon_base = tc_wrap(c0 + rp.lo, a.nlon);
+        rp.ent_off = a.win_off[widx];
+        rp.pad0 = rp.pad1 = rp.pad2 = 0;
+        pairs_s[filled + __popc(have & ((1u << lane) - 1u))] = rp;
+      }
+      filled += __popc(have);
+    }
+    if (lane == 0) n_pairs_s = filled;
+  }
+  if (!a.use_tma)  // per-thread staging leaves rows beyond a window and padding columns untouched: they must be finite
+    for (int x = threadIdx.x; x < 2 * buf_bytes / 16; x += THREADS) reinterpret_cast<uint4*>(smem_raw)[x] = make_uint4(0, 0, 0, 0);
+  if (threadIdx.x == 0) {
+    mbar_init(&copy_bar[0], 1);
+    mbar_init(&copy_bar[1], 1);
+    fence_mbar_init();
+  }
+
+  // owners' fragments (loop-invariant B operands) and their pre-swapped copies:
+  //   owners carry q: Im = sum_cols tile[col] * q'[col], q' = (-q_im, q_re);   owners carry k: k' = (k_im, -k_re)
+  unsigned f1[KQ][2], s1[NCK][2], f2[FWD ? 1 : KQ][2], s2[FWD ? 1 : NCK][2];
+  const bool own_b_present = c0 + own_b < a.nlon;
+  const int64_t own_b_base = (node0 + c0 + own_b) * a.D;
+  load_owner_columns<KS0, NCF, KSC>(P, a.own1 + own_b_base, own_b_present, words, h, c, f1);
+#pragma unroll
+  for (int kc = 0; kc < NCF * KSC; ++kc)
+#pragma unroll
+    for (int r = 0; r < 2; ++r) s1[kc][r] = PASS_S ? swap_neg(f1[KS0 + kc][r]) : swap_neg_lo(f1[KS0 + kc][r]);
+  if constexpr (!FWD) {
+    load_owner_columns<KS0, NCF, KSC>(P, a.own2 + own_b_base, own_b_present, words, h, c, f2);
+#pragma unroll
+    for (int kc = 0; kc < NCF * KSC; ++kc)
+#pragma unroll
+      for (int r = 0; r < 2; ++r) s2[kc][r] = PASS_S ? swap_neg(f2[KS0 + kc][r]) : swap_neg_lo(f2[KS0 + kc][r]);
+  }
+  float lse_o[2] = {0.f, 0.f}, dl_o[2] = {0.f, 0.f};  // pass T: the two accumulator-column owners' lse (base 2) and Delta
+  if (MODE == TC_BWD_T) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e)
+      if (c0 + own_c + e < a.nlon) {
+        lse_o[e] = a.lse[(node0 + c0 + own_c + e) * a.H + h] * TC_LOG2E;
+        dl_o[e] = a.delta[(node0 + c0 + own_c + e) * a.H + h];
+      }
+  }
+  float a1_0[4] = {0.f, 0.f, 0.f, 0.f}, a1_r[NCK][4], a1_i[NCK][4];
+  float a2_0[4] = {0.f, 0.f, 0.f, 0.f}, a2_r[PASS_S ? NCK : 1][4], a2_i[PASS_S ? NCK : 1][4];
+#pragma unroll
+  for (int m = 0; m < NCK; ++m)
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      a1_r[m][x] = a1_i[m][x] = 0.f;
+      if constexpr (PASS_S) a2_r[m][x] = a2_i[m][x] = 0.f;
+    }
+  float m_o[2] = {-1e30f, -1e30f}, l_o[2] = {0.f, 0.f};  // forward: reference maximum (base-2 logits), partial sums of the two owners
+  __syncthreads();
+  const int n_pairs = n_pairs_s;
+
+  // ---- stages = (row pair, chunk of its window), produced in order
+  struct Stage {
+    int ip, p0;       // row pair, first position of the chunk
+    int cnt, n_rows;  // window width, staged positions
+    int lon0;         // longitude of the chunk's first position (wrapped)
+    bool tma;         // consecutive longitudes (no wrap at the seam) and tensor maps available
+  };
+  auto load_stage = [&](Stage& s) {
+    const TnRowPair& rp = pairs_s[s.ip];
+    s.cnt = rp.cnt;
+    s.n_rows = min(TN_ROWS, TL + rp.cnt - 1 - s.p0);
+    int lon0 = rp.lon_base + s.p0;
+    if (lon0 >= a.nlon) lon0 %= a.nlon;
+    s.lon0 = lon0;
+    s.tma = a.use_tma && lon0 + s.n_rows <= a.nlon;
+  };
+  auto advance = [&](Stage& s) -> bool {
+    if (s.p0 + TN_ADV < TL + s.cnt - 1) {
+      s.p0 += TN_ADV;
+    } else {
+      if (++s.ip >= n_pairs) return false;
+      s.p0 = 0;
+    }
+    load_stage(s);
+    return true;
+  };
+  // per-thread staging slots of the cp.async path: thread -> (row within a pass, 16-byte chunk); the chunk's flat column is fixed
+  constexpr int ROWS_PER_PASS = THREADS / CH;
+  const int st_row = threadIdx.x / CH, st_ch = threadIdx.x - st_row * CH;
+  const int st_g0 = flat_column<KS0, NCF, KSC>(P, h, 8 * st_ch), st_g7 = flat_column<KS0, NCF, KSC>(P, h, 8 * st_ch + 7);
+  const bool st_active = st_row < ROWS_PER_PASS;
+  const bool st_whole = st_g0 >= 0 && st_g7 == st_g0 + 7 && (a.D % 8 == 0) && (st_g0 % 8 == 0);  // one aligned 16-byte chunk of real columns
+  const bool st_pad = st_g0 < 0 && st_g7 < 0 && flat_column<KS0, NCF, KSC>(P, h, 8 * st_ch + 3) < 0;  // all padding (stays zero)
+  auto issue = [&](const Stage& s, int buf) {  // asynchronous copies of one stage into buffer `buf`
+    const TnRowPair& rp = pairs_s[s.ip];
+    unsigned char* d1 = tile1(buf);
+    unsigned char* d2 = tile2(buf);
+    if (s.tma) {
+      if (threadIdx.x == 0) {
+        // the buffer was last touched through the generic proxy (ldmatrix, per-thread stores): order those first
+        fence_proxy_async();
+        mbar_expect_tx(&copy_bar[buf], 2u * TN_ROWS * (KS0 * L::REAL_PITCH + NCF * L::CX_PITCH));
+        if constexpr (KS0 > 0) {
+          tma_load_3d(d1, &a.maps[0][0], &copy_bar[buf], P.real_off + h * 16, s.lon0, rp.z);
+          tma_load_3d(d2, &a.maps[1][0], &copy_bar[buf], P.real_off + h * 16, s.lon0, rp.z);
+        }
+#pragma unroll
+        for (int f = 0; f < NCF; ++f) {
+          tma_load_3d(d1 + L::REAL_BYTES + f * L::CX_BYTES, &a.maps[0][1], &copy_bar[buf], P.cf_off[f] + h * 16 * KSC, s.lon0, rp.z);
+          tma_load_3d(d2 + L::REAL_BYTES + f * L::CX_BYTES, &a.maps[1][1], &copy_bar[buf], P.cf_off[f] + h * 16 * KSC, s.lon0, rp.z);
+        }
+      }
+    } else if (st_active && !st_pad) {
+      int lon = s.lon0 + st_row;
+      if (lon >= a.nlon) lon %= a.nlon;
+      const int step = ROWS_PER_PASS % a.nlon;
+      // with tensor maps in use the buffer may hold anything beyond the window: write zeros there (copies of size 0)
+      const int rows_to_write = a.use_tma ? TN_ROWS : s.n_rows;
+      for (int pl = st_row; pl < rows_to_write; pl += ROWS_PER_PASS) {
+        const int64_t nb = ((int64_t)rp.z * a.nlon + lon) * a.D;
+        const int off = L::chunk(pl, st_ch);
+        if (st_whole) {
+          const int bytes = pl < s.n_rows ? 16 : 0;
+          cp_async16(d1 + off, a.nb1 + nb + st_g0, bytes);
+          cp_async16(d2 + off, a.nb2 + nb + st_g0, bytes);
+        } else {  // a chunk that straddles padding or is misaligned: element by element (visible after the barrier)
+          unsigned short u1[8], u2[8];
+#pragma unroll
+          for (int x = 0; x < 8; ++x) {
+            const int gx = pl < s.n_rows ? flat_column<KS0, NCF, KSC>(P, h, 8 * st_ch + x) : -1;
+            u1[x] = gx >= 0 ? __bfloat16_as_ushort(a.nb1[nb + gx]) : (unsigned short)0;
+            u2[x] = gx >= 0 ? __bfloat16_as_ushort(a.nb2[nb + gx]) : (unsigned short)0;
+          }
+          *reinterpret_cast<uint4*>(d1 + off) =
+              make_uint4(u1[0] | (u1[1] << 16), u1[2] | (u1[3] << 16), u1[4] | (u1[5] << 16), u1[6] | (u1[7] << 16));
+          *reinterpret_cast<uint4*>(d2 + off) =
+              make_uint4(u2[0] | (u2[1] << 16), u2[2] | (u2[3] << 16), u2[4] | (u2[5] << 16), u2[6] | (u2[7] << 16));
+        }
+        lon += step;
+        if (lon >= a.nlon) lon -= a.nlon;
+      }
+    }
+    // table entries of the offsets x = p - owner the chunk can meet (clamped: validity is decided from x itself)
+    float* de = entry(buf);
+    const float* ent = a.entries + (size_t)rp.ent_off * 8;
+    for (int idx = threadIdx.x; idx < 2 * (s.n_rows + TL - 1); idx += THREADS) {
+      const int xi = idx >> 1, part = idx & 1;
+      const int x = min(max(xi + s.p0 - (TL - 1), 0), s.cnt - 1);
+      cp_async16(de + 8 * xi + 4 * part, ent + 8 * x + 4 * part, 16);
+    }
+    if constexpr (PASS_S) {
+      float* ds = stats(buf);
+      for (int idx = threadIdx.x; idx < 2 * s.n_rows; idx += THREADS) {
+        const int pl = idx >> 1, which = idx & 1;
+        int lon = s.lon0 + pl;
+        if (lon >= a.nlon) lon %= a.nlon;
+        const int64_t nn = ((int64_t)rp.z * a.nlon + lon) * a.H + h;
+        cp_async4(ds + 2 * pl + which, (which ? a.delta : a.lse) + nn, 4);
+      }
+    }
+    cp_async_commit();
+  };
+
+  Stage cur;
+  cur.ip = 0; cur.p0 = 0;
+  bool have = n_pairs > 0;
+  int buf = 0;
+  unsigned parity = 0;  // bit b: the phase of copy_bar[b] the next TMA stage into buffer b completes
+  if (have) {
+    load_stage(cur);
+    issue(cur, 0);
+  }
+  while (have) {
+    Stage nxt = cur;
+    const bool have_next = advance(nxt);
+    if (have_next) {
+      issue(nxt, buf ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    if (cur.tma) {
+      mbar_wait(&copy_bar[buf], (parity >> buf) & 1u);
+      parity ^= 1u << buf;
+    }
+    __syncthreads();
+    const unsigned t1 = (unsigned)__cvta_generic_to_shared(tile1(buf));
+    const unsigned t2 = (unsigned)__cvta_generic_to_shared(tile2(buf));
+    const float* e_s = entry(buf);
+    const float* stat_s = stats(buf);
+    const int p0 = cur.p0, cnt = cur.cnt;
+
+    // ---- this warp's steps inside the chunk: 16 positions each, on the lattice 8 warp + 16 i
+    const int p_first = p0 > 8 * warp ? p0 + ((8 * warp) & 8) : 8 * warp;
+    const int p_end = min(p0 + TN_ADV, 8 * warp + 7 + cnt);
+    for (int p = p_first; p < p_end; p += 16) {
+      const int pl = p - p0;
+      float s0[4], sr[NF][4], si[NF][4], h0[4], hr[NF][4], hi[NF][4];
+      gram_step<KS0, NCF, KSC, TL>(f1, s1, t1, pl, lane_off, s0, sr, si);
+      if constexpr (!FWD) gram_step<KS0, NCF, KSC, TL>(f2, s2, t2, pl, lane_off, h0, hr, hi);
+      // element x of a fragment: position pl + g + 8 (x >> 1), owner own_c + (x & 1)
+      float lg[4], tr[NF][4], ti[NF][4], dal[4];
+      bool valid[4];
+      const float* e_lane = e_s + 8 * (pl + g - own_c + (TL - 1));  // staged entry of the offset p - owner, element 0
+      const int off0 = p0 + pl + g - own_c;
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        const float* e = e_lane + 8 * (8 * (x >> 1) - (x & 1));
+        valid[x] = (unsigned)(off0 + 8 * (x >> 1) - (x & 1)) < (unsigned)cnt;
+        float sum = s0[x];
+        dal[x] = FWD ? 0.f : h0[x];
+        float tau[2 * NF];
+        if constexpr (NCF >= 2) {  // complex frequencies are the orders 1 .. NCF: the first two phases are the entry's first 16 bytes
+          const float4 t = *reinterpret_cast<const float4*>(e);
+          tau[0] = t.x; tau[1] = t.y; tau[2] = t.z; tau[3] = t.w;
+          if constexpr (NCF == 3) {
+            const float2 t3 = *reinterpret_cast<const float2*>(e + 4);
+            tau[4] = t3.x; tau[5] = t3.y;
+          }
+        } else if constexpr (NCF == 1) {
+          const float2 t = *reinterpret_cast<const float2*>(e);
+          tau[0] = t.x; tau[1] = t.y;
+        }
+#pragma unroll
+        for (int f = 0; f < NCF; ++f) {
+          tr[f][x] = tau[2 * f];
+          ti[f][x] = tau[2 * f + 1];
+          sum = fmaf(tau[2 * f], sr[f][x], sum);
+          sum = fmaf(-tau[2 * f + 1], si[f][x], sum);
+          if constexpr (!FWD) {
+            dal[x] = fmaf(tau[2 * f], hr[f][x], dal[x]);
+            dal[x] = fmaf(-tau[2 * f + 1], hi[f][x], dal[x]);
+          }
+        }
+        lg[x] = valid[x] ? fmaf(cscale, sum, TC_LOG2E * e[2 * a.NORD]) : -INFINITY;  // -inf: outside the window
+      }
+      float w1[4], w2[4];  // the weights the two accumulations use: forward p | pass T ds | pass S ds, p
+      if constexpr (FWD) {
+        // online softmax over the 16 positions: column maxima over this thread's rows, then across the 8 row groups.
+        // The reference maximum of an owner only moves when the new maximum exceeds it by more than 2^8 (weights stay
+        // below 256: exact in the normalised result), so most steps skip the rescaling of the accumulators.
+        float mx[2] = {fmaxf(lg[0], lg[2]), fmaxf(lg[1], lg[3])};
+#pragma unroll
+        for (int d = 4; d < 32; d <<= 1) {
+          mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], d));
+          mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], d));
+        }
+        if (__any_sync(0xffffffffu, mx[0] > m_o[0] + 8.f || mx[1] > m_o[1] + 8.f)) {
+          const float nm[2] = {mx[0] > m_o[0] + 8.f ? mx[0] : m_o[0], mx[1] > m_o[1] + 8.f ? mx[1] : m_o[1]};
+          const float corr[2] = {fast_exp2(m_o[0] - nm[0]), fast_exp2(m_o[1] - nm[1])};
+          m_o[0] = nm[0]; m_o[1] = nm[1];
+          l_o[0] *= corr[0]; l_o[1] *= corr[1];
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            a1_0[x] *= corr[x & 1];
+#pragma unroll
+            for (int m = 0; m < NCF * KSC; ++m) { a1_r[m][x] *= corr[x & 1]; a1_i[m][x] *= corr[x & 1]; }
+          }
+        }
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          w1[x] = fast_exp2(lg[x] - m_o[x & 1]);
+          l_o[x & 1] += w1[x];
+        }
+      } else {
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          float lse, delta;
+          if (PASS_S) {
+            const float2 st = *reinterpret_cast<const float2*>(stat_s + 2 * (pl + g + 8 * (x >> 1)));
+            lse = st.x * TC_LOG2E; delta = st.y;
+          } else {
+            lse = lse_o[x & 1]; delta = dl_o[x & 1];
+          }
+          const float pr = valid[x] ? fast_exp2(lg[x] - lse) : 0.f;
+          w1[x] = a.scale * pr * (dal[x] - delta);
+          w2[x] = pr;
+        }
+      }
+      // B operands: the weights (x phase parts), transposed to (owner column, position rows)
+      unsigned x0[2], xr[NF][2], xim[NF][2];
+      x0[0] = movmatrix_trans(pack_bf16(w1[0], w1[1]));
+      x0[1] = movmatrix_trans(pack_bf16(w1[2], w1[3]));
+#pragma unroll
+      for (int f = 0; f < NCF; ++f) {
+        xr[f][0] = movmatrix_trans(pack_bf16(w1[0] * tr[f][0], w1[1] * tr[f][1]));
+        xr[f][1] = movmatrix_trans(pack_bf16(w1[2] * tr[f][2], w1[3] * tr[f][3]));
+        xim[f][0] = movmatrix_trans(pack_bf16(w1[0] * ti[f][0], w1[1] * ti[f][1]));
+        xim[f][1] = movmatrix_trans(pack_bf16(w1[2] * ti[f][2], w1[3] * ti[f][3]));
+      }
+      if constexpr (FWD) {
+        accumulate_step<KS0, NCF, KSC, TL>(a1_0, a1_r, a1_i, x0, xr, xim, t2, pl, lane_off);  // out += (p tau) v
+      } else {
+        accumulate_step<KS0, NCF, KSC, TL>(a1_0, a1_r, a1_i, x0, xr, xim, t1, pl, lane_off);  // dq += (ds tau) k  |  dk += (ds conj tau) q
+        if constexpr (PASS_S) {
+          x0[0] = movmatrix_trans(pack_bf16(w2[0], w2[1]));
+          x0[1] = movmatrix_trans(pack_bf16(w2[2], w2[3]));
+#pragma unroll
+          for (int f = 0; f < NCF; ++f) {
+            xr[f][0] = movmatrix_trans(pack_bf16(w2[0] * tr[f][0], w2[1] * tr[f][1]));
+            xr[f][1] = movmatrix_trans(pack_bf16(w2[2] * tr[f][2], w2[3] * tr[f][3]));
+            xim[f][0] = movmatrix_trans(pack_bf16(w2[0] * ti[f][0], w2[1] * ti[f][1]));
+            xim[f][1] = movmatrix_trans(pack_bf16(w2[2] * ti[f][2], w2[3] * ti[f][3]));
+          }
+          accumulate_step<KS0, NCF, KSC, TL>(a2_0, a2_r, a2_i, x0, xr, xim, t2, pl, lane_off);  // dv += (p conj tau) dO
+        }
+      }
+    }
+    __syncthreads();  // everyone is done with `buf` before the stage after next is copied into it
+    cur = nxt;
+    have = have_next;
+    buf ^= 1;
+  }
+
+  // ---- epilogue: normalise, combine the two phase accumulators (multiplication by +-i = pair swap across rows g, g ^ 1),
+  // transpose in registers, store
+  float inv[2] = {1.f, 1.f};
+  if constexpr (FWD) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+#pragma unroll
+      for (int d = 4; d < 32; d <<= 1) l_o[e] += __shfl_xor_sync(0xffffffffu, l_o[e], d);
+      inv[e] = l_o[e] > 0.f ? 1.f / l_o[e] : 0.f;
+      if (g == 0 && c0 + own_c + e < a.nlon)
+        a.lse_out[(node0 + c0 + own_c + e) * a.H + h] = l_o[e] > 0.f ? (m_o[e] + log2f(l_o[e])) * TC_LN2 : -INFINITY;
+    }
+  }
+  store_result<KS0, NCF, KSC, PASS_S>(P, a.res1 + own_b_base, own_b_present, words, h, g, c, inv, a1_0, a1_r, a1_i);
+  if constexpr (PASS_S) store_result<KS0, NCF, KSC, true>(P, a.res2 + own_b_base, own_b_present, words, h, g, c, inv, a2_0, a2_r, a2_i);
+}
+
 // Delta[node, h] = <dO, O> over the head's columns
 __global__ void tc_delta_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ out, float* __restrict__ delta,
                                 int64_t n_nodes, int D, int H, TcPlan P) {
@@ -750,14 +1345,14 @@ PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
   return fn;
 }
 
-// Tensor map over one bf16 field seen as (D columns, nlon longitudes, batch * rows): boxes of `box_cols` columns x TC_SC
-// longitudes of one lattice row, written to shared memory in the swizzle that spans the box's rows.
-bool encode_field_map(CUtensorMap* map, const void* field, int D, int nlon, int64_t slabs, int box_cols) {
+// Tensor map over one bf16 field seen as (D columns, nlon longitudes, batch * rows): boxes of `box_cols` columns x `box_rows`
+// (box_rows) longitudes of one lattice row, written to shared memory in the swizzle that spans the box's rows.
+bool encode_field_map(CUtensorMap* map, const void* field, int D, int nlon, int64_t slabs, int box_cols, int box_rows) {
   auto encode = tensor_map_encoder();
   if (!encode) return false;
   const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)nlon, (cuuint64_t)slabs};
   const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)nlon * D * 2};
-  const cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)TC_SC, 1};
+  const cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1};
   const cuuint32_t estr[3] = {1, 1, 1};
   const CUtensorMapSwizzle swz = box_cols == 16 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B;
   return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(field), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
@@ -775,8 +1370,8 @@ int launch_tc(TcArgs& a, int n_order_rows, int64_t batch, cudaStream_t stream) {
   if (tma) {
     const void* fields[2] = {a.nb1, a.nb2};
     for (int x = 0; x < 2 && tma; ++x) {
-      if (KS0 > 0) tma = tma && encode_field_map(&a.maps[x][0], fields[x], a.D, a.nlon, batch * a.rows, 16);
-      tma = tma && encode_field_map(&a.maps[x][1], fields[x], a.D, a.nlon, batch * a.rows, 16 * KSC);
+      if (KS0 > 0) tma = tma && encode_field_map(&a.maps[x][0], fields[x], a.D, a.nlon, batch * a.rows, 16, TC_SC);
+      tma = tma && encode_field_map(&a.maps[x][1], fields[x], a.D, a.nlon, batch * a.rows, 16 * KSC, TC_SC);
     }
   }
   a.use_tma = tma ? 1 : 0;
@@ -790,9 +1385,49 @@ int launch_tc(TcArgs& a, int n_order_rows, int64_t batch, cudaStream_t stream) {
   return launch_status("gm_lattice_attention (tensor cores)");
 }
 
+template <int KS0, int NCF, int KSC, int MODE>
+int launch_tn(TcArgs& a, int n_order_rows, int64_t batch, cudaStream_t stream) {
+  constexpr int WARPS = TN_WARPS(MODE), TL = 8 * WARPS;
+  using L = TnLayout<KS0, NCF, KSC, TL>;
+  bool tma = !tma_disabled() && a.D % 8 == 0 && a.nlon >= TN_ROWS && batch * a.rows < (1ll << 31) && (KS0 == 0 || (a.plan.a0 == 16 && a.plan.real_off % 8 == 0)) &&
+             2 * a.plan.ac == 16 * KSC && reinterpret_cast<uintptr_t>(a.nb1) % 16 == 0 && reinterpret_cast<uintptr_t>(a.nb2) % 16 == 0;
+  for (int f = 0; f < a.plan.n_cf; ++f) tma = tma && a.plan.cf_off[f] % 8 == 0;
+  if (tma) {
+    const void* fields[2] = {a.nb1, a.nb2};
+    for (int x = 0; x < 2 && tma; ++x) {
+      if (KS0 > 0) tma = tma && encode_field_map(&a.maps[x][0], fields[x], a.D, a.nlon, batch * a.rows, 16, TN_ROWS);
+      tma = tma && encode_field_map(&a.maps[x][1], fields[x], a.D, a.nlon, batch * a.rows, 16 * KSC, TN_ROWS);
+    }
+  }
+  a.use_tma = tma ? 1 : 0;
+  const size_t smem = 2 * (size_t)L::BUFFER_BYTES + 1024;
+  auto kernel = lattice_tn_kernel<KS0, NCF, KSC, MODE, WARPS>;
+  int st = allow_smem(kernel, smem, "gm_lattice_attention (tensor cores)");
+  if (st != GM_OK) return st;
+  const int tiles = (a.nlon + TL - 1) / TL;
+  dim3 grid((unsigned)(n_order_rows * tiles), (unsigned)a.H, (unsigned)batch);
+  kernel<<<grid, 32 * WARPS, smem, stream>>>(a);
+  return launch_status("gm_lattice_attention (tensor cores)");
+}
+
+bool legacy_orientation() {
+  const char* v = getenv("GM_LATTICE_TC_OWNER_MAJOR");
+  return v && v[0] == '1';
+}
+
 template <int MODE>
 int dispatch_tc(TcArgs& a, int n_order_rows, int64_t batch, cudaStream_t cs) {
   const int ks0 = a.plan.a0 > 0 ? 1 : 0, ksc = a.plan.ac > 8 ? 2 : 1, ncf = a.plan.n_cf;
+  if (!legacy_orientation()) {
+    for (int f = 0; f < ncf; ++f)
+      GM_REQUIRE(a.plan.cf_order[f] == f + 1, GM_ERR_UNSUPPORTED, "gm_lattice_attention (tensor cores): complex frequencies must be the orders 1 .. %d", ncf);
+    if (ks0 == 1 && ncf == 2 && ksc == 2) return launch_tn<1, 2, 2, MODE>(a, n_order_rows, batch, cs);
+    if (ks0 == 1 && ncf == 2 && ksc == 1) return launch_tn<1, 2, 1, MODE>(a, n_order_rows, batch, cs);
+    if (ks0 == 1 && ncf == 3 && ksc == 1) return launch_tn<1, 3, 1, MODE>(a, n_order_rows, batch, cs);
+    if (ks0 == 1 && ncf == 1 && ksc == 2) return launch_tn<1, 1, 2, MODE>(a, n_order_rows, batch, cs);
+    if (ks0 == 1 && ncf == 1 && ksc == 1) return launch_tn<1, 1, 1, MODE>(a, n_order_rows, batch, cs);
+    if (ks0 == 0 && ncf == 2 && ksc == 1) return launch_tn<0, 2, 1, MODE>(a, n_order_rows, batch, cs);
+  }
   if (ks0 == 1 && ncf == 2 && ksc == 2) return launch_tc<1, 2, 2, MODE>(a, n_order_rows, batch, cs);
   if (ks0 == 1 && ncf == 2 && ksc == 1) return launch_tc<1, 2, 1, MODE>(a, n_order_rows, batch, cs);
   if (ks0 == 1 && ncf == 3 && ksc == 1) return launch_tc<1, 3, 1, MODE>(a, n_order_rows, batch, cs);
