@@ -38,7 +38,9 @@ inline int launch_status(const char* what) {
 // Opt a kernel in to `bytes` of dynamic shared memory (needed above 48 KiB).
 template <typename Kernel>
 inline int allow_smem(Kernel kernel, size_t bytes, const char* what) {
-  if (bytes <= 48 * 1024) return GM_OK;
+  cudaFuncAttributes attr;
+  GM_CUDA(cudaFuncGetAttributes(&attr, kernel));
+  if (bytes + attr.sharedSizeBytes <= 48 * 1024) return GM_OK;  // static + dynamic fit the default limit
   int device = 0, limit = 0;
   GM_CUDA(cudaGetDevice(&device));
   GM_CUDA(cudaDeviceGetAttribute(&limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));

@@ -76,6 +76,7 @@ struct TcArgs {
   const float* entries;               // (n_entries, 8): (cos, sin) of orders 1..NORD, bias at 2 NORD
   const int* row_order;
   int rows, nlon, D, H, W, NORD;
+  int exact;    // every block is exactly 16 (scalar) / 16 KSC (complex) columns wide and starts on an even column: no padding, 4-byte accesses
   int use_tma;  // the neighbours' fields have tensor maps (exact 16 / 32-column blocks, aligned, nlon >= TC_SC)
   float scale;
   TcPlan plan;
@@ -669,7 +670,7 @@ __global__ void __launch_bounds__(TC_THREADS, MODE == TC_BWD_S ? 2 : 3) lattice_
 // * Accumulators cover 8 owners: half the registers of the owner-major kernel, twice the warps per CTA.
 // * P (accumulator layout: position rows, owner columns) becomes a B operand with movmatrix (8 x 8 b16 transpose).
 // The result tile is transposed through shared memory for 16-byte stores.
-constexpr int TN_WARPS(int mode) { return 8; }
+constexpr int TN_WARPS(int mode) { return mode == TC_FWD ? 8 : 4; }
 constexpr int TN_ADV = 80;           // positions a chunk advances by
 constexpr int TN_ROWS = TN_ADV + 8;  // positions staged per chunk: a step of 16 may start 8 before the chunk's end
 
@@ -700,6 +701,12 @@ __device__ __forceinline__ unsigned movmatrix_trans(unsigned x) {
   return y;
 }
 __device__ __forceinline__ void mma_bf16_b2(float (&d)[4], const unsigned (&a)[4], const unsigned (&b)[2]) { mma_bf16(d, a, b[0], b[1]); }
+// d = a * b (no accumulator to zero first)
+__device__ __forceinline__ void mma_bf16_b2_init(float (&d)[4], const unsigned (&a)[4], const unsigned (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+               : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]), "f"(0.f));
+}
 
 __device__ __forceinline__ void ldsm_x4_sa(unsigned (&r)[4], unsigned addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -740,16 +747,12 @@ __device__ __forceinline__ void gram_step(const unsigned (&fb)[KS0 + NCF * KSC][
                                           unsigned tile, int pl, const TnLaneOffsets<KS0, NCF, KSC, TL>& lo, float (&g0)[4],
                                           float (&gr)[NCF > 0 ? NCF : 1][4], float (&gi)[NCF > 0 ? NCF : 1][4]) {
   using L = TnLayout<KS0, NCF, KSC, TL>;
-#pragma unroll
-  for (int x = 0; x < 4; ++x) {
-    g0[x] = 0.f;
-#pragma unroll
-    for (int f = 0; f < NCF; ++f) gr[f][x] = gi[f][x] = 0.f;
-  }
   if constexpr (KS0 > 0) {
     unsigned af[4];
     ldsm_x4_sa(af, tile + pl * L::REAL_PITCH + lo.g_real);
-    mma_bf16_b2(g0, af, fb[0]);
+    mma_bf16_b2_init(g0, af, fb[0]);
+  } else {
+    g0[0] = g0[1] = g0[2] = g0[3] = 0.f;
   }
   const unsigned cx = tile + pl * L::CX_PITCH;
 #pragma unroll
@@ -758,8 +761,13 @@ __device__ __forceinline__ void gram_step(const unsigned (&fb)[KS0 + NCF * KSC][
     for (int sub = 0; sub < KSC; ++sub) {
       unsigned af[4];
       ldsm_x4_sa(af, cx + lo.g_cx[sub] + f * L::CX_BYTES);
-      mma_bf16_b2(gr[f], af, fb[KS0 + f * KSC + sub]);
-      mma_bf16_b2(gi[f], af, fs[f * KSC + sub]);
+      if (sub == 0) {
+        mma_bf16_b2_init(gr[f], af, fb[KS0 + f * KSC + sub]);
+        mma_bf16_b2_init(gi[f], af, fs[f * KSC + sub]);
+      } else {
+        mma_bf16_b2(gr[f], af, fb[KS0 + f * KSC + sub]);
+        mma_bf16_b2(gi[f], af, fs[f * KSC + sub]);
+      }
     }
 }
 
@@ -803,37 +811,60 @@ __device__ __forceinline__ void flat_pair(const TcPlan& P, int h, int col, int& 
   }
 }
 
+// First flat column of k-step / m-tile KT of head h when every block is exactly as wide as its padded slot
+template <int KS0, int NCF, int KSC, int KT>
+__device__ __forceinline__ int exact_block(const TcPlan& P, int h) {
+  if constexpr (KT < KS0) return P.real_off + 16 * h + 16 * KT;
+  else return P.cf_off[(KT - KS0) / KSC] + 16 * KSC * h + 16 * ((KT - KS0) % KSC);
+}
+
 // B-operand fragments of one owner (column n = g of the warp's 8) for every k-step of the padded head layout
 template <int KS0, int NCF, int KSC, int KT = 0>
-__device__ __forceinline__ void load_owner_columns(const TcPlan& P, const __nv_bfloat16* src, bool present, bool words, int h, int c,
+__device__ __forceinline__ void load_owner_columns(const TcPlan& P, const __nv_bfloat16* src, bool present, bool exact, bool words, int h, int c,
                                                    unsigned (&fb)[KS0 + NCF * KSC][2]) {
   if constexpr (KT < KS0 + NCF * KSC) {
+    if (exact) {
+      const unsigned* w = reinterpret_cast<const unsigned*>(src + exact_block<KS0, NCF, KSC, KT>(P, h)) + c;
+      fb[KT][0] = present ? w[0] : 0u;
+      fb[KT][1] = present ? w[4] : 0u;
+    } else {
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      int g0, g1;
-      flat_pair<KS0, NCF, KSC, KT>(P, h, 2 * c + 8 * r, g0, g1);
-      unsigned w = 0u;
-      if (present) {
-        if (words && g0 >= 0 && g1 == g0 + 1 && (g0 & 1) == 0) {
-          w = *reinterpret_cast<const unsigned*>(src + g0);
-        } else {
-          if (g0 >= 0) w = __bfloat16_as_ushort(src[g0]);
-          if (g1 >= 0) w |= (unsigned)__bfloat16_as_ushort(src[g1]) << 16;
+      for (int r = 0; r < 2; ++r) {
+        int g0, g1;
+        flat_pair<KS0, NCF, KSC, KT>(P, h, 2 * c + 8 * r, g0, g1);
+        unsigned w = 0u;
+        if (present) {
+          if (words && g0 >= 0 && g1 == g0 + 1 && (g0 & 1) == 0) {
+            w = *reinterpret_cast<const unsigned*>(src + g0);
+          } else {
+            if (g0 >= 0) w = __bfloat16_as_ushort(src[g0]);
+            if (g1 >= 0) w |= (unsigned)__bfloat16_as_ushort(src[g1]) << 16;
+          }
         }
+        fb[KT][r] = w;
       }
-      fb[KT][r] = w;
     }
-    load_owner_columns<KS0, NCF, KSC, KT + 1>(P, src, present, words, h, c, fb);
+    load_owner_columns<KS0, NCF, KSC, KT + 1>(P, src, present, exact, words, h, c, fb);
   }
 }
 
 // One m-tile (16 head columns x 8 owners, accumulator layout) of a result -> global memory: transposed in registers
 // (movmatrix) so that a thread holds two adjacent columns of ONE owner (own_b): 4-byte stores.
 template <int KS0, int NCF, int KSC, int KT>
-__device__ __forceinline__ void store_tile(const TcPlan& P, __nv_bfloat16* dst, bool present, bool words, int h, int c, const float (&v)[4]) {
+__device__ __forceinline__ void store_tile(const TcPlan& P, __nv_bfloat16* dst, bool present, bool exact, bool words, int h, int c, const float (&v)[4]) {
+  const unsigned w0 = movmatrix_trans(pack_bf16(v[0], v[1]));  // (owner own_b; columns 2c, 2c + 1)
+  const unsigned w1 = movmatrix_trans(pack_bf16(v[2], v[3]));  // (owner own_b; columns 2c + 8, 2c + 9)
+  if (exact) {
+    unsigned* w = reinterpret_cast<unsigned*>(dst + exact_block<KS0, NCF, KSC, KT>(P, h)) + c;
+    if (present) {
+      w[0] = w0;
+      w[4] = w1;
+    }
+    return;
+  }
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
-    const unsigned w = movmatrix_trans(pack_bf16(v[2 * r], v[2 * r + 1]));  // (owner own_b; columns 2c + 8r, 2c + 8r + 1)
+    const unsigned w = r ? w1 : w0;
     int g0, g1;
     flat_pair<KS0, NCF, KSC, KT>(P, h, 2 * c + 8 * r, g0, g1);
     if (!present) continue;
@@ -848,12 +879,13 @@ __device__ __forceinline__ void store_tile(const TcPlan& P, __nv_bfloat16* dst, 
 
 // combine the phase accumulators of every complex m-tile and store all m-tiles of one result
 template <int KS0, int NCF, int KSC, bool CONJ, int M = 0>
-__device__ __forceinline__ void store_result(const TcPlan& P, __nv_bfloat16* dst, bool present, bool words, int h, int g, int c, const float (&inv)[2],
+__device__ __forceinline__ void store_result(const TcPlan& P, __nv_bfloat16* dst, bool present, bool exact, bool words, int h, int g, int c,
+                                             const float (&inv)[2],
                                              const float (&acc0)[4], const float (&accr)[NCF * KSC > 0 ? NCF * KSC : 1][4],
                                              const float (&acci)[NCF * KSC > 0 ? NCF * KSC : 1][4]) {
   if constexpr (M == 0 && KS0 > 0) {
     const float v[4] = {acc0[0] * inv[0], acc0[1] * inv[1], acc0[2] * inv[0], acc0[3] * inv[1]};
-    store_tile<KS0, NCF, KSC, 0>(P, dst, present, words, h, c, v);
+    store_tile<KS0, NCF, KSC, 0>(P, dst, present, exact, words, h, c, v);
   }
   if constexpr (M < NCF * KSC) {
     // rows of an accumulator m-tile are head columns g, g + 8: even = real part, odd = imaginary part.
@@ -862,8 +894,8 @@ __device__ __forceinline__ void store_result(const TcPlan& P, __nv_bfloat16* dst
     float v[4];
 #pragma unroll
     for (int x = 0; x < 4; ++x) v[x] = (accr[M][x] + sgn * __shfl_xor_sync(0xffffffffu, acci[M][x], 4)) * inv[x & 1];
-    store_tile<KS0, NCF, KSC, KS0 + M>(P, dst, present, words, h, c, v);
-    store_result<KS0, NCF, KSC, CONJ, M + 1>(P, dst, present, words, h, g, c, inv, acc0, accr, acci);
+    store_tile<KS0, NCF, KSC, KS0 + M>(P, dst, present, exact, words, h, c, v);
+    store_result<KS0, NCF, KSC, CONJ, M + 1>(P, dst, present, exact, words, h, g, c, inv, acc0, accr, acci);
   }
 }
 
@@ -874,7 +906,7 @@ struct TnRowPair {
 };
 
 template <int KS0, int NCF, int KSC, int MODE, int WARPS>
-__global__ void __launch_bounds__(32 * WARPS, MODE == TC_BWD_S ? 1 : 2) lattice_tn_kernel(const __grid_constant__ TcArgs a) {
+__global__ void __launch_bounds__(32 * WARPS, WARPS == 4 ? 3 : 2) lattice_tn_kernel(const __grid_constant__ TcArgs a) {
   constexpr int TL = 8 * WARPS, THREADS = 32 * WARPS;
   using L = TnLayout<KS0, NCF, KSC, TL>;
   constexpr int KQ = KS0 + NCF * KSC, CH = 2 * KQ, NCK = NCF * KSC > 0 ? NCF * KSC : 1;
@@ -905,6 +937,7 @@ __global__ void __launch_bounds__(32 * WARPS, MODE == TC_BWD_S ? 1 : 2) lattice_
   const int own_c = 8 * warp + 2 * c;  // the owners (own_c, own_c + 1) of this thread's accumulator columns
   const float cscale = a.scale * TC_LOG2E;
   const bool words = (a.D & 1) == 0;   // 4-byte accesses to (even column, next column) are aligned
+  const bool exact = a.exact != 0;
   TnLaneOffsets<KS0, NCF, KSC, TL> lane_off;
   lane_off.init(lane);
 
@@ -944,13 +977,13 @@ __global__ void __launch_bounds__(32 * WARPS, MODE == TC_BWD_S ? 1 : 2) lattice_
   unsigned f1[KQ][2], s1[NCK][2], f2[FWD ? 1 : KQ][2], s2[FWD ? 1 : NCK][2];
   const bool own_b_present = c0 + own_b < a.nlon;
   const int64_t own_b_base = (node0 + c0 + own_b) * a.D;
-  load_owner_columns<KS0, NCF, KSC>(P, a.own1 + own_b_base, own_b_present, words, h, c, f1);
+  load_owner_columns<KS0, NCF, KSC>(P, a.own1 + own_b_base, own_b_present, exact, words, h, c, f1);
 #pragma unroll
   for (int kc = 0; kc < NCF * KSC; ++kc)
 #pragma unroll
     for (int r = 0; r < 2; ++r) s1[kc][r] = PASS_S ? swap_neg(f1[KS0 + kc][r]) : swap_neg_lo(f1[KS0 + kc][r]);
   if constexpr (!FWD) {
-    load_owner_columns<KS0, NCF, KSC>(P, a.own2 + own_b_base, own_b_present, words, h, c, f2);
+    load_owner_columns<KS0, NCF, KSC>(P, a.own2 + own_b_base, own_b_present, exact, words, h, c, f2);
 #pragma unroll
     for (int kc = 0; kc < NCF * KSC; ++kc)
 #pragma unroll
@@ -983,13 +1016,16 @@ __global__ void __launch_bounds__(32 * WARPS, MODE == TC_BWD_S ? 1 : 2) lattice_
     int ip, p0;       // row pair, first position of the chunk
     int cnt, n_rows;  // window width, staged positions
     int lon0;         // longitude of the chunk's first position (wrapped)
+    int z, ent_off;   // sample * rows + neighbour row; first table entry of the row pair
     bool tma;         // consecutive longitudes (no wrap at the seam) and tensor maps available
   };
   auto load_stage = [&](Stage& s) {
-    const TnRowPair& rp = pairs_s[s.ip];
-    s.cnt = rp.cnt;
-    s.n_rows = min(TN_ROWS, TL + rp.cnt - 1 - s.p0);
-    int lon0 = rp.lon_base + s.p0;
+    const int4 ra = *reinterpret_cast<const int4*>(&pairs_s[s.ip]);  // cnt, lo, z, lon_base
+    s.cnt = ra.x;
+    s.z = ra.z;
+    s.ent_off = pairs_s[s.ip].ent_off;
+    s.n_rows = min(TN_ROWS, TL + ra.x - 1 - s.p0);
+    int lon0 = ra.w + s.p0;
     if (lon0 >= a.nlon) lon0 %= a.nlon;
     s.lon0 = lon0;
     s.tma = a.use_tma && lon0 + s.n_rows <= a.nlon;
@@ -1012,7 +1048,6 @@ __global__ void __launch_bounds__(32 * WARPS, MODE == TC_BWD_S ? 1 : 2) lattice_
   const bool st_whole = st_g0 >= 0 && st_g7 == st_g0 + 7 && (a.D % 8 == 0) && (st_g0 % 8 == 0);  // one aligned 16-byte chunk of real columns
   const bool st_pad = st_g0 < 0 && st_g7 < 0 && flat_column<KS0, NCF, KSC>(P, h, 8 * st_ch + 3) < 0;  // all padding (stays zero)
   auto issue = [&](const Stage& s, int buf) {  // asynchronous copies of one stage into buffer `buf`
-    const TnRowPair& rp = pairs_s[s.ip];
     unsigned char* d1 = tile1(buf);
     unsigned char* d2 = tile2(buf);
     if (s.tma) {
@@ -1021,13 +1056,13 @@ __global__ void __launch_bounds__(32 * WARPS, MODE == TC_BWD_S ? 1 : 2) lattice_
         fence_proxy_async();
         mbar_expect_tx(&copy_bar[buf], 2u * TN_ROWS * (KS0 * L::REAL_PITCH + NCF * L::CX_PITCH));
         if constexpr (KS0 > 0) {
-          tma_load_3d(d1, &a.maps[0][0], &copy_bar[buf], P.real_off + h * 16, s.lon0, rp.z);
-          tma_load_3d(d2, &a.maps[1][0], &copy_bar[buf], P.real_off + h * 16, s.lon0, rp.z);
+          tma_load_3d(d1, &a.maps[0][0], &copy_bar[buf], P.real_off + h * 16, s.lon0, s.z);
+          tma_load_3d(d2, &a.maps[1][0], &copy_bar[buf], P.real_off + h * 16, s.lon0, s.z);
         }
 #pragma unroll
         for (int f = 0; f < NCF; ++f) {
-          tma_load_3d(d1 + L::REAL_BYTES + f * L::CX_BYTES, &a.maps[0][1], &copy_bar[buf], P.cf_off[f] + h * 16 * KSC, s.lon0, rp.z);
-          tma_load_3d(d2 + L::REAL_BYTES + f * L::CX_BYTES, &a.maps[1][1], &copy_bar[buf], P.cf_off[f] + h * 16 * KSC, s.lon0, rp.z);
+          tma_load_3d(d1 + L::REAL_BYTES + f * L::CX_BYTES, &a.maps[0][1], &copy_bar[buf], P.cf_off[f] + h * 16 * KSC, s.lon0, s.z);
+          tma_load_3d(d2 + L::REAL_BYTES + f * L::CX_BYTES, &a.maps[1][1], &copy_bar[buf], P.cf_off[f] + h * 16 * KSC, s.lon0, s.z);
         }
       }
     } else if (st_active && !st_pad) {
@@ -1037,7 +1072,7 @@ __global__ void __launch_bounds__(32 * WARPS, MODE == TC_BWD_S ? 1 : 2) lattice_
       // with tensor maps in use the buffer may hold anything beyond the window: write zeros there (copies of size 0)
       const int rows_to_write = a.use_tma ? TN_ROWS : s.n_rows;
       for (int pl = st_row; pl < rows_to_write; pl += ROWS_PER_PASS) {
-        const int64_t nb = ((int64_t)rp.z * a.nlon + lon) * a.D;
+        const int64_t nb = ((int64_t)s.z * a.nlon + lon) * a.D;
         const int off = L::chunk(pl, st_ch);
         if (st_whole) {
           const int bytes = pl < s.n_rows ? 16 : 0;
@@ -1062,11 +1097,16 @@ __global__ void __launch_bounds__(32 * WARPS, MODE == TC_BWD_S ? 1 : 2) lattice_
     }
     // table entries of the offsets x = p - owner the chunk can meet (clamped: validity is decided from x itself)
     float* de = entry(buf);
-    const float* ent = a.entries + (size_t)rp.ent_off * 8;
-    for (int idx = threadIdx.x; idx < 2 * (s.n_rows + TL - 1); idx += THREADS) {
-      const int xi = idx >> 1, part = idx & 1;
-      const int x = min(max(xi + s.p0 - (TL - 1), 0), s.cnt - 1);
-      cp_async16(de + 8 * xi + 4 * part, ent + 8 * x + 4 * part, 16);
+    const float* ent = a.entries + (size_t)s.ent_off * 8;
+    static_assert(2 * (TN_ROWS + TL - 1) <= 2 * THREADS, "two guarded copies per thread cover a chunk's entries");
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+      const int idx = threadIdx.x + it * THREADS;
+      if (idx < 2 * (s.n_rows + TL - 1)) {
+        const int xi = idx >> 1, part = idx & 1;
+        const int x = min(max(xi + s.p0 - (TL - 1), 0), s.cnt - 1);
+        cp_async16(de + 8 * xi + 4 * part, ent + 8 * x + 4 * part, 16);
+      }
     }
     if constexpr (PASS_S) {
       float* ds = stats(buf);
@@ -1074,7 +1114,7 @@ __global__ void __launch_bounds__(32 * WARPS, MODE == TC_BWD_S ? 1 : 2) lattice_
         const int pl = idx >> 1, which = idx & 1;
         int lon = s.lon0 + pl;
         if (lon >= a.nlon) lon %= a.nlon;
-        const int64_t nn = ((int64_t)rp.z * a.nlon + lon) * a.H + h;
+        const int64_t nn = ((int64_t)s.z * a.nlon + lon) * a.H + h;
         cp_async4(ds + 2 * pl + which, (which ? a.delta : a.lse) + nn, 4);
       }
     }
@@ -1099,8 +1139,8 @@ __global__ void __launch_bounds__(32 * WARPS, MODE == TC_BWD_S ? 1 : 2) lattice_
     } else {
       cp_async_wait<0>();
     }
-    if (cur.tma) {
-      mbar_wait(&copy_bar[buf], (parity >> buf) & 1u);
+    if (cur.tma) {  // one warp watches the copy barrier; the others block in the CTA barrier below without issuing
+      if (warp == 0) mbar_wait(&copy_bar[buf], (parity >> buf) & 1u);
       parity ^= 1u << buf;
     }
     __syncthreads();
@@ -1115,44 +1155,40 @@ __global__ void __launch_bounds__(32 * WARPS, MODE == TC_BWD_S ? 1 : 2) lattice_
     const int p_end = min(p0 + TN_ADV, 8 * warp + 7 + cnt);
     for (int p = p_first; p < p_end; p += 16) {
       const int pl = p - p0;
-      float s0[4], sr[NF][4], si[NF][4], h0[4], hr[NF][4], hi[NF][4];
-      gram_step<KS0, NCF, KSC, TL>(f1, s1, t1, pl, lane_off, s0, sr, si);
-      if constexpr (!FWD) gram_step<KS0, NCF, KSC, TL>(f2, s2, t2, pl, lane_off, h0, hr, hi);
       // element x of a fragment: position pl + g + 8 (x >> 1), owner own_c + (x & 1)
-      float lg[4], tr[NF][4], ti[NF][4], dal[4];
+      float lg[4], tr[NF][4], ti[NF][4];
       bool valid[4];
       const float* e_lane = e_s + 8 * (pl + g - own_c + (TL - 1));  // staged entry of the offset p - owner, element 0
       const int off0 = p0 + pl + g - own_c;
+      {
+        float s0[4], sr[NF][4], si[NF][4];
+        gram_step<KS0, NCF, KSC, TL>(f1, s1, t1, pl, lane_off, s0, sr, si);
 #pragma unroll
-      for (int x = 0; x < 4; ++x) {
-        const float* e = e_lane + 8 * (8 * (x >> 1) - (x & 1));
-        valid[x] = (unsigned)(off0 + 8 * (x >> 1) - (x & 1)) < (unsigned)cnt;
-        float sum = s0[x];
-        dal[x] = FWD ? 0.f : h0[x];
-        float tau[2 * NF];
-        if constexpr (NCF >= 2) {  // complex frequencies are the orders 1 .. NCF: the first two phases are the entry's first 16 bytes
-          const float4 t = *reinterpret_cast<const float4*>(e);
-          tau[0] = t.x; tau[1] = t.y; tau[2] = t.z; tau[3] = t.w;
-          if constexpr (NCF == 3) {
-            const float2 t3 = *reinterpret_cast<const float2*>(e + 4);
-            tau[4] = t3.x; tau[5] = t3.y;
+        for (int x = 0; x < 4; ++x) {
+          const float* e = e_lane + 8 * (8 * (x >> 1) - (x & 1));
+          valid[x] = (unsigned)(off0 + 8 * (x >> 1) - (x & 1)) < (unsigned)cnt;
+          float sum = s0[x];
+          float tau[2 * NF];
+          if constexpr (NCF >= 2) {  // complex frequencies are the orders 1 .. NCF: the first two phases are the entry's first 16 bytes
+            const float4 t = *reinterpret_cast<const float4*>(e);
+            tau[0] = t.x; tau[1] = t.y; tau[2] = t.z; tau[3] = t.w;
+            if constexpr (NCF == 3) {
+              const float2 t3 = *reinterpret_cast<const float2*>(e + 4);
+              tau[4] = t3.x; tau[5] = t3.y;
+            }
+          } else if constexpr (NCF == 1) {
+            const float2 t = *reinterpret_cast<const float2*>(e);
+            tau[0] = t.x; tau[1] = t.y;
           }
-        } else if constexpr (NCF == 1) {
-          const float2 t = *reinterpret_cast<const float2*>(e);
-          tau[0] = t.x; tau[1] = t.y;
-        }
 #pragma unroll
-        for (int f = 0; f < NCF; ++f) {
-          tr[f][x] = tau[2 * f];
-          ti[f][x] = tau[2 * f + 1];
-          sum = fmaf(tau[2 * f], sr[f][x], sum);
-          sum = fmaf(-tau[2 * f + 1], si[f][x], sum);
-          if constexpr (!FWD) {
-            dal[x] = fmaf(tau[2 * f], hr[f][x], dal[x]);
-            dal[x] = fmaf(-tau[2 * f + 1], hi[f][x], dal[x]);
+          for (int f = 0; f < NCF; ++f) {
+            tr[f][x] = tau[2 * f];
+            ti[f][x] = tau[2 * f + 1];
+            sum = fmaf(tau[2 * f], sr[f][x], sum);
+            sum = fmaf(-tau[2 * f + 1], si[f][x], sum);
           }
+          lg[x] = valid[x] ? fmaf(cscale, sum, TC_LOG2E * e[2 * a.NORD]) : -INFINITY;  // -inf: outside the window
         }
-        lg[x] = valid[x] ? fmaf(cscale, sum, TC_LOG2E * e[2 * a.NORD]) : -INFINITY;  // -inf: outside the window
       }
       float w1[4], w2[4];  // the weights the two accumulations use: forward p | pass T ds | pass S ds, p
       if constexpr (FWD) {
@@ -1183,18 +1219,30 @@ __global__ void __launch_bounds__(32 * WARPS, MODE == TC_BWD_S ? 1 : 2) lattice_
           l_o[x & 1] += w1[x];
         }
       } else {
+        // p from the logits first (the (q, k) Gram blocks die here), then d alpha from the (dO, v) Gram blocks
+        float delta[4];
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
-          float lse, delta;
+          float lse;
           if (PASS_S) {
             const float2 st = *reinterpret_cast<const float2*>(stat_s + 2 * (pl + g + 8 * (x >> 1)));
-            lse = st.x * TC_LOG2E; delta = st.y;
+            lse = st.x * TC_LOG2E; delta[x] = st.y;
           } else {
-            lse = lse_o[x & 1]; delta = dl_o[x & 1];
+            lse = lse_o[x & 1]; delta[x] = dl_o[x & 1];
           }
-          const float pr = valid[x] ? fast_exp2(lg[x] - lse) : 0.f;
-          w1[x] = a.scale * pr * (dal[x] - delta);
-          w2[x] = pr;
+          w2[x] = valid[x] ? fast_exp2(lg[x] - lse) : 0.f;
+        }
+        float h0[4], hr[NF][4], hi[NF][4];
+        gram_step<KS0, NCF, KSC, TL>(f2, s2, t2, pl, lane_off, h0, hr, hi);
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          float dal = h0[x];
+#pragma unroll
+          for (int f = 0; f < NCF; ++f) {
+            dal = fmaf(tr[f][x], hr[f][x], dal);
+            dal = fmaf(-ti[f][x], hi[f][x], dal);
+          }
+          w1[x] = a.scale * w2[x] * (dal - delta[x]);
         }
       }
       // B operands: the weights (x phase parts), transposed to (owner column, position rows)
@@ -1245,8 +1293,8 @@ __global__ void __launch_bounds__(32 * WARPS, MODE == TC_BWD_S ? 1 : 2) lattice_
         a.lse_out[(node0 + c0 + own_c + e) * a.H + h] = l_o[e] > 0.f ? (m_o[e] + log2f(l_o[e])) * TC_LN2 : -INFINITY;
     }
   }
-  store_result<KS0, NCF, KSC, PASS_S>(P, a.res1 + own_b_base, own_b_present, words, h, g, c, inv, a1_0, a1_r, a1_i);
-  if constexpr (PASS_S) store_result<KS0, NCF, KSC, true>(P, a.res2 + own_b_base, own_b_present, words, h, g, c, inv, a2_0, a2_r, a2_i);
+  store_result<KS0, NCF, KSC, PASS_S>(P, a.res1 + own_b_base, own_b_present, exact, words, h, g, c, inv, a1_0, a1_r, a1_i);
+  if constexpr (PASS_S) store_result<KS0, NCF, KSC, true>(P, a.res2 + own_b_base, own_b_present, exact, words, h, g, c, inv, a2_0, a2_r, a2_i);
 }
 
 // Delta[node, h] = <dO, O> over the head's columns
@@ -1400,6 +1448,11 @@ int launch_tn(TcArgs& a, int n_order_rows, int64_t batch, cudaStream_t stream) {
     }
   }
   a.use_tma = tma ? 1 : 0;
+  bool exact = (KS0 == 0 || a.plan.a0 == 16) && 2 * a.plan.ac == 16 * KSC && a.D % 2 == 0 && (KS0 == 0 || a.plan.real_off % 2 == 0);
+  for (int f = 0; f < a.plan.n_cf; ++f) exact = exact && a.plan.cf_off[f] % 2 == 0;
+  const void* ptrs[6] = {a.own1, a.own2, a.nb1, a.nb2, a.res1, a.res2};
+  for (const void* q : ptrs) exact = exact && reinterpret_cast<uintptr_t>(q) % 4 == 0;
+  a.exact = exact ? 1 : 0;
   const size_t smem = 2 * (size_t)L::BUFFER_BYTES + 1024;
   auto kernel = lattice_tn_kernel<KS0, NCF, KSC, MODE, WARPS>;
   int st = allow_smem(kernel, smem, "gm_lattice_attention (tensor cores)");
