@@ -7,36 +7,39 @@
 //   <q_i, tau k_j> = G0 + sum_n Re( tau_n(i, j) * G_n ),   G_n = sum_c conj(q_{i,c}) k_{j,c},
 //   sum_j alpha_ij tau_n v_j = ((alpha o tau_n) V)_i,
 //
-// so for a tile of 16 consecutive targets of one lattice row and 16 consecutive
-// source longitudes of one neighbour row the Gram blocks G0, Re G_n, Im G_n are
-// plain bf16 x bf16 -> fp32 products (Re: Q K^T with the (re, im) interleave of
-// the flat layout as the contraction index; Im: the same Q against K with each
-// pair swapped and one sign flipped), the phases / bias / window enter
-// elementwise on the 16 x 16 tile in registers, and the value sums are
-// (P o tau) V products with P in registers as the A operand.  Pairs outside a
-// target's cyclic window are masked by staging their table entry with bias
-// -inf; only the longitude band of a row pair is visited, so the tiles are
-// dense in the polar rows (whole rows are neighbours) and ~20-40 % dense at the
-// equator.
+// so for 8 consecutive owners (targets; sources in the backward's source-major
+// pass) of one lattice row and 16 consecutive positions of one neighbour row the
+// Gram blocks G0, Re G_n, Im G_n are plain bf16 x bf16 -> fp32 products, the
+// phases / bias / window enter elementwise on the tile in registers, and the value
+// sums are products with the weights as an operand.  The staged neighbour
+// positions are the M dimension of the MMAs (16 per step) and a warp's owners the
+// N dimension (8 per warp):
 //
-// One CTA = 64 owners (targets; sources in the backward's source-major pass) x one
-// head x one sample; a warp owns 16 of them.  The neighbour rows of one lattice
-// row and the table entries they need are copied into shared memory as raw bf16 /
-// fp32, double-buffered: the copy of the next (row pair, chunk) runs while the
-// current one is consumed.  A staged field is one sub-tile per frequency block
-// (80 positions x 32 or 64 bytes) in the 32-byte / 64-byte shared-memory swizzle,
-// so that ldmatrix is conflict-free without padding and a whole sub-tile is ONE
-// TMA tensor copy (cp.async.bulk.tensor.3d over (column, longitude, sample * row),
-// completion on an mbarrier, issued by one thread).  Chunks that wrap the
-// longitude seam, and head layouts whose blocks are not exactly 16 / 32 columns,
-// are staged with per-thread cp.async into the same swizzled layout.  The
-// pair-swapped value operand of the imaginary phase part is made in registers
-// (one shuffle per fragment register).  Tensor-core instruction: mma.sync
-// m16n8k16 (bf16 inputs, fp32 accumulate); fragments via ldmatrix.
+//   S^T   (16 positions x 8 owners)  = tile (positions x columns) * owners^T      A: shared memory, B: loop-invariant registers
+//   out^T (16 columns   x 8 owners) += tile^T (columns x positions) * (P o tau)^T  A: shared memory (ldmatrix.trans), B: P^T
+//
+// * Only the longitude band of a row pair is visited; pairs outside an owner's cyclic window get logit -inf.  8 owners
+//   see a window of 7 + cnt positions, so the narrow equatorial windows (cnt <= 9) take ONE step per neighbour row;
+//   polar windows (whole rows) are dense.
+// * Im G_n uses a pre-swapped copy of the OWNERS' fragments, (re, im) -> (-im, re) or (im, -re), made once per CTA.
+// * The imaginary part of the phase accumulates into a second accumulator set; the multiplication by +-i (the pair
+//   swap) is applied once in the epilogue, so the staged value tile is never swapped.
+// * The weights P (accumulator layout: position rows, owner columns) become a B operand with movmatrix (8 x 8 b16
+//   transpose in registers); the same instruction turns the result tiles into 4-byte stores per owner.
+// * The softmax reference maximum of an owner moves only when it is exceeded by 2^8 (lazy rescaling).
+//
+// One CTA = 8 owners x WARPS warps x one head x one sample.  The neighbour rows of one lattice row and the table
+// entries they need are copied into shared memory as raw bf16 / fp32, double-buffered: the copy of the next
+// (row pair, chunk) runs while the current one is consumed.  A staged field is one sub-tile per frequency block
+// (88 positions x 32 or 64 bytes) in the 32-byte / 64-byte shared-memory swizzle, so that ldmatrix is conflict-free
+// without padding and a whole sub-tile is ONE TMA tensor copy (cp.async.bulk.tensor.3d over (column, longitude,
+// sample * row), completion on an mbarrier, issued by one thread).  Chunks that wrap the longitude seam, and head
+// layouts whose blocks are not exactly 16 / 32 columns, are staged with per-thread cp.async into the same swizzled
+// layout.  Tensor-core instruction: mma.sync m16n8k16 (bf16 inputs, fp32 accumulate); fragments via ldmatrix.
 //
 // Backward, two deterministic passes (no atomics):
 //   pass T: owners = targets.  Gram blocks of (q, k) and of (dO, v) give the logits and d alpha;
-//           ds = scale p (d alpha - Delta) is the A operand of (ds o tau) K -> dq.
+//           ds = scale p (d alpha - Delta) weights (ds o tau) K -> dq.
 //   pass S: owners = SOURCES, neighbours = the targets that see them (transposed tables, their lse / Delta
 //           staged with them).  Same Gram blocks with the roles swapped, then (ds o conj tau) Q -> dk and
 //           (p o conj tau) dO -> dv.
@@ -48,12 +51,9 @@
 namespace gmb {
 namespace {
 
-constexpr int TC_THREADS = 128;
-constexpr int TC_TL = 64;  // targets per CTA
 constexpr float TC_LOG2E = 1.4426950408889634f, TC_LN2 = 0.6931471805599453f;
 constexpr int TC_MAX_CF = 3;
 constexpr int TC_MAX_WIN = 33;  // 2 W + 1 neighbour rows at most
-constexpr int TC_SC = 80;       // staged positions per chunk: 64 owners + a window of up to 17 fit one chunk
 constexpr unsigned TC_WAIT_LIMIT = 1u << 22;  // polls of a copy barrier before the kernel gives up on it
 
 // set when a wait on a TMA completion barrier ran out (never expected; the results of that launch are invalid)
@@ -77,7 +77,7 @@ struct TcArgs {
   const int* row_order;
   int rows, nlon, D, H, W, NORD;
   int exact;    // every block is exactly 16 (scalar) / 16 KSC (complex) columns wide and starts on an even column: no padding, 4-byte accesses
-  int use_tma;  // the neighbours' fields have tensor maps (exact 16 / 32-column blocks, aligned, nlon >= TC_SC)
+  int use_tma;  // the neighbours' fields have tensor maps (exact 16 / 32-column blocks, aligned, at least one chunk of longitudes)
   float scale;
   TcPlan plan;
   // tensor maps over the neighbours' fields as (D, nlon, batch * rows): [field][0 = 16-column box, 1 = complex-block box]
@@ -95,18 +95,6 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], 
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void ldsm_x4(unsigned (&r)[4], const void* p) {
-  const unsigned addr = (unsigned)__cvta_generic_to_shared(p);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ void ldsm_x4_trans(unsigned (&r)[4], const void* p) {
-  const unsigned addr = (unsigned)__cvta_generic_to_shared(p);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ void ldsm_x2(unsigned (&r)[2], const void* p) {
-  const unsigned addr = (unsigned)__cvta_generic_to_shared(p);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
 }
 // ---- TMA + mbarrier (single CTA; no multicast)
 __device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
@@ -168,508 +156,7 @@ __device__ __forceinline__ int flat_column(const TcPlan& P, int h, int c) {
   return (f < P.n_cf && r < 2 * P.ac) ? P.cf_off[f] + 2 * h * P.ac + r : -1;
 }
 
-// A-operand fragments of 16 owner rows for every k-step of the padded head layout
-template <int KS0, int NCF, int KSC>
-__device__ __forceinline__ void load_owner_fragments(const TcPlan& P, const __nv_bfloat16* field, int64_t node0, int c0, int nlon, int D,
-                                                     int h, int tl_a, int tl_b, int c, unsigned (&fa)[KS0 + NCF * KSC][4]) {
-#pragma unroll
-  for (int ks = 0; ks < KS0 + NCF * KSC; ++ks)
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      const int tl = (r & 1) ? tl_b : tl_a;
-      const int col = 16 * ks + 2 * c + ((r & 2) ? 8 : 0);
-      const int t = c0 + tl;
-      float lo = 0.f, hi = 0.f;
-      if (t < nlon) {
-        const __nv_bfloat16* src = field + (node0 + t) * D;
-        const int g0 = flat_column<KS0, NCF, KSC>(P, h, col), g1 = flat_column<KS0, NCF, KSC>(P, h, col + 1);
-        if (g0 >= 0) lo = __bfloat162float(src[g0]);
-        if (g1 >= 0) hi = __bfloat162float(src[g1]);
-      }
-      fa[ks][r] = pack_bf16(lo, hi);
-    }
-}
-
-// Shared-memory layout of one staged field: a sub-tile per frequency block, TC_SC rows each.  The scalar block's rows
-// are 32 bytes (16 columns), a complex frequency's rows 32 * KSC bytes.  16-byte chunk cb of row r sits at
-// r * pitch + 16 * (cb ^ s(r)), s(r) = (r >> 2) & 1 for 32-byte rows and (r >> 1) & 3 for 64-byte rows: the hardware's
-// 32-byte / 64-byte swizzle when the sub-tile starts on a 1024-byte boundary, and conflict-free for ldmatrix.
-template <int KS0, int NCF, int KSC>
-struct TcLayout {
-  static constexpr __host__ __device__ int align1k(int x) { return (x + 1023) / 1024 * 1024; }
-  static constexpr int REAL_PITCH = 32, CX_PITCH = 32 * KSC;
-  static constexpr int REAL_BYTES = KS0 ? align1k(TC_SC * REAL_PITCH) : 0;
-  static constexpr int CX_BYTES = align1k(TC_SC * CX_PITCH);
-  static constexpr int FIELD_BYTES = REAL_BYTES + NCF * CX_BYTES;
-  static constexpr int ENT_BYTES = (TC_SC + TC_TL) * 32;
-  static constexpr int BUFFER_BYTES = align1k(2 * FIELD_BYTES + ENT_BYTES + TC_SC * 8);  // with the (lse, Delta) pairs of pass S
-  static __device__ __forceinline__ int real_chunk(int r, int cb) { return r * REAL_PITCH + 16 * (cb ^ ((r >> 2) & 1)); }
-  static __device__ __forceinline__ int cx_chunk(int f, int r, int cb) {
-    return REAL_BYTES + f * CX_BYTES + r * CX_PITCH + 16 * (cb ^ (KSC == 2 ? (r >> 1) & 3 : (r >> 2) & 1));
-  }
-  // offset of padded head-local chunk ch (8 columns) of staged row r
-  static __device__ __forceinline__ int chunk(int r, int ch) {
-    if (ch < 2 * KS0) return real_chunk(r, ch);
-    const int cc = ch - 2 * KS0;
-    return cx_chunk(cc / (2 * KSC), r, cc % (2 * KSC));
-  }
-};
-
-// Gram blocks of 16 owners x 8 staged rows (prow0 .. prow0 + 7, prow0 a multiple of 8): g0 (scalar block), gr / gi per
-// complex frequency.  OWNER_IS_Q: owners carry q, staged rows k (imaginary part against (k_im, -k_re)); otherwise owners
-// carry k, staged rows q (imaginary part against (-q_im, q_re)).  Same for (dO, v).
-template <int KS0, int NCF, int KSC, bool OWNER_IS_Q>
-__device__ __forceinline__ void gram_half(const unsigned (&fa)[KS0 + NCF * KSC][4], const unsigned char* tile, int prow0, int lane,
-                                          float (&g0)[4], float (&gr)[NCF > 0 ? NCF : 1][4], float (&gi)[NCF > 0 ? NCF : 1][4]) {
-  using L = TcLayout<KS0, NCF, KSC>;
-#pragma unroll
-  for (int x = 0; x < 4; ++x) {
-    g0[x] = 0.f;
-#pragma unroll
-    for (int f = 0; f < NCF; ++f) gr[f][x] = gi[f][x] = 0.f;
-  }
-  const int mi = lane >> 3, row = prow0 + (lane & 7);  // one 8 x 8 matrix per 16-byte chunk: matrix mi <- chunk mi of the block
-  if constexpr (KS0 > 0) {
-    unsigned bf[2];
-    ldsm_x2(bf, tile + L::real_chunk(row, mi & 1));
-    mma_bf16(g0, fa[0], bf[0], bf[1]);
-  }
-#pragma unroll
-  for (int f = 0; f < NCF; ++f) {
-    unsigned bf[4];
-    if constexpr (KSC == 2) {
-      ldsm_x4(bf, tile + L::cx_chunk(f, row, mi));
-    } else {
-      unsigned b2[2];
-      ldsm_x2(b2, tile + L::cx_chunk(f, row, mi & 1));
-      bf[0] = b2[0]; bf[1] = b2[1]; bf[2] = bf[3] = 0u;
-    }
-#pragma unroll
-    for (int sub = 0; sub < KSC; ++sub) {
-      const int kk = KS0 + f * KSC + sub;
-      const unsigned b0 = bf[2 * sub], b1 = bf[2 * sub + 1];
-      mma_bf16(gr[f], fa[kk], b0, b1);
-      if (OWNER_IS_Q) mma_bf16(gi[f], fa[kk], swap_neg(b0), swap_neg(b1));
-      else mma_bf16(gi[f], fa[kk], swap_neg_lo(b0), swap_neg_lo(b1));
-    }
-  }
-}
-
-// acc (16 owners x padded head width) += A (16 owners x 16 staged rows pl .. pl + 15, pl a multiple of 16) * tile with
-// the phase parts: scalar block a0 * tile; complex frequency f: ar[f] * tile + ai[f] * tile~, where tile~ holds each
-// (re, im) pair as (-im, re) [CONJ = false: multiplication by tau] or (im, -re) [CONJ = true: by conj tau].  tile~ is
-// formed in registers: the partner column of a B fragment lives in the lane 4 away.
-template <int KS0, int NCF, int KSC, bool CONJ>
-__device__ __forceinline__ void accumulate_tiles(float (&acc)[2 * (KS0 + NCF * KSC)][4], const unsigned (&a0)[4],
-                                                 const unsigned (&ar)[NCF > 0 ? NCF : 1][4], const unsigned (&ai)[NCF > 0 ? NCF : 1][4],
-                                                 const unsigned char* tile, int pl, int lane) {
-  using L = TcLayout<KS0, NCF, KSC>;
-  // this lane's column inside an n-tile is g = lane / 4: even = real part, odd = imaginary part
-  const unsigned flip = (((lane >> 2) & 1) == (CONJ ? 1 : 0)) ? 0x80008000u : 0u;
-  const int mi = lane >> 3;
-  const int prow = pl + 8 * (mi & 1) + (lane & 7), cbl = mi >> 1;  // matrices: (rows 0-7, chunk), (rows 8-15, chunk), same for chunk + 1
-  if constexpr (KS0 > 0) {
-    unsigned vf[4];
-    ldsm_x4_trans(vf, tile + L::real_chunk(prow, cbl));
-    mma_bf16(acc[0], a0, vf[0], vf[1]);
-    mma_bf16(acc[1], a0, vf[2], vf[3]);
-  }
-#pragma unroll
-  for (int f = 0; f < NCF; ++f)
-#pragma unroll
-    for (int pair = 0; pair < KSC; ++pair) {
-      const int nt = 2 * KS0 + 2 * KSC * f + 2 * pair;
-      unsigned vf[4], wf[4];
-      ldsm_x4_trans(vf, tile + L::cx_chunk(f, prow, 2 * pair + cbl));
-#pragma unroll
-      for (int x = 0; x < 4; ++x) wf[x] = __shfl_xor_sync(0xffffffffu, vf[x], 4) ^ flip;
-      mma_bf16(acc[nt], ar[f], vf[0], vf[1]);
-      mma_bf16(acc[nt], ai[f], wf[0], wf[1]);
-      mma_bf16(acc[nt + 1], ar[f], vf[2], vf[3]);
-      mma_bf16(acc[nt + 1], ai[f], wf[2], wf[3]);
-    }
-}
-
-// One (row pair, chunk) of the walk over an owner row's neighbour rows.
-struct TcStage {
-  int dj, p0, cnt, lo, window;
-  int z;  // sample * rows + neighbour row
-  int64_t nrow0;
-  const float* ent;
-};
-
-template <int KS0, int NCF, int KSC, int MODE>
-__global__ void __launch_bounds__(TC_THREADS, MODE == TC_BWD_S ? 2 : 3) lattice_tc_kernel(const __grid_constant__ TcArgs a) {
-  using L = TcLayout<KS0, NCF, KSC>;
-  constexpr int KQ = KS0 + NCF * KSC, CH = 2 * KQ, NT = 2 * KQ;
-  constexpr int NF = NCF > 0 ? NCF : 1;
-  constexpr bool FWD = MODE == TC_FWD, PASS_S = MODE == TC_BWD_S;
-  constexpr int SC = TC_SC;
-  extern __shared__ __align__(1024) unsigned char smem_dyn[];
-  // swizzled sub-tiles must start on 1024-byte boundaries of the shared-memory window: align by hand (1 KB of slack is requested)
-  unsigned char* const smem_raw = smem_dyn + ((1024u - ((unsigned)__cvta_generic_to_shared(smem_dyn) & 1023u)) & 1023u);
-  __shared__ __align__(8) unsigned long long copy_bar[2];  // completion of the TMA copies into buffer 0 / 1
-  const TcPlan& P = a.plan;
-  // two buffers, each: field 1 sub-tiles | field 2 sub-tiles | entries (SC + TC_TL, 8) fp32 | stats (SC, 2) fp32 (pass S)
-  constexpr int buf_bytes = L::BUFFER_BYTES;
-  auto tile1 = [&](int buf) { return smem_raw + buf * buf_bytes; };
-  auto tile2 = [&](int buf) { return smem_raw + buf * buf_bytes + L::FIELD_BYTES; };
-  auto entry = [&](int buf) { return reinterpret_cast<float*>(smem_raw + buf * buf_bytes + 2 * L::FIELD_BYTES); };
-  auto stats = [&](int buf) { return reinterpret_cast<float*>(smem_raw + buf * buf_bytes + 2 * L::FIELD_BYTES + L::ENT_BYTES); };
-
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, c = lane & 3;
-  const int tiles = (a.nlon + TC_TL - 1) / TC_TL;
-  const int row = a.row_order[blockIdx.x / tiles];
-  const int c0 = (blockIdx.x % tiles) * TC_TL;
-  const int h = blockIdx.y;
-  const int64_t b = blockIdx.z;
-  const int64_t node0 = (b * a.rows + row) * (int64_t)a.nlon;
-  const int tl_a = 16 * warp + g, tl_b = tl_a + 8;  // the two owner rows this thread sees in every fragment
-  const float cscale = a.scale * TC_LOG2E;
-  const bool orders_12 = NCF == 2 && P.n_cf == 2 && P.cf_order[0] == 1 && P.cf_order[1] == 2;
-
-  unsigned f1[KQ][4], f2[FWD ? 1 : KQ][4];
-  load_owner_fragments<KS0, NCF, KSC>(P, a.own1, node0, c0, a.nlon, a.D, h, tl_a, tl_b, c, f1);
-  if constexpr (!FWD) load_owner_fragments<KS0, NCF, KSC>(P, a.own2, node0, c0, a.nlon, a.D, h, tl_a, tl_b, c, f2);
-  float lse_a = 0.f, lse_b = 0.f, dl_a = 0.f, dl_b = 0.f;
-  if (MODE == TC_BWD_T) {
-    if (c0 + tl_a < a.nlon) { lse_a = a.lse[(node0 + c0 + tl_a) * a.H + h] * TC_LOG2E; dl_a = a.delta[(node0 + c0 + tl_a) * a.H + h]; }
-    if (c0 + tl_b < a.nlon) { lse_b = a.lse[(node0 + c0 + tl_b) * a.H + h] * TC_LOG2E; dl_b = a.delta[(node0 + c0 + tl_b) * a.H + h]; }
-  }
-  float acc1[NT][4], acc2[PASS_S ? NT : 1][4];
-#pragma unroll
-  for (int nt = 0; nt < NT; ++nt) {
-    acc1[nt][0] = acc1[nt][1] = acc1[nt][2] = acc1[nt][3] = 0.f;
-    if constexpr (PASS_S) acc2[nt][0] = acc2[nt][1] = acc2[nt][2] = acc2[nt][3] = 0.f;
-  }
-  float m_a = -1e30f, m_b = -1e30f, l_a = 0.f, l_b = 0.f;  // forward: running max (base-2 logits), partial row sums
-
-  // ---- the walk: stages = (neighbour row, chunk of its window), produced in order.  The owner row's window
-  // table (2W + 1 row pairs) is read once into shared memory so that stepping to the next stage costs no global load.
-  __shared__ int win_s[3 * TC_MAX_WIN];
-  for (int x = threadIdx.x; x < 2 * a.W + 1; x += TC_THREADS) {
-    const int widx = row * (2 * a.W + 1) + x;
-    win_s[3 * x] = a.win_cnt[widx];
-    win_s[3 * x + 1] = a.win_lo[widx];
-    win_s[3 * x + 2] = a.win_off[widx];
-  }
-  __syncthreads();
-  auto first_chunk_of_row = [&](TcStage& s, int dj) -> bool {  // set s to chunk 0 of the first non-empty row pair >= dj
-    for (; dj <= a.W; ++dj) {
-      const int j = row + dj;
-      if (j < 0 || j >= a.rows) continue;
-      const int cnt = win_s[3 * (dj + a.W)];
-      if (cnt == 0) continue;
-      s.dj = dj; s.p0 = 0; s.cnt = cnt; s.lo = win_s[3 * (dj + a.W) + 1]; s.window = TC_TL + cnt - 1;
-      s.z = (int)(b * a.rows + j);
-      s.nrow0 = (int64_t)s.z * a.nlon;
-      s.ent = a.entries + (size_t)win_s[3 * (dj + a.W) + 2] * 8;
-      return true;
-    }
-    return false;
-  };
-  auto advance = [&](TcStage& s) -> bool {
-    if (s.p0 + SC < s.window) { s.p0 += SC; return true; }
-    return first_chunk_of_row(s, s.dj + 1);
-  };
-  // per-thread staging slots of the cp.async path: thread -> (row within a pass, 16-byte chunk); the chunk's flat column is fixed
-  constexpr int ROWS_PER_PASS = TC_THREADS / CH;
-  const int st_row = threadIdx.x / CH, st_ch = threadIdx.x - st_row * CH;
-  const int st_g0 = flat_column<KS0, NCF, KSC>(P, h, 8 * st_ch), st_g7 = flat_column<KS0, NCF, KSC>(P, h, 8 * st_ch + 7);
-  const bool st_active = st_row < ROWS_PER_PASS;
-  const bool st_whole = st_g0 >= 0 && st_g7 == st_g0 + 7 && (a.D % 8 == 0) && (st_g0 % 8 == 0);  // one aligned 16-byte chunk of real columns
-  const bool st_pad = st_g0 < 0 && st_g7 < 0 && flat_column<KS0, NCF, KSC>(P, h, 8 * st_ch + 3) < 0;  // all padding (stays zero)
-  // zero both buffers once: rows beyond a window and padding columns are never written again and must be finite
-  for (int x = threadIdx.x; x < 2 * buf_bytes / 16; x += TC_THREADS) reinterpret_cast<uint4*>(smem_raw)[x] = make_uint4(0, 0, 0, 0);
-  if (threadIdx.x == 0) {
-    mbar_init(&copy_bar[0], 1);
-    mbar_init(&copy_bar[1], 1);
-    fence_mbar_init();
-  }
-  __syncthreads();
-  // a stage goes through the tensor maps when its positions are consecutive longitudes (no wrap at the seam)
-  auto by_tma = [&](const TcStage& s) -> bool {
-    if (!a.use_tma) return false;
-    const int lon0 = tc_wrap(c0 + s.lo + s.p0, a.nlon);
-    return lon0 + min(SC, s.window - s.p0) <= a.nlon;
-  };
-  auto issue = [&](const TcStage& s, int buf) {  // asynchronous copies of one stage into buffer `buf`
-    unsigned char* d1 = tile1(buf);
-    unsigned char* d2 = tile2(buf);
-    const int n_rows = min(SC, s.window - s.p0);
-    if (by_tma(s)) {
-      if (threadIdx.x == 0) {
-        // the buffer was last touched through the generic proxy (zero fill, ldmatrix, fallback stores): order those first
-        fence_proxy_async();
-        const int lon0 = tc_wrap(c0 + s.lo + s.p0, a.nlon);
-        mbar_expect_tx(&copy_bar[buf], 2u * SC * (KS0 * L::REAL_PITCH + NCF * L::CX_PITCH));
-        if constexpr (KS0 > 0) {
-          tma_load_3d(d1, &a.maps[0][0], &copy_bar[buf], P.real_off + h * 16, lon0, s.z);
-          tma_load_3d(d2, &a.maps[1][0], &copy_bar[buf], P.real_off + h * 16, lon0, s.z);
-        }
-#pragma unroll
-        for (int f = 0; f < NCF; ++f) {
-          tma_load_3d(d1 + L::REAL_BYTES + f * L::CX_BYTES, &a.maps[0][1], &copy_bar[buf], P.cf_off[f] + h * 16 * KSC, lon0, s.z);
-          tma_load_3d(d2 + L::REAL_BYTES + f * L::CX_BYTES, &a.maps[1][1], &copy_bar[buf], P.cf_off[f] + h * 16 * KSC, lon0, s.z);
-        }
-      }
-    } else if (st_active && !st_pad) {
-      int lon = tc_wrap(c0 + s.lo + s.p0 + st_row, a.nlon);
-      const int step = ROWS_PER_PASS % a.nlon;
-      for (int pl = st_row; pl < n_rows; pl += ROWS_PER_PASS) {
-        const int64_t nb = (s.nrow0 + lon) * a.D;
-        const int off = L::chunk(pl, st_ch);
-        if (st_whole) {
-          cp_async16(d1 + off, a.nb1 + nb + st_g0, 16);
-          cp_async16(d2 + off, a.nb2 + nb + st_g0, 16);
-        } else {  // a chunk that straddles padding or is misaligned: element by element (visible after the barrier)
-          unsigned short u1[8], u2[8];
-#pragma unroll
-          for (int x = 0; x < 8; ++x) {
-            const int gx = flat_column<KS0, NCF, KSC>(P, h, 8 * st_ch + x);
-            u1[x] = gx >= 0 ? __bfloat16_as_ushort(a.nb1[nb + gx]) : (unsigned short)0;
-            u2[x] = gx >= 0 ? __bfloat16_as_ushort(a.nb2[nb + gx]) : (unsigned short)0;
-          }
-          *reinterpret_cast<uint4*>(d1 + off) =
-              make_uint4(u1[0] | (u1[1] << 16), u1[2] | (u1[3] << 16), u1[4] | (u1[5] << 16), u1[6] | (u1[7] << 16));
-          *reinterpret_cast<uint4*>(d2 + off) =
-              make_uint4(u2[0] | (u2[1] << 16), u2[2] | (u2[3] << 16), u2[4] | (u2[5] << 16), u2[6] | (u2[7] << 16));
-        }
-        lon += step;
-        if (lon >= a.nlon) lon -= a.nlon;
-      }
-    }
-    // table entries of the offsets x = p - tl the chunk can meet (clamped: validity is decided from x itself)
-    float* de = entry(buf);
-    for (int idx = threadIdx.x; idx < 2 * (n_rows + TC_TL - 1); idx += TC_THREADS) {
-      const int xi = idx >> 1, part = idx & 1;
-      const int x = min(max(xi + s.p0 - (TC_TL - 1), 0), s.cnt - 1);
-      cp_async16(de + 8 * xi + 4 * part, s.ent + (size_t)x * 8 + 4 * part, 16);
-    }
-    if constexpr (PASS_S) {
-      float* ds = stats(buf);
-      for (int idx = threadIdx.x; idx < 2 * n_rows; idx += TC_THREADS) {
-        const int pl = idx >> 1, which = idx & 1;
-        const int64_t nn = (s.nrow0 + tc_wrap(c0 + s.lo + s.p0 + pl, a.nlon)) * a.H + h;
-        cp_async4(ds + 2 * pl + which, (which ? a.delta : a.lse) + nn, 4);
-      }
-    }
-    cp_async_commit();
-  };
-
-  TcStage cur;
-  bool have = first_chunk_of_row(cur, -a.W);
-  int buf = 0;
-  unsigned parity = 0;  // bit b: the phase of copy_bar[b] the next TMA stage into buffer b completes
-  if (have) issue(cur, 0);
-  while (have) {
-    TcStage nxt = cur;
-    const bool have_next = advance(nxt);
-    if (have_next) {
-      issue(nxt, buf ^ 1);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
-    if (by_tma(cur)) {
-      mbar_wait(&copy_bar[buf], (parity >> buf) & 1u);
-      parity ^= 1u << buf;
-    }
-    __syncthreads();
-    const unsigned char* t1 = tile1(buf);
-    const unsigned char* t2 = tile2(buf);
-    const float* e_s = entry(buf);
-    const float* stat_s = stats(buf);
-    const int p0 = cur.p0, cnt = cur.cnt;
-
-    // ---- this warp's 16-position steps inside the chunk
-    const int p_lo = max(p0, 16 * warp), p_hi = min(min(p0 + SC, cur.window), 16 * warp + 15 + cnt);
-    for (int p = p_lo; p < p_hi; p += 16) {
-      const int pl = p - p0;
-      unsigned xa[4], xar[NF][4], xai[NF][4];   // forward: p, p tau | backward: ds, ds tau
-      unsigned ya[4], yar[NF][4], yai[NF][4];   // pass S: p, p tau
-      float lg[2][4], tr[NF][2][4], ti[NF][2][4];
-      float mx_a = m_a, mx_b = m_b;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        if (half == 1 && p + 8 >= p_hi) {  // the upper 8 positions are beyond every owner's window (warp-uniform): no work
-#pragma unroll
-          for (int x = 0; x < 4; ++x) {
-            lg[1][x] = -INFINITY;
-#pragma unroll
-            for (int f = 0; f < NCF; ++f) tr[f][1][x] = ti[f][1][x] = 0.f;
-          }
-          xa[2] = xa[3] = ya[2] = ya[3] = 0u;
-#pragma unroll
-          for (int f = 0; f < NCF; ++f) xar[f][2] = xar[f][3] = xai[f][2] = xai[f][3] = yar[f][2] = yar[f][3] = yai[f][2] = yai[f][3] = 0u;
-          continue;
-        }
-        float s0[4], sr[NF][4], si[NF][4], h0[4], hr[NF][4], hi[NF][4];
-        gram_half<KS0, NCF, KSC, !PASS_S>(f1, t1, pl + 8 * half, lane, s0, sr, si);
-        if constexpr (!FWD) gram_half<KS0, NCF, KSC, !PASS_S>(f2, t2, pl + 8 * half, lane, h0, hr, hi);
-        float ds[4], pr[4];
-#pragma unroll
-        for (int x = 0; x < 4; ++x) {
-          const int tl = (x & 2) ? tl_b : tl_a;
-          const int pos = pl + 8 * half + 2 * c + (x & 1);
-          const int xi = pos - tl + (TC_TL - 1);                    // staged entry of the offset x = p - tl
-          const bool valid = (unsigned)(p0 + pos - tl) < (unsigned)cnt;
-          float sum = s0[x], dal = FWD ? 0.f : h0[x];
-          float tau[2 * NF];
-          if (NCF == 2 && orders_12) {  // the usual case, frequencies 1 and 2: their phases are the entry's first 16 bytes
-            const float4 t = *reinterpret_cast<const float4*>(e_s + 8 * xi);
-            tau[0] = t.x; tau[1] = t.y; tau[2] = t.z; tau[3] = t.w;
-          } else {
-#pragma unroll
-            for (int f = 0; f < NCF; ++f) {
-              const float2 t = *reinterpret_cast<const float2*>(e_s + 8 * xi + 2 * (P.cf_order[f < P.n_cf ? f : 0] - 1));
-              tau[2 * f] = t.x; tau[2 * f + 1] = t.y;
-            }
-          }
-#pragma unroll
-          for (int f = 0; f < NCF; ++f) {
-            tr[f][half][x] = tau[2 * f];
-            ti[f][half][x] = tau[2 * f + 1];
-            sum += tau[2 * f] * sr[f][x] - tau[2 * f + 1] * si[f][x];
-            if constexpr (!FWD) dal += tau[2 * f] * hr[f][x] - tau[2 * f + 1] * hi[f][x];
-          }
-          const float logit = valid ? TC_LOG2E * e_s[8 * xi + 2 * a.NORD] + cscale * sum : -INFINITY;  // -inf: outside the window
-          if constexpr (FWD) {
-            lg[half][x] = logit;
-            if (x & 2) mx_b = fmaxf(mx_b, logit); else mx_a = fmaxf(mx_a, logit);
-          } else {
-            float lse, delta;
-            if (PASS_S) { lse = stat_s[2 * pos] * TC_LOG2E; delta = stat_s[2 * pos + 1]; }
-            else { lse = (x & 2) ? lse_b : lse_a; delta = (x & 2) ? dl_b : dl_a; }
-            pr[x] = valid ? exp2f(logit - lse) : 0.f;
-            ds[x] = a.scale * pr[x] * (dal - delta);
-          }
-        }
-        if constexpr (!FWD) {
-          xa[2 * half] = pack_bf16(ds[0], ds[1]);
-          xa[2 * half + 1] = pack_bf16(ds[2], ds[3]);
-          if (PASS_S) {
-            ya[2 * half] = pack_bf16(pr[0], pr[1]);
-            ya[2 * half + 1] = pack_bf16(pr[2], pr[3]);
-          }
-#pragma unroll
-          for (int f = 0; f < NCF; ++f) {
-            xar[f][2 * half] = pack_bf16(ds[0] * tr[f][half][0], ds[1] * tr[f][half][1]);
-            xar[f][2 * half + 1] = pack_bf16(ds[2] * tr[f][half][2], ds[3] * tr[f][half][3]);
-            xai[f][2 * half] = pack_bf16(ds[0] * ti[f][half][0], ds[1] * ti[f][half][1]);
-            xai[f][2 * half + 1] = pack_bf16(ds[2] * ti[f][half][2], ds[3] * ti[f][half][3]);
-            if (PASS_S) {
-              yar[f][2 * half] = pack_bf16(pr[0] * tr[f][half][0], pr[1] * tr[f][half][1]);
-              yar[f][2 * half + 1] = pack_bf16(pr[2] * tr[f][half][2], pr[3] * tr[f][half][3]);
-              yai[f][2 * half] = pack_bf16(pr[0] * ti[f][half][0], pr[1] * ti[f][half][1]);
-              yai[f][2 * half + 1] = pack_bf16(pr[2] * ti[f][half][2], pr[3] * ti[f][half][3]);
-            }
-          }
-        }
-      }
-      if constexpr (FWD) {
-        // online softmax over the 16 positions: row maxima across the quad, rescale, exponentials, P o tau fragments
-        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
-        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
-        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
-        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
-        if (__any_sync(0xffffffffu, mx_a != m_a || mx_b != m_b)) {  // some row's maximum moved: rescale what was summed so far
-          const float corr_a = exp2f(m_a - mx_a), corr_b = exp2f(m_b - mx_b);
-          m_a = mx_a;
-          m_b = mx_b;
-          l_a *= corr_a;
-          l_b *= corr_b;
-#pragma unroll
-          for (int nt = 0; nt < NT; ++nt) {
-            acc1[nt][0] *= corr_a; acc1[nt][1] *= corr_a;
-            acc1[nt][2] *= corr_b; acc1[nt][3] *= corr_b;
-          }
-        }
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          float pr[4];
-#pragma unroll
-          for (int x = 0; x < 4; ++x) {
-            pr[x] = exp2f(lg[half][x] - ((x & 2) ? m_b : m_a));
-            if (x & 2) l_b += pr[x]; else l_a += pr[x];
-          }
-          xa[2 * half] = pack_bf16(pr[0], pr[1]);
-          xa[2 * half + 1] = pack_bf16(pr[2], pr[3]);
-#pragma unroll
-          for (int f = 0; f < NCF; ++f) {
-            xar[f][2 * half] = pack_bf16(pr[0] * tr[f][half][0], pr[1] * tr[f][half][1]);
-            xar[f][2 * half + 1] = pack_bf16(pr[2] * tr[f][half][2], pr[3] * tr[f][half][3]);
-            xai[f][2 * half] = pack_bf16(pr[0] * ti[f][half][0], pr[1] * ti[f][half][1]);
-            xai[f][2 * half + 1] = pack_bf16(pr[2] * ti[f][half][2], pr[3] * ti[f][half][3]);
-          }
-        }
-        accumulate_tiles<KS0, NCF, KSC, false>(acc1, xa, xar, xai, t2, pl, lane);   // out += (p tau) v
-      } else if constexpr (!PASS_S) {
-        accumulate_tiles<KS0, NCF, KSC, false>(acc1, xa, xar, xai, t1, pl, lane);   // dq += (ds tau) k
-      } else {
-        accumulate_tiles<KS0, NCF, KSC, true>(acc1, xa, xar, xai, t1, pl, lane);    // dk += (ds conj tau) q
-        accumulate_tiles<KS0, NCF, KSC, true>(acc2, ya, yar, yai, t2, pl, lane);    // dv += (p conj tau) dO
-      }
-    }
-    __syncthreads();  // everyone is done with `buf` before the stage after next is copied into it
-    cur = nxt;
-    have = have_next;
-    buf ^= 1;
-  }
-
-  // ---- epilogue
-  float inv_a = 1.f, inv_b = 1.f;
-  if constexpr (FWD) {
-    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
-    l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
-    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
-    l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
-    inv_a = l_a > 0.f ? 1.f / l_a : 0.f;
-    inv_b = l_b > 0.f ? 1.f / l_b : 0.f;
-    if (c == 0) {
-      if (c0 + tl_a < a.nlon) a.lse_out[(node0 + c0 + tl_a) * a.H + h] = l_a > 0.f ? (m_a + log2f(l_a)) * TC_LN2 : -INFINITY;
-      if (c0 + tl_b < a.nlon) a.lse_out[(node0 + c0 + tl_b) * a.H + h] = l_b > 0.f ? (m_b + log2f(l_b)) * TC_LN2 : -INFINITY;
-    }
-  }
-#pragma unroll
-  for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-    for (int x = 0; x < 4; x += 2) {
-      const int t = c0 + ((x & 2) ? tl_b : tl_a);
-      const int col = 8 * nt + 2 * c;
-      const int g0 = flat_column<KS0, NCF, KSC>(P, h, col), g1 = flat_column<KS0, NCF, KSC>(P, h, col + 1);
-      const float inv = (x & 2) ? inv_b : inv_a;
-      if (t >= a.nlon) continue;
-      __nv_bfloat16* r1 = a.res1 + (node0 + t) * a.D;
-      if (g0 >= 0 && g1 == g0 + 1 && (((node0 + t) * a.D + g0) & 1) == 0) {  // both columns: one 4-byte store
-        *reinterpret_cast<unsigned*>(r1 + g0) = pack_bf16(acc1[nt][x] * inv, acc1[nt][x + 1] * inv);
-        if constexpr (PASS_S) *reinterpret_cast<unsigned*>(a.res2 + (node0 + t) * a.D + g0) = pack_bf16(acc2[nt][x], acc2[nt][x + 1]);
-      } else {
-        if (g0 >= 0) r1[g0] = __float2bfloat16_rn(acc1[nt][x] * inv);
-        if (g1 >= 0) r1[g1] = __float2bfloat16_rn(acc1[nt][x + 1] * inv);
-        if constexpr (PASS_S) {
-          if (g0 >= 0) a.res2[(node0 + t) * a.D + g0] = __float2bfloat16_rn(acc2[nt][x]);
-          if (g1 >= 0) a.res2[(node0 + t) * a.D + g1] = __float2bfloat16_rn(acc2[nt][x + 1]);
-        }
-      }
-    }
-}
-
-// =====================================================================================================================
-// Owner-minor orientation.  The same layer with the roles of the two MMA dimensions exchanged: the staged neighbour
-// positions are the M dimension (16 per step) and a warp's owners the N dimension (8 per warp):
-//
-//   S^T   (16 positions x 8 owners)  = tile (positions x columns) * owners^T      A from shared memory, B loop-invariant registers
-//   out^T (16 columns   x 8 owners) += tile^T (columns x positions) * (P o tau)^T  A from shared memory (ldmatrix.trans), B = P^T
-//
-// * 8 owners see a window of 7 + cnt positions, so the narrow equatorial windows (cnt <= 9) take ONE step of 16
-//   positions instead of the two a 16-owner warp needs: ~1.5 x fewer computed pairs where most rows are.
-// * The imaginary Gram part uses a pre-swapped copy of the OWNERS' fragments (made once), not a per-step swap of the tile.
-// * The phase's imaginary part accumulates into a second accumulator set; the multiplication by i (the pair swap) is
-//   applied once in the epilogue, so the value tile is never swapped.
-// * Accumulators cover 8 owners: half the registers of the owner-major kernel, twice the warps per CTA.
-// * P (accumulator layout: position rows, owner columns) becomes a B operand with movmatrix (8 x 8 b16 transpose).
-// The result tile is transposed through shared memory for 16-byte stores.
+// owners per CTA = 8 x warps: 8 warps forward, 4 in the backward passes (more registers per thread, three CTAs per SM)
 constexpr int TN_WARPS(int mode) { return mode == TC_FWD ? 8 : 4; }
 constexpr int TN_ADV = 80;           // positions a chunk advances by
 constexpr int TN_ROWS = TN_ADV + 8;  // positions staged per chunk: a step of 16 may start 8 before the chunk's end
@@ -683,7 +170,6 @@ struct TnLayout {
   static constexpr int FIELD_BYTES = REAL_BYTES + NCF * CX_BYTES;
   static constexpr int ENT_BYTES = (TN_ROWS + TL) * 32;
   static constexpr int BUFFER_BYTES = align1k(2 * FIELD_BYTES + ENT_BYTES + TN_ROWS * 8);  // with the (lse, Delta) pairs of pass S
-  static constexpr int OUT_PITCH = 16 * (KS0 + NCF * KSC) + 8;  // result tile (owners x padded columns), bf16 elements per row
   static __device__ __forceinline__ int real_chunk(int r, int cb) { return r * REAL_PITCH + 16 * (cb ^ ((r >> 2) & 1)); }
   static __device__ __forceinline__ int cx_chunk(int f, int r, int cb) {
     return REAL_BYTES + f * CX_BYTES + r * CX_PITCH + 16 * (cb ^ (KSC == 2 ? (r >> 1) & 3 : (r >> 2) & 1));
@@ -708,10 +194,10 @@ __device__ __forceinline__ void mma_bf16_b2_init(float (&d)[4], const unsigned (
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]), "f"(0.f));
 }
 
-__device__ __forceinline__ void ldsm_x4_sa(unsigned (&r)[4], unsigned addr) {
+__device__ __forceinline__ void ldsm_x4(unsigned (&r)[4], unsigned addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
-__device__ __forceinline__ void ldsm_x4_trans_sa(unsigned (&r)[4], unsigned addr) {
+__device__ __forceinline__ void ldsm_x4_trans(unsigned (&r)[4], unsigned addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
 __device__ __forceinline__ float fast_exp2(float x) {  // ex2.approx: exp2(-inf) = 0, relative error ~2^-22
@@ -749,7 +235,7 @@ __device__ __forceinline__ void gram_step(const unsigned (&fb)[KS0 + NCF * KSC][
   using L = TnLayout<KS0, NCF, KSC, TL>;
   if constexpr (KS0 > 0) {
     unsigned af[4];
-    ldsm_x4_sa(af, tile + pl * L::REAL_PITCH + lo.g_real);
+    ldsm_x4(af, tile + pl * L::REAL_PITCH + lo.g_real);
     mma_bf16_b2_init(g0, af, fb[0]);
   } else {
     g0[0] = g0[1] = g0[2] = g0[3] = 0.f;
@@ -760,7 +246,7 @@ __device__ __forceinline__ void gram_step(const unsigned (&fb)[KS0 + NCF * KSC][
 #pragma unroll
     for (int sub = 0; sub < KSC; ++sub) {
       unsigned af[4];
-      ldsm_x4_sa(af, cx + lo.g_cx[sub] + f * L::CX_BYTES);
+      ldsm_x4(af, cx + lo.g_cx[sub] + f * L::CX_BYTES);
       if (sub == 0) {
         mma_bf16_b2_init(gr[f], af, fb[KS0 + f * KSC + sub]);
         mma_bf16_b2_init(gi[f], af, fs[f * KSC + sub]);
@@ -780,7 +266,7 @@ __device__ __forceinline__ void accumulate_step(float (&acc0)[4], float (&accr)[
   using L = TnLayout<KS0, NCF, KSC, TL>;
   if constexpr (KS0 > 0) {
     unsigned af[4];
-    ldsm_x4_trans_sa(af, tile + pl * L::REAL_PITCH + lo.a_real);
+    ldsm_x4_trans(af, tile + pl * L::REAL_PITCH + lo.a_real);
     mma_bf16_b2(acc0, af, x0);
   }
   const unsigned cx = tile + pl * L::CX_PITCH;
@@ -789,7 +275,7 @@ __device__ __forceinline__ void accumulate_step(float (&acc0)[4], float (&accr)[
 #pragma unroll
     for (int sub = 0; sub < KSC; ++sub) {
       unsigned af[4];
-      ldsm_x4_trans_sa(af, cx + lo.a_cx[sub] + f * L::CX_BYTES);
+      ldsm_x4_trans(af, cx + lo.a_cx[sub] + f * L::CX_BYTES);
       mma_bf16_b2(accr[f * KSC + sub], af, xr[f]);
       mma_bf16_b2(acci[f * KSC + sub], af, xi[f]);
     }
@@ -1011,130 +497,127 @@ __global__ void __launch_bounds__(32 * WARPS, WARPS == 4 ? 3 : 2) lattice_tn_ker
   __syncthreads();
   const int n_pairs = n_pairs_s;
 
-  // ---- stages = (row pair, chunk of its window), produced in order
-  struct Stage {
-    int ip, p0;       // row pair, first position of the chunk
-    int cnt, n_rows;  // window width, staged positions
-    int lon0;         // longitude of the chunk's first position (wrapped)
-    int z, ent_off;   // sample * rows + neighbour row; first table entry of the row pair
-    bool tma;         // consecutive longitudes (no wrap at the seam) and tensor maps available
+  // ---- stages = (row pair, chunk of its window), produced in order by a cursor that runs one stage ahead of the consumer
+  struct Consumed {   // what the consumer of a stage needs to know about it
+    int p0, cnt;      // first position of the chunk, window width
+    bool tma;         // staged by tensor copies (completion on the copy barrier)
   };
-  auto load_stage = [&](Stage& s) {
-    const int4 ra = *reinterpret_cast<const int4*>(&pairs_s[s.ip]);  // cnt, lo, z, lon_base
-    s.cnt = ra.x;
-    s.z = ra.z;
-    s.ent_off = pairs_s[s.ip].ent_off;
-    s.n_rows = min(TN_ROWS, TL + ra.x - 1 - s.p0);
-    int lon0 = ra.w + s.p0;
-    if (lon0 >= a.nlon) lon0 %= a.nlon;
-    s.lon0 = lon0;
-    s.tma = a.use_tma && lon0 + s.n_rows <= a.nlon;
-  };
-  auto advance = [&](Stage& s) -> bool {
-    if (s.p0 + TN_ADV < TL + s.cnt - 1) {
-      s.p0 += TN_ADV;
-    } else {
-      if (++s.ip >= n_pairs) return false;
-      s.p0 = 0;
-    }
-    load_stage(s);
-    return true;
-  };
-  // per-thread staging slots of the cp.async path: thread -> (row within a pass, 16-byte chunk); the chunk's flat column is fixed
+  int next_pair = 0, next_p0 = 0;  // the producer cursor
+  // per-thread slot of the cp.async path: thread -> (row within a pass, 16-byte chunk of the padded head row)
   constexpr int ROWS_PER_PASS = THREADS / CH;
   const int st_row = threadIdx.x / CH, st_ch = threadIdx.x - st_row * CH;
-  const int st_g0 = flat_column<KS0, NCF, KSC>(P, h, 8 * st_ch), st_g7 = flat_column<KS0, NCF, KSC>(P, h, 8 * st_ch + 7);
   const bool st_active = st_row < ROWS_PER_PASS;
-  const bool st_whole = st_g0 >= 0 && st_g7 == st_g0 + 7 && (a.D % 8 == 0) && (st_g0 % 8 == 0);  // one aligned 16-byte chunk of real columns
-  const bool st_pad = st_g0 < 0 && st_g7 < 0 && flat_column<KS0, NCF, KSC>(P, h, 8 * st_ch + 3) < 0;  // all padding (stays zero)
-  auto issue = [&](const Stage& s, int buf) {  // asynchronous copies of one stage into buffer `buf`
+  auto issue_next = [&](int buf) -> Consumed {  // asynchronous copies of the cursor's stage into buffer `buf`; advances the cursor
+    const int4 ra = *reinterpret_cast<const int4*>(&pairs_s[next_pair]);  // cnt, lo, z, lon_base
+    const int ent_off = pairs_s[next_pair].ent_off;
+    const int cnt = ra.x, z = ra.z, p0 = next_p0;
+    const int n_rows = min(TN_ROWS, TL + cnt - 1 - p0);
+    int lon0 = ra.w + p0;
+    if (lon0 >= a.nlon) lon0 %= a.nlon;
+    const bool tma = a.use_tma && lon0 + n_rows <= a.nlon;  // consecutive longitudes: no wrap at the seam
+    if (p0 + TN_ADV < TL + cnt - 1) {
+      next_p0 = p0 + TN_ADV;
+    } else {
+      ++next_pair;
+      next_p0 = 0;
+    }
     unsigned char* d1 = tile1(buf);
     unsigned char* d2 = tile2(buf);
-    if (s.tma) {
+    if (tma) {
       if (threadIdx.x == 0) {
         // the buffer was last touched through the generic proxy (ldmatrix, per-thread stores): order those first
         fence_proxy_async();
         mbar_expect_tx(&copy_bar[buf], 2u * TN_ROWS * (KS0 * L::REAL_PITCH + NCF * L::CX_PITCH));
         if constexpr (KS0 > 0) {
-          tma_load_3d(d1, &a.maps[0][0], &copy_bar[buf], P.real_off + h * 16, s.lon0, s.z);
-          tma_load_3d(d2, &a.maps[1][0], &copy_bar[buf], P.real_off + h * 16, s.lon0, s.z);
+          tma_load_3d(d1, &a.maps[0][0], &copy_bar[buf], P.real_off + h * 16, lon0, z);
+          tma_load_3d(d2, &a.maps[1][0], &copy_bar[buf], P.real_off + h * 16, lon0, z);
         }
 #pragma unroll
         for (int f = 0; f < NCF; ++f) {
-          tma_load_3d(d1 + L::REAL_BYTES + f * L::CX_BYTES, &a.maps[0][1], &copy_bar[buf], P.cf_off[f] + h * 16 * KSC, s.lon0, s.z);
-          tma_load_3d(d2 + L::REAL_BYTES + f * L::CX_BYTES, &a.maps[1][1], &copy_bar[buf], P.cf_off[f] + h * 16 * KSC, s.lon0, s.z);
+          tma_load_3d(d1 + L::REAL_BYTES + f * L::CX_BYTES, &a.maps[0][1], &copy_bar[buf], P.cf_off[f] + h * 16 * KSC, lon0, z);
+          tma_load_3d(d2 + L::REAL_BYTES + f * L::CX_BYTES, &a.maps[1][1], &copy_bar[buf], P.cf_off[f] + h * 16 * KSC, lon0, z);
         }
       }
-    } else if (st_active && !st_pad) {
-      int lon = s.lon0 + st_row;
-      if (lon >= a.nlon) lon %= a.nlon;
-      const int step = ROWS_PER_PASS % a.nlon;
-      // with tensor maps in use the buffer may hold anything beyond the window: write zeros there (copies of size 0)
-      const int rows_to_write = a.use_tma ? TN_ROWS : s.n_rows;
-      for (int pl = st_row; pl < rows_to_write; pl += ROWS_PER_PASS) {
-        const int64_t nb = ((int64_t)s.z * a.nlon + lon) * a.D;
-        const int off = L::chunk(pl, st_ch);
-        if (st_whole) {
-          const int bytes = pl < s.n_rows ? 16 : 0;
-          cp_async16(d1 + off, a.nb1 + nb + st_g0, bytes);
-          cp_async16(d2 + off, a.nb2 + nb + st_g0, bytes);
-        } else {  // a chunk that straddles padding or is misaligned: element by element (visible after the barrier)
-          unsigned short u1[8], u2[8];
+    } else if (st_active) {
+      const int st_g0 = flat_column<KS0, NCF, KSC>(P, h, 8 * st_ch), st_g7 = flat_column<KS0, NCF, KSC>(P, h, 8 * st_ch + 7);
+      const bool whole = st_g0 >= 0 && st_g7 == st_g0 + 7 && (a.D % 8 == 0) && (st_g0 % 8 == 0);  // one aligned 16-byte chunk of real columns
+      const bool pad = st_g0 < 0 && st_g7 < 0 && flat_column<KS0, NCF, KSC>(P, h, 8 * st_ch + 3) < 0;  // all padding (stays zero)
+      if (!pad) {
+        // this thread's chunk of every row: block base + row * pitch + 16 (chunk ^ swizzle(row))
+        const bool in_real = st_ch < 2 * KS0;
+        const int cc = st_ch - 2 * KS0;
+        const int blk = in_real ? 0 : L::REAL_BYTES + (cc / (2 * KSC)) * L::CX_BYTES, cb = in_real ? st_ch : cc % (2 * KSC);
+        const int pitch = in_real ? L::REAL_PITCH : L::CX_PITCH;
+        const bool wide = !in_real && KSC == 2;  // 64-byte rows
+        const __nv_bfloat16* src1 = a.nb1 + (int64_t)z * a.nlon * a.D + st_g0;
+        const __nv_bfloat16* src2 = a.nb2 + (int64_t)z * a.nlon * a.D + st_g0;
+        int lon = lon0 + st_row;
+        if (lon >= a.nlon) lon %= a.nlon;
+        const int step = ROWS_PER_PASS % a.nlon;
+        // with tensor maps in use the buffer may hold anything beyond the window: write zeros there (copies of size 0)
+        const int rows_to_write = a.use_tma ? TN_ROWS : n_rows;
+        for (int pl = st_row; pl < rows_to_write; pl += ROWS_PER_PASS) {
+          const int off = blk + pl * pitch + 16 * (cb ^ (wide ? (pl >> 1) & 3 : (pl >> 2) & 1));
+          const int64_t nb = (int64_t)lon * a.D;
+          if (whole) {
+            const int bytes = pl < n_rows ? 16 : 0;
+            cp_async16(d1 + off, src1 + nb, bytes);
+            cp_async16(d2 + off, src2 + nb, bytes);
+          } else {  // a chunk that straddles padding or is misaligned: element by element (visible after the barrier)
+            unsigned short u1[8], u2[8];
 #pragma unroll
-          for (int x = 0; x < 8; ++x) {
-            const int gx = pl < s.n_rows ? flat_column<KS0, NCF, KSC>(P, h, 8 * st_ch + x) : -1;
-            u1[x] = gx >= 0 ? __bfloat16_as_ushort(a.nb1[nb + gx]) : (unsigned short)0;
-            u2[x] = gx >= 0 ? __bfloat16_as_ushort(a.nb2[nb + gx]) : (unsigned short)0;
+            for (int x = 0; x < 8; ++x) {
+              const int gx = pl < n_rows ? flat_column<KS0, NCF, KSC>(P, h, 8 * st_ch + x) : -1;
+              u1[x] = gx >= 0 ? __bfloat16_as_ushort(src1[nb + gx - st_g0]) : (unsigned short)0;
+              u2[x] = gx >= 0 ? __bfloat16_as_ushort(src2[nb + gx - st_g0]) : (unsigned short)0;
+            }
+            *reinterpret_cast<uint4*>(d1 + off) =
+                make_uint4(u1[0] | (u1[1] << 16), u1[2] | (u1[3] << 16), u1[4] | (u1[5] << 16), u1[6] | (u1[7] << 16));
+            *reinterpret_cast<uint4*>(d2 + off) =
+                make_uint4(u2[0] | (u2[1] << 16), u2[2] | (u2[3] << 16), u2[4] | (u2[5] << 16), u2[6] | (u2[7] << 16));
           }
-          *reinterpret_cast<uint4*>(d1 + off) =
-              make_uint4(u1[0] | (u1[1] << 16), u1[2] | (u1[3] << 16), u1[4] | (u1[5] << 16), u1[6] | (u1[7] << 16));
-          *reinterpret_cast<uint4*>(d2 + off) =
-              make_uint4(u2[0] | (u2[1] << 16), u2[2] | (u2[3] << 16), u2[4] | (u2[5] << 16), u2[6] | (u2[7] << 16));
+          lon += step;
+          if (lon >= a.nlon) lon -= a.nlon;
         }
-        lon += step;
-        if (lon >= a.nlon) lon -= a.nlon;
       }
     }
     // table entries of the offsets x = p - owner the chunk can meet (clamped: validity is decided from x itself)
     float* de = entry(buf);
-    const float* ent = a.entries + (size_t)s.ent_off * 8;
+    const float* ent = a.entries + (size_t)ent_off * 8;
     static_assert(2 * (TN_ROWS + TL - 1) <= 2 * THREADS, "two guarded copies per thread cover a chunk's entries");
 #pragma unroll
     for (int it = 0; it < 2; ++it) {
       const int idx = threadIdx.x + it * THREADS;
-      if (idx < 2 * (s.n_rows + TL - 1)) {
+      if (idx < 2 * (n_rows + TL - 1)) {
         const int xi = idx >> 1, part = idx & 1;
-        const int x = min(max(xi + s.p0 - (TL - 1), 0), s.cnt - 1);
+        const int x = min(max(xi + p0 - (TL - 1), 0), cnt - 1);
         cp_async16(de + 8 * xi + 4 * part, ent + 8 * x + 4 * part, 16);
       }
     }
     if constexpr (PASS_S) {
       float* ds = stats(buf);
-      for (int idx = threadIdx.x; idx < 2 * s.n_rows; idx += THREADS) {
+      for (int idx = threadIdx.x; idx < 2 * n_rows; idx += THREADS) {
         const int pl = idx >> 1, which = idx & 1;
-        int lon = s.lon0 + pl;
+        int lon = lon0 + pl;
         if (lon >= a.nlon) lon %= a.nlon;
-        const int64_t nn = ((int64_t)s.z * a.nlon + lon) * a.H + h;
+        const int64_t nn = ((int64_t)z * a.nlon + lon) * a.H + h;
         cp_async4(ds + 2 * pl + which, (which ? a.delta : a.lse) + nn, 4);
       }
     }
     cp_async_commit();
+    return Consumed{p0, cnt, tma};
   };
 
-  Stage cur;
-  cur.ip = 0; cur.p0 = 0;
   bool have = n_pairs > 0;
   int buf = 0;
   unsigned parity = 0;  // bit b: the phase of copy_bar[b] the next TMA stage into buffer b completes
-  if (have) {
-    load_stage(cur);
-    issue(cur, 0);
-  }
+  Consumed cur{0, 0, false};
+  if (have) cur = issue_next(0);
   while (have) {
-    Stage nxt = cur;
-    const bool have_next = advance(nxt);
+    const bool have_next = next_pair < n_pairs;
+    Consumed nxt{0, 0, false};
     if (have_next) {
-      issue(nxt, buf ^ 1);
+      nxt = issue_next(buf ^ 1);
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
@@ -1408,32 +891,6 @@ bool encode_field_map(CUtensorMap* map, const void* field, int D, int nlon, int6
 }
 
 template <int KS0, int NCF, int KSC, int MODE>
-int launch_tc(TcArgs& a, int n_order_rows, int64_t batch, cudaStream_t stream) {
-  using L = TcLayout<KS0, NCF, KSC>;
-  // TMA staging needs blocks of exactly 16 / 16 KSC columns starting on 16-byte boundaries, rows of a multiple of 16 bytes,
-  // and at least one chunk of longitudes; everything else is staged by the threads.
-  bool tma = !tma_disabled() && a.D % 8 == 0 && a.nlon >= TC_SC && batch * a.rows < (1ll << 31) && (KS0 == 0 || (a.plan.a0 == 16 && a.plan.real_off % 8 == 0)) &&
-             2 * a.plan.ac == 16 * KSC && reinterpret_cast<uintptr_t>(a.nb1) % 16 == 0 && reinterpret_cast<uintptr_t>(a.nb2) % 16 == 0;
-  for (int f = 0; f < a.plan.n_cf; ++f) tma = tma && a.plan.cf_off[f] % 8 == 0;
-  if (tma) {
-    const void* fields[2] = {a.nb1, a.nb2};
-    for (int x = 0; x < 2 && tma; ++x) {
-      if (KS0 > 0) tma = tma && encode_field_map(&a.maps[x][0], fields[x], a.D, a.nlon, batch * a.rows, 16, TC_SC);
-      tma = tma && encode_field_map(&a.maps[x][1], fields[x], a.D, a.nlon, batch * a.rows, 16 * KSC, TC_SC);
-    }
-  }
-  a.use_tma = tma ? 1 : 0;
-  const size_t smem = 2 * (size_t)L::BUFFER_BYTES + 1024;
-  auto kernel = lattice_tc_kernel<KS0, NCF, KSC, MODE>;
-  int st = allow_smem(kernel, smem, "gm_lattice_attention (tensor cores)");
-  if (st != GM_OK) return st;
-  const int tiles = (a.nlon + TC_TL - 1) / TC_TL;
-  dim3 grid((unsigned)(n_order_rows * tiles), (unsigned)a.H, (unsigned)batch);
-  kernel<<<grid, TC_THREADS, smem, stream>>>(a);
-  return launch_status("gm_lattice_attention (tensor cores)");
-}
-
-template <int KS0, int NCF, int KSC, int MODE>
 int launch_tn(TcArgs& a, int n_order_rows, int64_t batch, cudaStream_t stream) {
   constexpr int WARPS = TN_WARPS(MODE), TL = 8 * WARPS;
   using L = TnLayout<KS0, NCF, KSC, TL>;
@@ -1463,30 +920,17 @@ int launch_tn(TcArgs& a, int n_order_rows, int64_t batch, cudaStream_t stream) {
   return launch_status("gm_lattice_attention (tensor cores)");
 }
 
-bool legacy_orientation() {
-  const char* v = getenv("GM_LATTICE_TC_OWNER_MAJOR");
-  return v && v[0] == '1';
-}
-
 template <int MODE>
 int dispatch_tc(TcArgs& a, int n_order_rows, int64_t batch, cudaStream_t cs) {
   const int ks0 = a.plan.a0 > 0 ? 1 : 0, ksc = a.plan.ac > 8 ? 2 : 1, ncf = a.plan.n_cf;
-  if (!legacy_orientation()) {
-    for (int f = 0; f < ncf; ++f)
-      GM_REQUIRE(a.plan.cf_order[f] == f + 1, GM_ERR_UNSUPPORTED, "gm_lattice_attention (tensor cores): complex frequencies must be the orders 1 .. %d", ncf);
-    if (ks0 == 1 && ncf == 2 && ksc == 2) return launch_tn<1, 2, 2, MODE>(a, n_order_rows, batch, cs);
-    if (ks0 == 1 && ncf == 2 && ksc == 1) return launch_tn<1, 2, 1, MODE>(a, n_order_rows, batch, cs);
-    if (ks0 == 1 && ncf == 3 && ksc == 1) return launch_tn<1, 3, 1, MODE>(a, n_order_rows, batch, cs);
-    if (ks0 == 1 && ncf == 1 && ksc == 2) return launch_tn<1, 1, 2, MODE>(a, n_order_rows, batch, cs);
-    if (ks0 == 1 && ncf == 1 && ksc == 1) return launch_tn<1, 1, 1, MODE>(a, n_order_rows, batch, cs);
-    if (ks0 == 0 && ncf == 2 && ksc == 1) return launch_tn<0, 2, 1, MODE>(a, n_order_rows, batch, cs);
-  }
-  if (ks0 == 1 && ncf == 2 && ksc == 2) return launch_tc<1, 2, 2, MODE>(a, n_order_rows, batch, cs);
-  if (ks0 == 1 && ncf == 2 && ksc == 1) return launch_tc<1, 2, 1, MODE>(a, n_order_rows, batch, cs);
-  if (ks0 == 1 && ncf == 3 && ksc == 1) return launch_tc<1, 3, 1, MODE>(a, n_order_rows, batch, cs);
-  if (ks0 == 1 && ncf == 1 && ksc == 2) return launch_tc<1, 1, 2, MODE>(a, n_order_rows, batch, cs);
-  if (ks0 == 1 && ncf == 1 && ksc == 1) return launch_tc<1, 1, 1, MODE>(a, n_order_rows, batch, cs);
-  if (ks0 == 0 && ncf == 2 && ksc == 1) return launch_tc<0, 2, 1, MODE>(a, n_order_rows, batch, cs);
+  for (int f = 0; f < ncf; ++f)
+    GM_REQUIRE(a.plan.cf_order[f] == f + 1, GM_ERR_UNSUPPORTED, "gm_lattice_attention (tensor cores): complex frequencies must be the orders 1 .. %d", ncf);
+  if (ks0 == 1 && ncf == 2 && ksc == 2) return launch_tn<1, 2, 2, MODE>(a, n_order_rows, batch, cs);
+  if (ks0 == 1 && ncf == 2 && ksc == 1) return launch_tn<1, 2, 1, MODE>(a, n_order_rows, batch, cs);
+  if (ks0 == 1 && ncf == 3 && ksc == 1) return launch_tn<1, 3, 1, MODE>(a, n_order_rows, batch, cs);
+  if (ks0 == 1 && ncf == 1 && ksc == 2) return launch_tn<1, 1, 2, MODE>(a, n_order_rows, batch, cs);
+  if (ks0 == 1 && ncf == 1 && ksc == 1) return launch_tn<1, 1, 1, MODE>(a, n_order_rows, batch, cs);
+  if (ks0 == 0 && ncf == 2 && ksc == 1) return launch_tn<0, 2, 1, MODE>(a, n_order_rows, batch, cs);
   return fail(GM_ERR_UNSUPPORTED, "gm_lattice_attention (tensor cores): no kernel for this head layout (a0=%d, %d x %d complex)",
               a.plan.a0, ncf, a.plan.ac);
 }
