@@ -383,11 +383,11 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
                 b_ev.record()
             torch.cuda.synchronize()
             per_pass[name] = statistics.mean(x.elapsed_time(y) for x, y in ev[1:])
-        top_kernel = "lattice_tc_kernel<1,2,2,TC_BWD_S> (source-major backward pass: dk, dv)"
+        top_kernel = "lattice_tn_kernel<1,2,2,TC_BWD_S,4> (source-major backward pass: dk, dv)"
         top_ms = per_pass["pass_s"]
         top_bytes = 6 * n_rows_local * D * elem + 2 * n_rows_local * heads * 4
         # DRAM read + write of this kernel per node, from the ncu capture on the 128x256x4 workload (profiles/), scaled by nodes
-        top_traffic = int(4484 * n_rows_local)
+        top_traffic = int(4851 * n_rows_local)
         del out0, lse0, ws
     else:
         per_pass = None

@@ -42,6 +42,7 @@ SIGNATURES: dict[str, list[Any]] = {
     "gm_factored_backward": [_P] * 15 + [_L, _L, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P],
     "gm_pairs_forward": [_P] * 8 + [_L, _I, _I, _I, _I, _I, _P],
     "gm_pairs_backward": [_P] * 11 + [_L, _I, _I, _I, _I, _I, _P],
+    "gm_lattice_attention_tc_wait_expired": [_P],
     "gm_attention_backward_static": [_P] * 12 + [_L, _L, _L, _I, _I, _I, _I, _D, _I, _P, _P, _P, _P],
 }
 #: entry points that return a size instead of a status

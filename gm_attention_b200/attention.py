@@ -272,11 +272,14 @@ def _check_lattice(q: Tensor, k: Tensor, v: Tensor, t: LatticeTables) -> tuple[t
 
 def tensor_core_layout_supported(rows: tuple[tuple[int, int, int, int, int], ...]) -> bool:
     """Head layouts of the tensor-core lattice kernels: an optional scalar block of <= 16 copies and one
-    to three complex frequencies sharing a multiplicity <= 16 (the instantiated combinations)."""
+    to three complex frequencies of orders 1, 2, 3 sharing a multiplicity <= 16 (the instantiated combinations)."""
     scalar = [a for n, a, *_ in rows if n == 0]
     mult = {a for n, a, *_ in rows if n > 0}
-    n_cf = sum(1 for n, *_ in rows if n > 0)
+    orders = sorted(n for n, *_ in rows if n > 0)
+    n_cf = len(orders)
     if len(scalar) > 1 or len(mult) != 1 or (scalar and scalar[0] > 16) or next(iter(mult)) > 16:
+        return False
+    if orders != list(range(1, n_cf + 1)):
         return False
     ksc = 2 if next(iter(mult)) > 8 else 1
     return (bool(scalar), n_cf, ksc) in {(True, 2, 2), (True, 2, 1), (True, 3, 1), (True, 1, 2), (True, 1, 1), (False, 2, 1)}

@@ -857,11 +857,8 @@ int make_tc_plan(const int64_t* desc_host, int F, int H, int D, TcPlan& P) {
 
 // GM_LATTICE_TMA=0 stages every chunk with per-thread copies (for comparing the two staging paths)
 bool tma_disabled() {
-  static const bool off = [] {
-    const char* v = getenv("GM_LATTICE_TMA");
-    return v && v[0] == '0';
-  }();
-  return off;
+  const char* v = getenv("GM_LATTICE_TMA");
+  return v && v[0] == '0';
 }
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link against the driver library)
@@ -1035,4 +1032,10 @@ extern "C" int gm_lattice_attention_backward_tc_passes(const void* dout, const v
     status = dispatch_tc<TC_BWD_S>(a, t_n_order_rows, batch, cs);
   }
   return status;
+}
+
+extern "C" int gm_lattice_attention_tc_wait_expired(int* expired) {
+  GM_REQUIRE(expired, GM_ERR_ARGUMENT, "gm_lattice_attention_tc_wait_expired: null pointer");
+  GM_CUDA(cudaMemcpyFromSymbol(expired, g_tc_wait_expired, sizeof(int)));
+  return GM_OK;
 }

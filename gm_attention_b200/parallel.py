@@ -222,13 +222,15 @@ def row_pair_counts(lattice, radius: float) -> Tensor:
 
 
 def tensor_core_row_cost(pair_counts: Tensor) -> list[float]:
-    """Relative cost of one lattice row under the tensor-core lattice kernels.  A warp owns 16 consecutive owners and
-    walks, for every neighbour row, the 15 + cnt positions their windows cover: Gram + elementwise work per 8 positions,
-    softmax + value accumulation per 16, plus a fixed cost per staged row pair.  Narrow equatorial windows therefore cost
-    several times more PER EDGE than whole-row polar windows, which an edge-count balance ignores."""
+    """Relative cost of one lattice row under the tensor-core lattice kernels (forward + both backward passes).
+    A warp owns 8 consecutive owners and walks, for every neighbour row, the 7 + cnt positions their windows cover in
+    steps of 16; a CTA stages the neighbour row in chunks of 80 positions (64 owners forward, 32 in the backward
+    passes) and pays a fixed cost per owner tile.  The weights are a fit to measured times of row groups from the pole
+    to the equator of a 256 x 512 lattice (within 15 % for every group).  Narrow equatorial windows cost several times
+    more PER EDGE than whole-row polar windows, which an edge-count balance ignores."""
     cnt = pair_counts.to(torch.float64)
     present = cnt > 0
-    halves = torch.ceil((15 + cnt) / 8)
-    steps = torch.ceil((15 + cnt) / 16)
-    cost = torch.where(present, 150.0 * halves + 115.0 * steps + 150.0, torch.zeros_like(cnt))
-    return cost.sum(1).tolist()
+    steps = torch.ceil((7 + cnt) / 16)
+    chunks = torch.ceil((63 + cnt) / 80) + torch.ceil((31 + cnt) / 80)
+    cost = torch.where(present, 7.1 * steps + 2.9 * chunks, torch.zeros_like(cnt))
+    return (10.0 + cost.sum(1)).tolist()

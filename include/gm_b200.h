@@ -274,10 +274,13 @@ int gm_pairs_backward(const void* hidden, const void* weight, const void* bias, 
  * Tensor-core variants of the lattice fast path for bf16 node fields (same
  * tables, same results within bf16 rounding of the attention weights): the
  * per-frequency Gram blocks and the (alpha o tau) V sums run as m16n8k16 bf16
- * matrix products on 16 x 16 (target, source) tiles of the longitude band.
- * Head layouts: an optional scalar block of <= 16 copies and up to three complex
- * frequencies sharing one multiplicity <= 16; otherwise GM_ERR_UNSUPPORTED (use
- * gm_lattice_attention_forward).
+ * matrix products on (16 source positions x 8 targets) tiles of the longitude
+ * band; neighbour rows are staged with TMA tensor copies where the head's
+ * blocks are exactly 16 / 32 columns wide, with per-thread copies otherwise
+ * (environment GM_LATTICE_TMA=0 forces the latter; same results bit for bit).
+ * Head layouts: an optional scalar block of <= 16 copies and one to three complex
+ * frequencies of orders 1, 2, 3 sharing one multiplicity <= 16; otherwise
+ * GM_ERR_UNSUPPORTED (use gm_lattice_attention_forward).
  * ------------------------------------------------------------------------ */
 int gm_lattice_attention_backward_tc(const void* dout, const void* q, const void* k, const void* v, const void* out, const float* lse,
                                      const int* win_cnt, const int* win_lo, const int* win_off, const float* entries,
@@ -295,6 +298,12 @@ int gm_lattice_attention_backward_tc_passes(const void* dout, const void* q, con
                                             int t_n_order_rows, const int64_t* desc_host, int F, int rows, int nlon, int64_t batch,
                                             int D, int H, int W, int ES, int NORD, double scale, void* dq, void* dk, void* dv,
                                             float* delta, int passes, void* stream);
+
+/* Health flag of the tensor-core lattice kernels (no counterpart in the reference).  Their waits on the
+ * completion barriers of the TMA copies are bounded; a wait that runs out sets a per-device flag and the
+ * launch's results are invalid.  Writes the flag of the current device to *expired (0: never happened);
+ * synchronises the device. */
+int gm_lattice_attention_tc_wait_expired(int* expired);
 
 int gm_lattice_attention_forward_tc(const void* q, const void* k, const void* v, const int* win_cnt, const int* win_lo,
                                     const int* win_off, const float* entries, const int* row_order, int n_order_rows,

@@ -113,7 +113,10 @@ def test_lattice_through_autograd_and_unsupported_layout():
     assert lattice_layout_supported(lat.desc_rows)
 
 
-TC_CASES = [CASES[0], CASES[1], CASES[2], CASES[3], CASES[4], (8, 16, 2 * math.pi / 8, {1: 6, 2: 6}, 1, "hard", 2)]
+#: headline head layout on a lattice wide enough for the TMA staging path: tiles that wrap the longitude seam and
+#: tiles that do not, windows from a few positions (one staged chunk) to whole rows (several chunks)
+TMA_CASE = (6, 256, 1.2 * math.pi / 6, {0: 16, 1: 16, 2: 16}, 2, "hard", 2)
+TC_CASES = [CASES[0], CASES[1], CASES[2], CASES[3], CASES[4], (8, 16, 2 * math.pi / 8, {1: 6, 2: 6}, 1, "hard", 2), TMA_CASE]
 
 
 @pytest.mark.parametrize("case", TC_CASES)
@@ -156,6 +159,31 @@ def test_tensor_core_backward_bf16(case):
     for name, a, b, a2 in zip(("dq", "dk", "dv"), got, grads, again):
         assert rel_err(a.float().cpu().numpy(), b) < 2e-2, name
         assert torch.equal(a, a2), name
+
+
+def test_tma_staging_equals_per_thread_staging(monkeypatch):
+    """The two staging paths of the tensor-core kernels (TMA tensor copies; per-thread cp.async) feed the same
+    arithmetic: results are bit-identical, and no wait on a copy barrier ever ran out."""
+    import ctypes
+
+    from gm_attention_b200 import _lib
+    from gm_attention_b200.attention import lattice_attention_backward, lattice_attention_forward
+
+    batch = TMA_CASE[6]
+    c = make_case(*TMA_CASE[:5], dtype=np.float32, window=TMA_CASE[5])
+    _, lat = tables_for(c)
+    Q, K, V, G = (torch.from_numpy(x).bfloat16().cuda() for x in seeded((batch * c.n_nodes, c.width), 60, np.float32, 4))
+    results = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("GM_LATTICE_TMA", mode)
+        out, lse = lattice_attention_forward(Q, K, V, lat, tensor_cores=True)
+        results[mode] = (out, lse, *lattice_attention_backward(G, Q, K, V, out, lse, lat, tensor_cores=True))
+    for a, b in zip(results["1"], results["0"]):
+        assert torch.equal(a, b)
+    assert torch.isfinite(results["1"][0].float()).all()
+    expired = ctypes.c_int(-1)
+    _lib.call("gm_lattice_attention_tc_wait_expired", ctypes.byref(expired))
+    assert expired.value == 0
 
 
 def test_host_pipeline_equals_the_device_path():
