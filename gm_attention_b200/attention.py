@@ -361,10 +361,16 @@ class HostPipeline:
         shape = (chunk * n, width)
         self.inputs = [[torch.empty(shape, dtype=dtype, device=device) for _ in range(4)] for _ in range(2)]
         self.streams = [torch.cuda.Stream(device) for _ in range(3)]  # h2d, compute, d2h
+        self.consumed: list[Any] = [None, None]  # per staging slot: the compute that last read it has finished
         self.lattice = isinstance(tables, LatticeTables)
 
-    def run(self, q: Tensor, k: Tensor, v: Tensor, dout: Tensor, out: Tensor, dq: Tensor, dk: Tensor, dv: Tensor) -> None:
-        """All arguments are host tensors ``(batch * n_nodes, D)`` (pinned for overlap); the last four are written."""
+    def run(self, q: Tensor, k: Tensor, v: Tensor, dout: Tensor, out: Tensor, dq: Tensor, dk: Tensor, dv: Tensor,
+            wait: bool = True) -> None:
+        """All arguments are host tensors ``(batch * n_nodes, D)`` (pinned for overlap); the last four are written.
+
+        ``wait=True``: the caller's current stream waits for the results (they are valid once that stream has
+        synchronised).  ``wait=False`` only enqueues: back-to-back calls then overlap (the first copies of one call
+        run under the last compute and write-back of the previous one); call :meth:`join` before reading results."""
         fwd = lattice_attention_forward if self.lattice else attention_forward
         bwd = lattice_attention_backward if self.lattice else attention_backward
         h2d, comp, d2h = self.streams
@@ -375,14 +381,12 @@ class HostPipeline:
             s.wait_stream(main)
         loaded = [torch.cuda.Event() for _ in range(n_chunks)]
         computed = [torch.cuda.Event() for _ in range(n_chunks)]
-        stored = [torch.cuda.Event() for _ in range(n_chunks)]
-        results: list[tuple[Tensor, ...]] = [()] * n_chunks
         for i in range(n_chunks):
             sl = slice(i * rows, (i + 1) * rows)
             slot = self.inputs[i % 2]
             with torch.cuda.stream(h2d):
-                if i >= 2:
-                    h2d.wait_event(computed[i - 2])  # the slot's previous occupant has been consumed
+                if self.consumed[i % 2] is not None:
+                    h2d.wait_event(self.consumed[i % 2])  # the slot's previous occupant (this call's or the last one's) has been consumed
                 for dst, src in zip(slot, (q, k, v, dout)):
                     dst.copy_(src[sl], non_blocking=True)
                 loaded[i].record(h2d)
@@ -395,13 +399,18 @@ class HostPipeline:
                 grads = bwd(slot[3], slot[0], slot[1], slot[2], o, lse, self.tables)
                 if self.halo is not None:
                     self.halo.reduce_halos(grads[1].view(banded), grads[2].view(banded))
-                results[i] = (o, *grads)
                 computed[i].record(comp)
+                self.consumed[i % 2] = computed[i]
             with torch.cuda.stream(d2h):
                 d2h.wait_event(computed[i])
-                for dst, src in zip((out, dq, dk, dv), results[i]):
+                for dst, src in zip((out, dq, dk, dv), (o, *grads)):
                     dst[sl].copy_(src, non_blocking=True)
                     src.record_stream(d2h)
-                stored[i].record(d2h)
+        if wait:
+            self.join()
+
+    def join(self) -> None:
+        """Make the caller's current stream wait for everything enqueued so far."""
+        main = torch.cuda.current_stream(self.device)
         for s in self.streams:
             main.wait_stream(s)

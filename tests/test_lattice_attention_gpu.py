@@ -199,6 +199,12 @@ def test_host_pipeline_equals_the_device_path():
     for _ in range(2):  # the second run reuses the staging buffers
         pipe.run(*host, *outs)
         torch.cuda.synchronize()
+    for x in outs:
+        x.zero_()
+    for _ in range(3):  # enqueue-only calls overlap one another; join before reading
+        pipe.run(*host, *outs, wait=False)
+    pipe.join()
+    torch.cuda.synchronize()
     Q, K, V, G = (x.cuda() for x in host)
     out, lse = lattice_attention_forward(Q, K, V, lat)
     want = (out, *lattice_attention_backward(G, Q, K, V, out, lse, lat))
