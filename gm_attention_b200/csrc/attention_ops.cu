@@ -268,97 +268,246 @@ __device__ __forceinline__ T rho_power(T rho, int n) {  // (r / c)^{2n} by repea
   return s;
 }
 
+// One work item of the depthwise conv = one copy of one frequency: a scalar column, or a (re, im) column pair.
+struct ConvItem {
+  int col;    // flat column (of the real part)
+  int order;  // frequency n
+  int coef;   // index into a row of rc (n = 0) / of cc: A at coef, B at coef + 2 mult (n > 0)
+  int mult;
+};
+
+template <typename T> struct Pair;
+template <> struct Pair<float> { using type = float2; };
+template <> struct Pair<double> { using type = double2; };
+
+// (x, y) at p: one vector access when the address allows it (decided from the address itself), two scalar ones otherwise
+template <typename T>
+__device__ __forceinline__ void load_pair(const T* p, T& x, T& y) {
+  if ((reinterpret_cast<uintptr_t>(p) & (2 * sizeof(T) - 1)) == 0) {
+    const typename Pair<T>::type t = *reinterpret_cast<const typename Pair<T>::type*>(p);
+    x = t.x; y = t.y;
+  } else {
+    x = p[0]; y = p[1];
+  }
+}
+template <typename T>
+__device__ __forceinline__ void store_pair(T* p, T x, T y) {
+  if ((reinterpret_cast<uintptr_t>(p) & (2 * sizeof(T) - 1)) == 0) {
+    typename Pair<T>::type t;
+    t.x = x; t.y = y;
+    *reinterpret_cast<typename Pair<T>::type*>(p) = t;
+  } else {
+    p[0] = x; p[1] = y;
+  }
+}
+
+// The items of the (single-head) descriptor, in column order, into shared memory; returns their number.
+__device__ __forceinline__ int build_conv_items(const int64_t* desc, int F, ConvItem* items_s) {
+  int total = 0;
+  for (int f = 0; f < F; ++f) {
+    const int64_t* row = desc + f * DESC;
+    const int n = (int)row[0], a_n = (int)row[1], off = (int)row[2], coff = (int)row[3], dim = (int)row[4];
+    for (int x = threadIdx.x; x < a_n; x += blockDim.x)
+      items_s[total + x] = ConvItem{off + dim * x, n, n == 0 ? x : coff + 2 * x, a_n};
+    total += a_n;
+  }
+  return total;
+}
+
+// Depthwise conv, forward: a warp per target node, a lane per item (scalar items and complex items in separate
+// passes, so a pass never diverges); the node's edges are walked in order -- same summation order per output as a
+// sequential loop -- four at a time, with the four edges' loads issued before their arithmetic.
+constexpr int CONV_UNROLL = 4;
+
 template <typename T>
 __global__ void conv_forward_kernel(ConvArgs<T> a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  ColumnSlot* slot_s = reinterpret_cast<ColumnSlot*>(smem_raw);
-  for (int c = threadIdx.x; c < a.D; c += blockDim.x) slot_s[c] = decode_column(a.desc, a.F, 1, c);
+  ConvItem* items_s = reinterpret_cast<ConvItem*>(smem_raw);
+  const int n_items = build_conv_items(a.desc, a.F, items_s);
   __syncthreads();
-  for (int64_t i = blockIdx.x; i < a.n_nodes; i += gridDim.x) {
+  int n_real = 0;  // items are in column order: the scalar block (frequency 0) first
+  while (n_real < n_items && items_s[n_real].order == 0) ++n_real;
+  const int lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  for (int64_t i = (int64_t)blockIdx.x * warps + (threadIdx.x >> 5); i < a.n_nodes; i += (int64_t)gridDim.x * warps) {
     const int64_t e0 = a.row_ptr[i], e1 = a.row_ptr[i + 1];
-    for (int c = threadIdx.x; c < a.D; c += blockDim.x) {
-      const ColumnSlot s = slot_s[c];
+    for (int t0 = 0; t0 < n_real; t0 += 32) {
+      if (t0 + lane >= n_real) continue;
+      const ConvItem it = items_s[t0 + lane];
       T y = T(0);
-      if (s.order == 0) {
-        for (int64_t e = e0; e < e1; ++e) y += a.weights[e] * (a.rc[e * a.A0 + s.copy] * a.v[a.source[e] * a.D + c]);
-      } else if (s.order > 0) {
-        const int n = s.order, re = s.partner > 0 ? c : c - 1;
-        for (int64_t e = e0; e < e1; ++e) {
-          const T* v_j = a.v + a.source[e] * a.D;
-          const T tr = a.transport[(e * a.orders + n) * 2], ti = a.transport[(e * a.orders + n) * 2 + 1];
-          const T vr = v_j[re], vi = v_j[re + 1];
-          const T zr = tr * vr - ti * vi, zi = tr * vi + ti * vr;  // z = tau v
-          const T* co = a.cc + e * a.W + s.coff;
-          const T Ar = co[2 * s.copy], Ai = co[2 * s.copy + 1];
-          const T Br = co[2 * s.mult + 2 * s.copy], Bi = co[2 * s.mult + 2 * s.copy + 1];
-          const T p = rho_power(a.rho[e], n);
-          const T wr = p * a.angular[(e * a.orders + 2 * n) * 2], wi = p * a.angular[(e * a.orders + 2 * n) * 2 + 1];
-          // m = A z + w (B conj z)
-          const T bzr = Br * zr + Bi * zi, bzi = Bi * zr - Br * zi;
-          const T mr = (Ar * zr - Ai * zi) + (wr * bzr - wi * bzi);
-          const T mi = (Ar * zi + Ai * zr) + (wr * bzi + wi * bzr);
-          y += a.weights[e] * (s.partner > 0 ? mr : mi);
+      int64_t e = e0;
+      for (; e + CONV_UNROLL <= e1; e += CONV_UNROLL) {
+        T w[CONV_UNROLL], r[CONV_UNROLL], x[CONV_UNROLL];
+#pragma unroll
+        for (int u = 0; u < CONV_UNROLL; ++u) {
+          w[u] = a.weights[e + u];
+          r[u] = a.rc[(e + u) * a.A0 + it.coef];
+          x[u] = a.v[a.source[e + u] * a.D + it.col];
         }
+#pragma unroll
+        for (int u = 0; u < CONV_UNROLL; ++u) y += w[u] * (r[u] * x[u]);
       }
-      a.out[i * a.D + c] = y;
+      for (; e < e1; ++e) y += a.weights[e] * (a.rc[e * a.A0 + it.coef] * a.v[a.source[e] * a.D + it.col]);
+      a.out[i * a.D + it.col] = y;
+    }
+    for (int t0 = n_real; t0 < n_items; t0 += 32) {
+      if (t0 + lane >= n_items) continue;
+      const ConvItem it = items_s[t0 + lane];
+      const int n = it.order;
+      T yr = T(0), yi = T(0);
+      auto message = [&](T w_e, T rho, T tr, T ti, T vr, T vi, T Ar, T Ai, T Br, T Bi, T ar, T ai) {
+        const T zr = tr * vr - ti * vi, zi = tr * vi + ti * vr;  // z = tau v
+        const T p = rho_power(rho, n);
+        const T wr = p * ar, wi = p * ai;
+        // m = A z + w (B conj z)
+        const T bzr = Br * zr + Bi * zi, bzi = Bi * zr - Br * zi;
+        const T mr = (Ar * zr - Ai * zi) + (wr * bzr - wi * bzi);
+        const T mi = (Ar * zi + Ai * zr) + (wr * bzi + wi * bzr);
+        yr += w_e * mr;
+        yi += w_e * mi;
+      };
+      int64_t e = e0;
+      for (; e + CONV_UNROLL <= e1; e += CONV_UNROLL) {
+        T w[CONV_UNROLL], rho[CONV_UNROLL], tr[CONV_UNROLL], ti[CONV_UNROLL], vr[CONV_UNROLL], vi[CONV_UNROLL];
+        T Ar[CONV_UNROLL], Ai[CONV_UNROLL], Br[CONV_UNROLL], Bi[CONV_UNROLL], ar[CONV_UNROLL], ai[CONV_UNROLL];
+#pragma unroll
+        for (int u = 0; u < CONV_UNROLL; ++u) {
+          const int64_t eu = e + u;
+          w[u] = a.weights[eu];
+          rho[u] = a.rho[eu];
+          load_pair(a.v + a.source[eu] * a.D + it.col, vr[u], vi[u]);
+          load_pair(a.transport + (eu * a.orders + n) * 2, tr[u], ti[u]);
+          load_pair(a.angular + (eu * a.orders + 2 * n) * 2, ar[u], ai[u]);
+          const T* co = a.cc + eu * a.W + it.coef;
+          load_pair(co, Ar[u], Ai[u]);
+          load_pair(co + 2 * it.mult, Br[u], Bi[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < CONV_UNROLL; ++u) message(w[u], rho[u], tr[u], ti[u], vr[u], vi[u], Ar[u], Ai[u], Br[u], Bi[u], ar[u], ai[u]);
+      }
+      for (; e < e1; ++e) {
+        T tr, ti, vr, vi, Ar, Ai, Br, Bi, ar, ai;
+        load_pair(a.transport + (e * a.orders + n) * 2, tr, ti);
+        load_pair(a.v + a.source[e] * a.D + it.col, vr, vi);
+        const T* co = a.cc + e * a.W + it.coef;
+        load_pair(co, Ar, Ai);
+        load_pair(co + 2 * it.mult, Br, Bi);
+        load_pair(a.angular + (e * a.orders + 2 * n) * 2, ar, ai);
+        message(a.weights[e], a.rho[e], tr, ti, vr, vi, Ar, Ai, Br, Bi, ar, ai);
+      }
+      store_pair(a.out + i * a.D + it.col, yr, yi);
     }
   }
 }
 
+// Backward: same walk and grouping; the edge-owned coefficient gradients are written once, dv is accumulated atomically.
 template <typename T>
 __global__ void conv_backward_kernel(ConvArgs<T> a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  T* dy_s = reinterpret_cast<T*>(smem_raw);
-  ColumnSlot* slot_s = reinterpret_cast<ColumnSlot*>(dy_s + a.D);
-  for (int c = threadIdx.x; c < a.D; c += blockDim.x) slot_s[c] = decode_column(a.desc, a.F, 1, c);
-  for (int64_t i = blockIdx.x; i < a.n_nodes; i += gridDim.x) {
+  ConvItem* items_s = reinterpret_cast<ConvItem*>(smem_raw);
+  const int n_items = build_conv_items(a.desc, a.F, items_s);
+  __syncthreads();
+  int n_real = 0;
+  while (n_real < n_items && items_s[n_real].order == 0) ++n_real;
+  const int lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  for (int64_t i = (int64_t)blockIdx.x * warps + (threadIdx.x >> 5); i < a.n_nodes; i += (int64_t)gridDim.x * warps) {
     const int64_t e0 = a.row_ptr[i], e1 = a.row_ptr[i + 1];
-    __syncthreads();
-    for (int c = threadIdx.x; c < a.D; c += blockDim.x) dy_s[c] = a.g[i * a.D + c];
-    __syncthreads();
-    for (int c = threadIdx.x; c < a.D; c += blockDim.x) {
-      const ColumnSlot s = slot_s[c];
-      if (s.order == 0) {
-        const T dy = dy_s[c];
-        for (int64_t e = e0; e < e1; ++e) {
-          const int64_t j = a.source[e];
-          const T dm = a.weights[e] * dy;
-          a.drc[e * a.A0 + s.copy] = dm * a.v[j * a.D + c];
-          atomicAdd(a.dv + j * a.D + c, dm * a.rc[e * a.A0 + s.copy]);
+    for (int t0 = 0; t0 < n_real; t0 += 32) {
+      if (t0 + lane >= n_real) continue;
+      const ConvItem it = items_s[t0 + lane];
+      const T dy = a.g[i * a.D + it.col];
+      int64_t e = e0;
+      for (; e + CONV_UNROLL <= e1; e += CONV_UNROLL) {
+        T w[CONV_UNROLL], r[CONV_UNROLL], x[CONV_UNROLL];
+        int64_t j[CONV_UNROLL];
+#pragma unroll
+        for (int u = 0; u < CONV_UNROLL; ++u) {
+          j[u] = a.source[e + u];
+          w[u] = a.weights[e + u];
+          r[u] = a.rc[(e + u) * a.A0 + it.coef];
+          x[u] = a.v[j[u] * a.D + it.col];
         }
-      } else if (s.order > 0) {
-        const int n = s.order, re = s.partner > 0 ? c : c - 1;
-        const bool real_part = s.partner > 0;
-        const T dyr = dy_s[re], dyi = dy_s[re + 1];
-        for (int64_t e = e0; e < e1; ++e) {
-          const int64_t j = a.source[e];
-          const T* v_j = a.v + j * a.D;
-          const T tr = a.transport[(e * a.orders + n) * 2], ti = a.transport[(e * a.orders + n) * 2 + 1];
-          const T vr = v_j[re], vi = v_j[re + 1];
-          const T zr = tr * vr - ti * vi, zi = tr * vi + ti * vr;
-          const int64_t ci = e * a.W + s.coff + 2 * s.copy;
-          const T Ar = a.cc[ci], Ai = a.cc[ci + 1];
-          const T Br = a.cc[ci + 2 * s.mult], Bi = a.cc[ci + 2 * s.mult + 1];
-          const T p = rho_power(a.rho[e], n);
-          const T wr = p * a.angular[(e * a.orders + 2 * n) * 2], wi = p * a.angular[(e * a.orders + 2 * n) * 2 + 1];
-          const T w_e = a.weights[e];
-          const T dmr = w_e * dyr, dmi = w_e * dyi;
-          // dA = dm conj(z); dB = (dm conj(w)) z
-          const T dAr = dmr * zr + dmi * zi, dAi = dmi * zr - dmr * zi;
-          const T cr = dmr * wr + dmi * wi, ci2 = dmi * wr - dmr * wi;
-          const T dBr = cr * zr - ci2 * zi, dBi = cr * zi + ci2 * zr;
-          a.dcc[ci + (real_part ? 0 : 1)] = real_part ? dAr : dAi;
-          a.dcc[ci + 2 * s.mult + (real_part ? 0 : 1)] = real_part ? dBr : dBi;
-          // dz = conj(A) dm + w (B conj(dm)); dv = conj(tau) dz
-          const T bdr = Br * dmr + Bi * dmi, bdi = Bi * dmr - Br * dmi;
-          const T dzr = (Ar * dmr + Ai * dmi) + (wr * bdr - wi * bdi);
-          const T dzi = (Ar * dmi - Ai * dmr) + (wr * bdi + wi * bdr);
-          const T dvr = tr * dzr + ti * dzi, dvi = tr * dzi - ti * dzr;
-          atomicAdd(a.dv + j * a.D + c, real_part ? dvr : dvi);
+#pragma unroll
+        for (int u = 0; u < CONV_UNROLL; ++u) {
+          const T dm = w[u] * dy;
+          a.drc[(e + u) * a.A0 + it.coef] = dm * x[u];
+          atomicAdd(a.dv + j[u] * a.D + it.col, dm * r[u]);
         }
+      }
+      for (; e < e1; ++e) {
+        const int64_t j = a.source[e];
+        const T dm = a.weights[e] * dy;
+        a.drc[e * a.A0 + it.coef] = dm * a.v[j * a.D + it.col];
+        atomicAdd(a.dv + j * a.D + it.col, dm * a.rc[e * a.A0 + it.coef]);
+      }
+    }
+    for (int t0 = n_real; t0 < n_items; t0 += 32) {
+      if (t0 + lane >= n_items) continue;
+      const ConvItem it = items_s[t0 + lane];
+      const int n = it.order;
+      T dyr, dyi;
+      load_pair(a.g + i * a.D + it.col, dyr, dyi);
+      auto edge = [&](int64_t e, int64_t j, T w_e, T rho, T tr, T ti, T vr, T vi, T Ar, T Ai, T Br, T Bi, T ar, T ai) {
+        const T zr = tr * vr - ti * vi, zi = tr * vi + ti * vr;
+        const T p = rho_power(rho, n);
+        const T wr = p * ar, wi = p * ai;
+        const T dmr = w_e * dyr, dmi = w_e * dyi;
+        // dA = dm conj(z); dB = (dm conj(w)) z
+        const T dAr = dmr * zr + dmi * zi, dAi = dmi * zr - dmr * zi;
+        const T cr = dmr * wr + dmi * wi, ci2 = dmi * wr - dmr * wi;
+        const T dBr = cr * zr - ci2 * zi, dBi = cr * zi + ci2 * zr;
+        const int64_t ci = e * a.W + it.coef;
+        store_pair(a.dcc + ci, dAr, dAi);
+        store_pair(a.dcc + ci + 2 * it.mult, dBr, dBi);
+        // dz = conj(A) dm + w (B conj(dm)); dv = conj(tau) dz
+        const T bdr = Br * dmr + Bi * dmi, bdi = Bi * dmr - Br * dmi;
+        const T dzr = (Ar * dmr + Ai * dmi) + (wr * bdr - wi * bdi);
+        const T dzi = (Ar * dmi - Ai * dmr) + (wr * bdi + wi * bdr);
+        atomicAdd(a.dv + j * a.D + it.col, tr * dzr + ti * dzi);
+        atomicAdd(a.dv + j * a.D + it.col + 1, tr * dzi - ti * dzr);
+      };
+      int64_t e = e0;
+      for (; e + CONV_UNROLL <= e1; e += CONV_UNROLL) {
+        T w[CONV_UNROLL], rho[CONV_UNROLL], tr[CONV_UNROLL], ti[CONV_UNROLL], vr[CONV_UNROLL], vi[CONV_UNROLL];
+        T Ar[CONV_UNROLL], Ai[CONV_UNROLL], Br[CONV_UNROLL], Bi[CONV_UNROLL], ar[CONV_UNROLL], ai[CONV_UNROLL];
+        int64_t j[CONV_UNROLL];
+#pragma unroll
+        for (int u = 0; u < CONV_UNROLL; ++u) {
+          const int64_t eu = e + u;
+          j[u] = a.source[eu];
+          w[u] = a.weights[eu];
+          rho[u] = a.rho[eu];
+          load_pair(a.v + j[u] * a.D + it.col, vr[u], vi[u]);
+          load_pair(a.transport + (eu * a.orders + n) * 2, tr[u], ti[u]);
+          load_pair(a.angular + (eu * a.orders + 2 * n) * 2, ar[u], ai[u]);
+          const T* co = a.cc + eu * a.W + it.coef;
+          load_pair(co, Ar[u], Ai[u]);
+          load_pair(co + 2 * it.mult, Br[u], Bi[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < CONV_UNROLL; ++u)
+          edge(e + u, j[u], w[u], rho[u], tr[u], ti[u], vr[u], vi[u], Ar[u], Ai[u], Br[u], Bi[u], ar[u], ai[u]);
+      }
+      for (; e < e1; ++e) {
+        const int64_t j = a.source[e];
+        T tr, ti, vr, vi, Ar, Ai, Br, Bi, ar, ai;
+        load_pair(a.transport + (e * a.orders + n) * 2, tr, ti);
+        load_pair(a.v + j * a.D + it.col, vr, vi);
+        const T* co = a.cc + e * a.W + it.coef;
+        load_pair(co, Ar, Ai);
+        load_pair(co + 2 * it.mult, Br, Bi);
+        load_pair(a.angular + (e * a.orders + 2 * n) * 2, ar, ai);
+        edge(e, j, a.weights[e], a.rho[e], tr, ti, vr, vi, Ar, Ai, Br, Bi, ar, ai);
       }
     }
   }
+}
+
+constexpr int CONV_THREADS = 128;  // 4 target nodes per CTA
+
+int conv_grid(int64_t n_nodes) {  // a few CTAs per SM, each striding the nodes: the item table is built once per CTA
+  const int64_t want = (n_nodes + CONV_THREADS / 32 - 1) / (CONV_THREADS / 32);
+  const int64_t cap = (int64_t)sm_count() * 16;
+  return (int)(want < cap ? (want < 1 ? 1 : want) : cap);
 }
 
 int column_threads(int D) {
@@ -504,7 +653,7 @@ extern "C" int gm_conv_forward(const void* v, const void* rc, const void* cc, co
     using T = decltype(tag);
     auto a = conv_args<T>(v, rc, cc, transport, angular, rho, weights, desc, row_ptr, source, n_nodes, D, F, orders, A0, W);
     a.out = (T*)out;
-    conv_forward_kernel<T><<<grid_for(n_nodes), column_threads(D), D * sizeof(ColumnSlot), (cudaStream_t)stream>>>(a);
+    conv_forward_kernel<T><<<conv_grid(n_nodes), CONV_THREADS, D * sizeof(ConvItem), (cudaStream_t)stream>>>(a);
     return launch_status("gm_conv_forward");
   };
   return dtype == GM_F32 ? run(float()) : run(double());
@@ -522,8 +671,7 @@ extern "C" int gm_conv_backward(const void* g, const void* v, const void* rc, co
     using T = decltype(tag);
     auto a = conv_args<T>(v, rc, cc, transport, angular, rho, weights, desc, row_ptr, source, n_nodes, D, F, orders, A0, W);
     a.g = (const T*)g; a.dv = (T*)dv; a.drc = (T*)drc; a.dcc = (T*)dcc;
-    const size_t smem = D * sizeof(T) + D * sizeof(ColumnSlot);
-    conv_backward_kernel<T><<<grid_for(n_nodes), column_threads(D), smem, (cudaStream_t)stream>>>(a);
+    conv_backward_kernel<T><<<conv_grid(n_nodes), CONV_THREADS, D * sizeof(ConvItem), (cudaStream_t)stream>>>(a);
     return launch_status("gm_conv_backward");
   };
   return dtype == GM_F32 ? run(float()) : run(double());

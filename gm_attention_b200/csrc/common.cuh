@@ -35,6 +35,13 @@ inline int launch_status(const char* what) {
   return GM_OK;
 }
 
+// SMs of the current device
+inline int sm_count() {
+  int device = 0, n = 148;
+  if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device);
+  return n;
+}
+
 // Opt a kernel in to `bytes` of dynamic shared memory (needed above 48 KiB).
 template <typename Kernel>
 inline int allow_smem(Kernel kernel, size_t bytes, const char* what) {
