@@ -23,35 +23,6 @@ constexpr int MAX_H = 8;
 constexpr int MAX_F = 8;
 constexpr int DESC = 5;
 
-// One flat column's slot. order < 0: the column belongs to no descriptor row.
-struct ColumnSlot {
-  int16_t order;    // frequency n (0: scalar)
-  int16_t head;     // head owning the column
-  int16_t partner;  // +1 for a real part, -1 for an imaginary part, 0 for a scalar
-  int16_t copy;     // copy index within the head, a
-  int16_t mult;     // copies per head, a_n
-  int16_t coff;     // coefficient offset of the frequency
-};
-
-__device__ __forceinline__ ColumnSlot decode_column(const int64_t* desc, int F, int H, int c) {
-  ColumnSlot s{-1, 0, 0, 0, 0, 0};
-  for (int f = 0; f < F; ++f) {
-    const int64_t* row = desc + f * DESC;
-    const int n = (int)row[0], a_n = (int)row[1], off = (int)row[2], dim = (int)row[4];
-    if (c >= off && c < off + H * a_n * dim) {
-      const int local = c - off, copy = local / dim, part = local % dim;
-      s.order = (int16_t)n;
-      s.head = (int16_t)(copy / a_n);
-      s.copy = (int16_t)(copy % a_n);
-      s.mult = (int16_t)a_n;
-      s.coff = (int16_t)row[3];
-      s.partner = (int16_t)(dim == 1 ? 0 : (part == 0 ? 1 : -1));
-      return s;
-    }
-  }
-  return s;
-}
-
 // ------------------------------------------------------------------ softmax
 
 template <typename T>
@@ -168,9 +139,8 @@ __global__ void __launch_bounds__(128) softmax_forward_grouped_kernel(SoftmaxArg
   }
   const int64_t e0 = a.row_ptr[i], e1 = a.row_ptr[i + 1];
   T m = neg_inf<T>();
-  for (int64_t e = e0; e < e1; ++e) {
-    const T* k_j = a.k + a.source[e] * a.D;
-    const T* tau = a.transport + e * a.orders * 2;
+  // this lane's share of <q_i, tau k_j> for one edge
+  auto dot = [&](const T* k_j, const T* tau) -> T {
     T part = T(0);
 #pragma unroll
     for (int f = 0; f < MAX_F; ++f) {
@@ -187,10 +157,33 @@ __global__ void __launch_bounds__(128) softmax_forward_grouped_kernel(SoftmaxArg
         }
       }
     }
-    for (int o = L >> 1; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    return part;
+  };
+  auto finish = [&](int64_t e, T part) {
     const T lw = a.scale * part + a.bias[e];
     if (a.inside[e] && lw > m) m = lw;
     if (s == 0) a.alpha[e * a.H + h] = lw;
+  };
+  constexpr int U = 4;  // edges in flight: their gathers of k_j are issued together
+  int64_t e = e0;
+  for (; e + U <= e1; e += U) {
+    const T* k_j[U];
+    T part[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) k_j[u] = a.k + a.source[e + u] * a.D;
+#pragma unroll
+    for (int u = 0; u < U; ++u) part[u] = dot(k_j[u], a.transport + (e + u) * a.orders * 2);
+    for (int o = L >> 1; o > 0; o >>= 1) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) part[u] += __shfl_xor_sync(0xffffffffu, part[u], o);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) finish(e + u, part[u]);
+  }
+  for (; e < e1; ++e) {
+    T part = dot(a.k + a.source[e] * a.D, a.transport + e * a.orders * 2);
+    for (int o = L >> 1; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    finish(e, part);
   }
   __syncwarp();
   // normalise: the group's lanes stride the row's edges for their head
@@ -202,52 +195,6 @@ __global__ void __launch_bounds__(128) softmax_forward_grouped_kernel(SoftmaxArg
   }
   for (int o = L >> 1; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
   for (int64_t e = e0 + s; e < e1; e += L) a.alpha[e * a.H + h] /= sum;
-}
-
-template <typename T>
-__global__ void softmax_backward_kernel(SoftmaxArgs<T> a) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  T* q_s = reinterpret_cast<T*>(smem_raw);
-  T* total_s = q_s + a.D;  // MAX_H
-  ColumnSlot* slot_s = reinterpret_cast<ColumnSlot*>(total_s + MAX_H);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
-  for (int c = threadIdx.x; c < a.D; c += blockDim.x) slot_s[c] = decode_column(a.desc, a.F, a.H, c);
-  for (int64_t i = blockIdx.x; i < a.n_nodes; i += gridDim.x) {
-    const int64_t e0 = a.row_ptr[i], e1 = a.row_ptr[i + 1];
-    __syncthreads();
-    for (int c = threadIdx.x; c < a.D; c += blockDim.x) q_s[c] = a.q[i * a.D + c];
-    for (int h = warp; h < a.H; h += n_warps) {
-      T total = T(0);
-      for (int64_t e = e0 + lane; e < e1; e += 32) total += a.alpha_in[e * a.H + h] * a.dalpha[e * a.H + h];
-      total = warp_sum(total);
-      if (lane == 0) total_s[h] = total;
-    }
-    __syncthreads();
-    for (int c = threadIdx.x; c < a.D; c += blockDim.x) {
-      const ColumnSlot s = slot_s[c];
-      T dq = T(0);
-      if (s.order >= 0) {
-        const T total = total_s[s.head];
-        const T sign = s.partner > 0 ? T(-1) : T(1);
-        const T q_c = q_s[c], q_p = q_s[c + s.partner];
-        for (int64_t e = e0; e < e1; ++e) {
-          const T al = a.alpha_in[e * a.H + s.head];
-          const T ds = a.scale * al * (a.dalpha[e * a.H + s.head] - total);
-          const int64_t j = a.source[e];
-          const T* k_j = a.k + j * a.D;
-          if (s.order == 0) {
-            dq += ds * k_j[c];
-            atomicAdd(a.dk + j * a.D + c, ds * q_c);
-          } else {
-            const T tr = a.transport[(e * a.orders + s.order) * 2], ti = a.transport[(e * a.orders + s.order) * 2 + 1];
-            dq += ds * (tr * k_j[c] + sign * ti * k_j[c + s.partner]);  // (tau k)[c]
-            atomicAdd(a.dk + j * a.D + c, ds * (tr * q_c - sign * ti * q_p));  // (conj(tau) q)[c]
-          }
-        }
-      }
-      a.dq[i * a.D + c] = dq;
-    }
-  }
 }
 
 // ------------------------------------------------------------------ depthwise conv
@@ -298,6 +245,111 @@ __device__ __forceinline__ void store_pair(T* p, T x, T y) {
     *reinterpret_cast<typename Pair<T>::type*>(p) = t;
   } else {
     p[0] = x; p[1] = y;
+  }
+}
+
+// One (head, frequency, copy) of the scores' backward: a scalar column or a (re, im) column pair of one head
+struct ScoreItem {
+  int col, order, head, pad;
+};
+
+// Backward of scores + softmax: a warp per target node.  The lanes first reduce sum_e alpha dalpha per head, then
+// every lane owns one item and walks the node's edges in order (dq is a sequential sum per column), four edges'
+// gathers in flight; dk is accumulated atomically.
+template <typename T>
+__global__ void softmax_backward_kernel(SoftmaxArgs<T> a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  ScoreItem* items_s = reinterpret_cast<ScoreItem*>(smem_raw);
+  int n_items = 0, n_real = 0;
+  for (int f = 0; f < a.F; ++f) {
+    const int n = (int)a.desc[f * DESC], a_n = (int)a.desc[f * DESC + 1], off = (int)a.desc[f * DESC + 2], dim = (int)a.desc[f * DESC + 4];
+    for (int x = threadIdx.x; x < a.H * a_n; x += blockDim.x) items_s[n_items + x] = ScoreItem{off + dim * x, n, x / a_n, 0};
+    n_items += a.H * a_n;
+    if (n == 0) n_real = n_items;  // items are in column order: the scalar block first
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  constexpr int U = 4;
+  for (int64_t i = (int64_t)blockIdx.x * warps + (threadIdx.x >> 5); i < a.n_nodes; i += (int64_t)gridDim.x * warps) {
+    const int64_t e0 = a.row_ptr[i], e1 = a.row_ptr[i + 1];
+    T total_of_lane = T(0);  // lane h < H ends up with sum_e alpha[e, h] dalpha[e, h]
+    for (int h = 0; h < a.H; ++h) {
+      T total = T(0);
+      for (int64_t e = e0 + lane; e < e1; e += 32) total += a.alpha_in[e * a.H + h] * a.dalpha[e * a.H + h];
+      total = warp_sum(total);
+      if (lane == h) total_of_lane = total;
+    }
+    for (int t0 = 0; t0 < n_items; t0 += 32) {
+      // a block of 32 items never mixes scalar and complex items unless it straddles the boundary: split it there
+      const int t1 = (t0 < n_real && t0 + 32 > n_real) ? n_real : min(t0 + 32, n_items);
+      const bool active = t0 + lane < t1;
+      const ScoreItem it = items_s[active ? t0 + lane : t0];
+      const T total = __shfl_sync(0xffffffffu, total_of_lane, it.head);
+      if (active && it.order == 0) {
+        const T q_c = a.q[i * a.D + it.col];
+        T dq = T(0);
+        int64_t e = e0;
+        for (; e + U <= e1; e += U) {
+          int64_t j[U];
+          T al[U], da[U], kc[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            j[u] = a.source[e + u];
+            al[u] = a.alpha_in[(e + u) * a.H + it.head];
+            da[u] = a.dalpha[(e + u) * a.H + it.head];
+            kc[u] = a.k[j[u] * a.D + it.col];
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const T ds = a.scale * al[u] * (da[u] - total);
+            dq += ds * kc[u];
+            atomicAdd(a.dk + j[u] * a.D + it.col, ds * q_c);
+          }
+        }
+        for (; e < e1; ++e) {
+          const int64_t j = a.source[e];
+          const T ds = a.scale * a.alpha_in[e * a.H + it.head] * (a.dalpha[e * a.H + it.head] - total);
+          dq += ds * a.k[j * a.D + it.col];
+          atomicAdd(a.dk + j * a.D + it.col, ds * q_c);
+        }
+        a.dq[i * a.D + it.col] = dq;
+      } else if (active) {
+        T q_r, q_i;
+        load_pair(a.q + i * a.D + it.col, q_r, q_i);
+        T dq_r = T(0), dq_i = T(0);
+        auto edge = [&](int64_t j, T al, T da, T tr, T ti, T kr, T ki) {
+          const T ds = a.scale * al * (da - total);
+          dq_r += ds * (tr * kr - ti * ki);  // (tau k)
+          dq_i += ds * (tr * ki + ti * kr);
+          atomicAdd(a.dk + j * a.D + it.col, ds * (tr * q_r + ti * q_i));  // conj(tau) q
+          atomicAdd(a.dk + j * a.D + it.col + 1, ds * (tr * q_i - ti * q_r));
+        };
+        int64_t e = e0;
+        for (; e + U <= e1; e += U) {
+          int64_t j[U];
+          T al[U], da[U], tr[U], ti[U], kr[U], ki[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            j[u] = a.source[e + u];
+            al[u] = a.alpha_in[(e + u) * a.H + it.head];
+            da[u] = a.dalpha[(e + u) * a.H + it.head];
+            load_pair(a.transport + ((e + u) * a.orders + it.order) * 2, tr[u], ti[u]);
+            load_pair(a.k + j[u] * a.D + it.col, kr[u], ki[u]);
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u) edge(j[u], al[u], da[u], tr[u], ti[u], kr[u], ki[u]);
+        }
+        for (; e < e1; ++e) {
+          const int64_t j = a.source[e];
+          T tr, ti, kr, ki;
+          load_pair(a.transport + (e * a.orders + it.order) * 2, tr, ti);
+          load_pair(a.k + j * a.D + it.col, kr, ki);
+          edge(j, a.alpha_in[e * a.H + it.head], a.dalpha[e * a.H + it.head], tr, ti, kr, ki);
+        }
+        store_pair(a.dq + i * a.D + it.col, dq_r, dq_i);
+      }
+      if (t1 != min(t0 + 32, n_items)) t0 = t1 - 32;  // resume at the boundary
+    }
   }
 }
 
@@ -510,11 +562,6 @@ int conv_grid(int64_t n_nodes) {  // a few CTAs per SM, each striding the nodes:
   return (int)(want < cap ? (want < 1 ? 1 : want) : cap);
 }
 
-int column_threads(int D) {
-  int t = ((D + 31) / 32) * 32;
-  return t > 512 ? 512 : (t < 32 ? 32 : t);
-}
-
 int grid_for(int64_t n_nodes) { return (int)(n_nodes < (int64_t)1 << 30 ? n_nodes : (int64_t)1 << 30); }
 
 template <typename T>
@@ -542,8 +589,7 @@ int softmax_forward_t(SoftmaxArgs<T> a, int64_t deg_max, int max_mult, cudaStrea
 
 template <typename T>
 int softmax_backward_t(SoftmaxArgs<T> a, cudaStream_t stream) {
-  const size_t smem = (a.D + MAX_H) * sizeof(T) + a.D * sizeof(ColumnSlot);
-  softmax_backward_kernel<T><<<grid_for(a.n_nodes), column_threads(a.D), smem, stream>>>(a);
+  softmax_backward_kernel<T><<<conv_grid(a.n_nodes), CONV_THREADS, a.D * sizeof(ScoreItem), stream>>>(a);
   return launch_status("gm_softmax_backward");
 }
 
