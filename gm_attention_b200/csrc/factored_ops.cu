@@ -81,60 +81,94 @@ __device__ __forceinline__ void stage_node(const FArgs<T>& a, int64_t j, T* zc_s
 }
 
 template <typename T>
-__global__ void __launch_bounds__(FTHREADS) factored_forward_kernel(FArgs<T> a) {
+__global__ void __launch_bounds__(FTHREADS) factored_forward_kernel(FArgs<T> a, int pitch) {
   extern __shared__ __align__(16) unsigned char raw[];
   T* zc_s = reinterpret_cast<T*>(raw);
   T* zr_s = zc_s + a.k * a.wc * 2;
+  // every thread builds its edge's row in shared memory (odd pitch: no bank conflicts); the warp then writes its 32 rows
+  // to global memory one row per store instruction (contiguous) instead of 32 scattered elements per instruction
+  T* row = zr_s + ((a.k * a.wr + 3) / 4) * 4 + (size_t)threadIdx.x * pitch;
+  const int lane = threadIdx.x & 31;
   for (int64_t grp = blockIdx.x; grp < a.n_groups; grp += gridDim.x) {
     const int64_t j = a.group_source[grp], first = a.group_ptr[grp], last = a.group_ptr[grp + 1];
     __syncthreads();
     stage_node(a, j, zc_s, zr_s);
     __syncthreads();
-    for (int64_t x = first + threadIdx.x; x < last; x += blockDim.x) {
-      const int64_t e = a.order[x];
-      T hh[FMAX_K];
-      hh[0] = T(1);
+    for (int64_t x0 = first; x0 < last; x0 += blockDim.x) {  // x0: uniform, so that whole warps take part in the row hand-over
+      const int64_t x = x0 + threadIdx.x;
+      const bool mine = x < last;
+      const int64_t e = mine ? a.order[x] : -1;
+      if (mine) {
+        T hh[FMAX_K];
+        hh[0] = T(1);
 #pragma unroll
-      for (int t = 1; t < FMAX_K; ++t) hh[t] = t < a.k ? a.h[e * (a.k - 1) + t - 1] : T(0);
-      T* row = a.out + e * a.d_out;
-      // Blocks are sorted by output offset; blocks of one offset add into the same columns.  The
-      // first block of a group writes, the following ones read-modify-write the edge's own row.
-      int open_offset = -1;
-      for (int b = 0; b < a.n_blocks; ++b) {
-        const int32_t* d = a.desc + b * FDESC;
-        const int kind = d[0], zoff = d[1], bm = d[2], ooff = d[6];
-        const bool take_real = d[7] != 0;
-        const bool first_of_group = ooff != open_offset;
-        open_offset = ooff;
-        if (kind == 0) {
-          for (int c = 0; c < bm; ++c) {
-            T s = T(0);
+        for (int t = 1; t < FMAX_K; ++t) hh[t] = t < a.k ? a.h[e * (a.k - 1) + t - 1] : T(0);
+        // Blocks are sorted by output offset; blocks of one offset add into the same columns.  The
+        // first block of a group writes, the following ones add to the edge's row.
+        int open_offset = -1;
+        for (int b = 0; b < a.n_blocks; ++b) {
+          const int32_t* d = a.desc + b * FDESC;
+          const int kind = d[0], zoff = d[1], bm = d[2], ooff = d[6];
+          const bool take_real = d[7] != 0;
+          const bool first_of_group = ooff != open_offset;
+          open_offset = ooff;
+          if (kind == 0) {
+            for (int c = 0; c < bm; ++c) {
+              T s = T(0);
+#pragma unroll
+              for (int t = 0; t < FMAX_K; ++t)
+                if (t < a.k) s += hh[t] * zr_s[t * a.wr + zoff + c];
+              row[ooff + c] = first_of_group ? s : row[ooff + c] + s;
+            }
+            continue;
+          }
+          T fr, fi;
+          block_factor(a, e, d, fr, fi);
+          auto emit = [&](int c, T ur, T ui) {
+            const T vr = fr * ur - fi * ui, vi = fr * ui + fi * ur;
+            if (take_real) {
+              row[ooff + c] = first_of_group ? vr : row[ooff + c] + vr;
+            } else {
+              row[ooff + 2 * c] = first_of_group ? vr : row[ooff + 2 * c] + vr;
+              row[ooff + 2 * c + 1] = first_of_group ? vi : row[ooff + 2 * c + 1] + vi;
+            }
+          };
+          int c = 0;
+          if (sizeof(T) == 4 && (a.wc % 2) == 0 && (zoff % 2) == 0) {
+            // two complex columns per 16-byte shared-memory load: (re, im, re, im) of columns c, c + 1 for one t
+            for (; c + 2 <= bm; c += 2) {
+              T ur0 = T(0), ui0 = T(0), ur1 = T(0), ui1 = T(0);
+#pragma unroll
+              for (int t = 0; t < FMAX_K; ++t)
+                if (t < a.k) {
+                  const float4 z = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(zc_s) + (t * a.wc + zoff + c) * 2);
+                  ur0 += hh[t] * (T)z.x; ui0 += hh[t] * (T)z.y;
+                  ur1 += hh[t] * (T)z.z; ui1 += hh[t] * (T)z.w;
+                }
+              emit(c, ur0, ui0);
+              emit(c + 1, ur1, ui1);
+            }
+          }
+          for (; c < bm; ++c) {
+            T ur = T(0), ui = T(0);
 #pragma unroll
             for (int t = 0; t < FMAX_K; ++t)
-              if (t < a.k) s += hh[t] * zr_s[t * a.wr + zoff + c];
-            row[ooff + c] = first_of_group ? s : row[ooff + c] + s;
-          }
-          continue;
-        }
-        T fr, fi;
-        block_factor(a, e, d, fr, fi);
-        for (int c = 0; c < bm; ++c) {
-          T ur = T(0), ui = T(0);
-#pragma unroll
-          for (int t = 0; t < FMAX_K; ++t)
-            if (t < a.k) {
-              ur += hh[t] * zc_s[(t * a.wc + zoff + c) * 2];
-              ui += hh[t] * zc_s[(t * a.wc + zoff + c) * 2 + 1];
-            }
-          const T vr = fr * ur - fi * ui, vi = fr * ui + fi * ur;
-          if (take_real) {
-            row[ooff + c] = first_of_group ? vr : row[ooff + c] + vr;
-          } else {
-            row[ooff + 2 * c] = first_of_group ? vr : row[ooff + 2 * c] + vr;
-            row[ooff + 2 * c + 1] = first_of_group ? vi : row[ooff + 2 * c + 1] + vi;
+              if (t < a.k) {
+                ur += hh[t] * zc_s[(t * a.wc + zoff + c) * 2];
+                ui += hh[t] * zc_s[(t * a.wc + zoff + c) * 2 + 1];
+              }
+            emit(c, ur, ui);
           }
         }
       }
+      __syncwarp();
+      const T* warp_rows = row - (size_t)lane * pitch;
+      for (int r = 0; r < 32; ++r) {
+        const int64_t e_r = __shfl_sync(0xffffffffu, e, r);
+        if (e_r < 0) break;  // lanes take consecutive x: the first idle lane ends the warp's rows
+        for (int c = lane; c < a.d_out; c += 32) a.out[e_r * a.d_out + c] = warp_rows[(size_t)r * pitch + c];
+      }
+      __syncwarp();
     }
   }
 }
@@ -278,11 +312,12 @@ extern "C" int gm_factored_forward(const void* h, const void* zc, const void* zr
     a.h = (const T*)h; a.zc = (const T*)zc; a.zr = (const T*)zr; a.angular = (const T*)angular; a.transport = (const T*)transport;
     a.rho = (const T*)rho; a.desc = desc; a.source = source; a.order = order; a.group_ptr = group_ptr; a.group_source = group_source;
     a.out = (T*)out;
-    const size_t smem = (size_t)k * (2 * wc + wr) * sizeof(T);
+    const int pitch = d_out | 1;  // per-thread output rows in shared memory, odd pitch
+    const size_t smem = ((size_t)k * 2 * wc + ((size_t)k * wr + 3) / 4 * 4 + (size_t)FTHREADS * pitch) * sizeof(T);
     int st = allow_smem(factored_forward_kernel<T>, smem, "gm_factored_forward");
     if (st != GM_OK) return st;
     const unsigned blocks = (unsigned)(n_groups < (1 << 20) ? n_groups : (1 << 20));
-    factored_forward_kernel<T><<<blocks, FTHREADS, smem, (cudaStream_t)stream>>>(a);
+    factored_forward_kernel<T><<<blocks, FTHREADS, smem, (cudaStream_t)stream>>>(a, pitch);
     return launch_status("gm_factored_forward");
   };
   return dtype == GM_F32 ? run(float()) : run(double());

@@ -11,8 +11,9 @@
 //
 // One thread per edge.  The input side (A <= 16) and the trunk (T <= 16) are
 // unrolled to their bounds with predicates so that every per-edge vector stays
-// in registers; the output side (B) is a runtime loop.  W and b are read
-// through the read-only path: every thread of a warp reads the same address.
+// in registers; the output side (B) is a runtime loop.  W (rows padded to 16
+// trunk columns) and b are staged in shared memory once per CTA and read with
+// 16-byte loads: every thread of a warp reads the same address (broadcast).
 #include "common.cuh"
 
 namespace gmb {
@@ -59,32 +60,69 @@ __device__ __forceinline__ void load_edge(const PArgs<T>& p, int64_t e, T (&h)[P
   }
 }
 
+// Weights and bias of the term in shared memory: w_s (rows, PMAX) zero-padded beyond the trunk width, b_s (rows);
+// rows = a b (real matrix) or 2 a b (complex: real row, then imaginary row of every entry).
+template <typename T>
+__device__ __forceinline__ void stage_weights(const PArgs<T>& p, T* w_s, T* b_s) {
+  const int rows = ((p.flags & MATRIX_COMPLEX) ? 2 : 1) * p.a * p.b;
+  for (int x = threadIdx.x; x < rows * PMAX; x += blockDim.x) {
+    const int r = x / PMAX, k = x - r * PMAX;
+    w_s[x] = k < p.trunk ? p.weight[(int64_t)r * p.trunk + k] : T(0);
+  }
+  for (int r = threadIdx.x; r < rows; r += blockDim.x) b_s[r] = p.bias ? p.bias[r] : T(0);
+  __syncthreads();
+}
+
+// <row r of W, v> over the trunk, four (fp32) / two (fp64) weights per shared-memory load
+template <typename T>
+__device__ __forceinline__ T row_dot(const T* w_s, int r, int trunk, const T (&v)[PMAX]) {
+  constexpr int V = 16 / sizeof(T);
+  const T* w = w_s + r * PMAX;
+  T acc = T(0);
+#pragma unroll
+  for (int k0 = 0; k0 < PMAX; k0 += V)
+    if (k0 < trunk) {
+      T q[V];
+      *reinterpret_cast<uint4*>(q) = *reinterpret_cast<const uint4*>(w + k0);
+#pragma unroll
+      for (int x = 0; x < V; ++x) acc += q[x] * v[k0 + x];
+    }
+  return acc;
+}
+
+// v += s * (row r of W), same access pattern
+template <typename T>
+__device__ __forceinline__ void row_axpy(const T* w_s, int r, int trunk, T s, T (&v)[PMAX]) {
+  constexpr int V = 16 / sizeof(T);
+  const T* w = w_s + r * PMAX;
+#pragma unroll
+  for (int k0 = 0; k0 < PMAX; k0 += V)
+    if (k0 < trunk) {
+      T q[V];
+      *reinterpret_cast<uint4*>(q) = *reinterpret_cast<const uint4*>(w + k0);
+#pragma unroll
+      for (int x = 0; x < V; ++x) v[k0 + x] += q[x] * s;
+    }
+}
+
 // M_idx = <W rows, h> + b
 template <typename T>
-__device__ __forceinline__ void entry(const PArgs<T>& p, int idx, const T (&h)[PMAX], T& mr, T& mi) {
+__device__ __forceinline__ void entry(const PArgs<T>& p, const T* w_s, const T* b_s, int idx, const T (&h)[PMAX], T& mr, T& mi) {
   if (p.flags & MATRIX_COMPLEX) {
-    mr = p.bias ? __ldg(p.bias + 2 * idx) : T(0);
-    mi = p.bias ? __ldg(p.bias + 2 * idx + 1) : T(0);
-    const T* wr = p.weight + (int64_t)(2 * idx) * p.trunk;
-    const T* wi = wr + p.trunk;
-#pragma unroll
-    for (int k = 0; k < PMAX; ++k)
-      if (k < p.trunk) {
-        mr += __ldg(wr + k) * h[k];
-        mi += __ldg(wi + k) * h[k];
-      }
+    mr = b_s[2 * idx] + row_dot(w_s, 2 * idx, p.trunk, h);
+    mi = b_s[2 * idx + 1] + row_dot(w_s, 2 * idx + 1, p.trunk, h);
   } else {
-    mr = p.bias ? __ldg(p.bias + idx) : T(0);
+    mr = b_s[idx] + row_dot(w_s, idx, p.trunk, h);
     mi = T(0);
-    const T* w = p.weight + (int64_t)idx * p.trunk;
-#pragma unroll
-    for (int k = 0; k < PMAX; ++k)
-      if (k < p.trunk) mr += __ldg(w + k) * h[k];
   }
 }
 
 template <typename T>
 __global__ void pairs_forward_kernel(PArgs<T> p) {
+  extern __shared__ __align__(16) unsigned char pairs_smem[];
+  T* w_s = reinterpret_cast<T*>(pairs_smem);
+  T* b_s = w_s + ((p.flags & MATRIX_COMPLEX) ? 2 : 1) * p.a * p.b * PMAX;
+  stage_weights(p, w_s, b_s);
   for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < p.n_edges; e += (int64_t)gridDim.x * blockDim.x) {
     T h[PMAX], ur[PMAX], ui[PMAX], s, pr, pi, qr, qi;
     load_edge(p, e, h, ur, ui, s, pr, pi, qr, qi);
@@ -94,7 +132,7 @@ __global__ void pairs_forward_kernel(PArgs<T> p) {
       for (int x = 0; x < PMAX; ++x)
         if (x < p.a) {
           T mr, mi;
-          entry(p, bi * p.a + x, h, mr, mi);
+          entry(p, w_s, b_s, bi * p.a + x, h, mr, mi);
           accr += mr * ur[x] - mi * ui[x];
           acci += mr * ui[x] + mi * ur[x];
         }
@@ -110,6 +148,10 @@ __global__ void pairs_forward_kernel(PArgs<T> p) {
 
 template <typename T>
 __global__ void pairs_backward_kernel(PArgs<T> p) {
+  extern __shared__ __align__(16) unsigned char pairs_smem[];
+  T* w_s = reinterpret_cast<T*>(pairs_smem);
+  T* b_s = w_s + ((p.flags & MATRIX_COMPLEX) ? 2 : 1) * p.a * p.b * PMAX;
+  stage_weights(p, w_s, b_s);
   for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < p.n_edges; e += (int64_t)gridDim.x * blockDim.x) {
     T h[PMAX], ur[PMAX], ui[PMAX], s, pr, pi, qr, qi;
     load_edge(p, e, h, ur, ui, s, pr, pi, qr, qi);
@@ -133,22 +175,16 @@ __global__ void pairs_backward_kernel(PArgs<T> p) {
           const int idx = bi * p.a + x;
           const T gmr = gqr * ur[x] + gqi * ui[x], gmi = gqi * ur[x] - gqr * ui[x];  // gm = gq conj(uu)
           T mr, mi;
-          entry(p, idx, h, mr, mi);
+          entry(p, w_s, b_s, idx, h, mr, mi);
           gur[x] += mr * gqr + mi * gqi;  // guu += conj(m) gq
           gui[x] += mr * gqi - mi * gqr;
           if (p.flags & MATRIX_COMPLEX) {
-            const T* wr = p.weight + (int64_t)(2 * idx) * p.trunk;
-            const T* wi = wr + p.trunk;
-#pragma unroll
-            for (int k = 0; k < PMAX; ++k)
-              if (k < p.trunk) gh[k] += __ldg(wr + k) * gmr + __ldg(wi + k) * gmi;
+            row_axpy(w_s, 2 * idx, p.trunk, gmr, gh);
+            row_axpy(w_s, 2 * idx + 1, p.trunk, gmi, gh);
             p.grad_k[(int64_t)(2 * idx) * p.n_edges + e] = gmr;
             p.grad_k[(int64_t)(2 * idx + 1) * p.n_edges + e] = gmi;
           } else {
-            const T* w = p.weight + (int64_t)idx * p.trunk;
-#pragma unroll
-            for (int k = 0; k < PMAX; ++k)
-              if (k < p.trunk) gh[k] += __ldg(w + k) * gmr;
+            row_axpy(w_s, idx, p.trunk, gmr, gh);
             p.grad_k[(int64_t)idx * p.n_edges + e] = gmr;
           }
         }
@@ -199,8 +235,12 @@ extern "C" int gm_pairs_forward(const void* hidden, const void* weight, const vo
     using T = decltype(tag);
     PArgs<T> p{n_edges, a, b, trunk, flags, (const T*)hidden, (const T*)weight, (const T*)bias, (const T*)u, (const T*)pre,
                (const T*)post, (const T*)scale, (T*)out, nullptr, nullptr, nullptr, nullptr};
-    const unsigned blocks = (unsigned)((n_edges + 127) / 128 < 148 * 32 ? (n_edges + 127) / 128 : 148 * 32);
-    pairs_forward_kernel<T><<<blocks, 128, 0, (cudaStream_t)stream>>>(p);
+    const int rows = ((flags & MATRIX_COMPLEX) ? 2 : 1) * a * b;
+    const size_t smem = (size_t)rows * (PMAX + 1) * sizeof(T);
+    int st = allow_smem(pairs_forward_kernel<T>, smem, "gm_pairs_forward");
+    if (st != GM_OK) return st;
+    const int64_t want = (n_edges + 127) / 128, cap = (int64_t)sm_count() * 8;  // each CTA stages the weights once and strides the edges
+    pairs_forward_kernel<T><<<(unsigned)(want < cap ? want : cap), 128, smem, (cudaStream_t)stream>>>(p);
     return launch_status("gm_pairs_forward");
   };
   return dtype == GM_F32 ? run(float()) : run(double());
@@ -216,8 +256,12 @@ extern "C" int gm_pairs_backward(const void* hidden, const void* weight, const v
     using T = decltype(tag);
     PArgs<T> p{n_edges, a, b, trunk, flags, (const T*)hidden, (const T*)weight, (const T*)bias, (const T*)u, (const T*)pre,
                (const T*)post, (const T*)scale, nullptr, (const T*)grad_out, (T*)grad_u, (T*)grad_hidden, (T*)grad_k};
-    const unsigned blocks = (unsigned)((n_edges + 127) / 128 < 148 * 32 ? (n_edges + 127) / 128 : 148 * 32);
-    pairs_backward_kernel<T><<<blocks, 128, 0, (cudaStream_t)stream>>>(p);
+    const int rows = ((flags & MATRIX_COMPLEX) ? 2 : 1) * a * b;
+    const size_t smem = (size_t)rows * (PMAX + 1) * sizeof(T);
+    int st = allow_smem(pairs_backward_kernel<T>, smem, "gm_pairs_backward");
+    if (st != GM_OK) return st;
+    const int64_t want = (n_edges + 127) / 128, cap = (int64_t)sm_count() * 8;  // each CTA stages the weights once and strides the edges
+    pairs_backward_kernel<T><<<(unsigned)(want < cap ? want : cap), 128, smem, (cudaStream_t)stream>>>(p);
     return launch_status("gm_pairs_backward");
   };
   return dtype == GM_F32 ? run(float()) : run(double());
