@@ -18,7 +18,8 @@
 // in tiles of 32; each lane of the first warp... every thread of the tile builds its
 // edge's packed row W(e) = scale * G conj(F) and h~(e) in shared memory, then the CTA
 // forms dh(e, t) = <W(e), Z_t(j)> (one thread per (edge, t)) and accumulates
-// dZ(t, c) += h~_t(e) W_c(e) with (t, c) pairs owned by fixed threads in registers.
+// dZ(t, c) += h~_t(e) W_c(e) with patches of 4 (fp32) / 2 (fp64) consecutive columns of one t
+// owned by fixed threads in registers; both read shared memory 16 bytes at a time.
 #include "common.cuh"
 
 namespace gmb {
@@ -188,24 +189,33 @@ __global__ void aggregate_kernel(const T* __restrict__ rows, const T* __restrict
   }
 }
 
+// Backward.  C = 2 wc + wr packed columns, CP = C rounded up to a whole number of 16-byte vectors (the padding
+// columns of Z and W stay zero), so that both small products run on 16-byte shared-memory loads:
+//   dh(e, t)   = <W(e), Z_t>           one thread per (edge, t), V columns per pair of loads
+//   dZ(t, c)  += h~_t(e) W_c(e)        a thread owns patches of V consecutive columns of one t, in registers
 template <typename T>
-__global__ void __launch_bounds__(FTHREADS) factored_backward_kernel(FArgs<T> a, int C, int WS) {
+__global__ void __launch_bounds__(FTHREADS) factored_backward_kernel(FArgs<T> a, int C, int CP) {
+  constexpr int V = 16 / sizeof(T);
+  constexpr int MAX_PATCH = MAX_OWNED / V;
   extern __shared__ __align__(16) unsigned char raw[];
   const int K = a.k;
-  T* z_s = reinterpret_cast<T*>(raw);  // (K, C): packed per t as [zc (wc, 2) | zr (wr)]
-  T* w_s = z_s + K * C;                // (TILE, WS)
-  T* h_s = w_s + TILE * WS;            // (TILE, K)
-  const int wc2 = 2 * a.wc;
+  T* z_s = reinterpret_cast<T*>(raw);  // (K, CP): packed per t as [zc (wc, 2) | zr (wr) | 0]
+  T* w_s = z_s + K * CP;               // (TILE, CP)
+  T* h_s = w_s + TILE * CP;            // (TILE, K)
+  const int wc2 = 2 * a.wc, patches = K * (CP / V);
+  for (int x = threadIdx.x; x < TILE * CP; x += blockDim.x) w_s[x] = T(0);  // the padding columns are never written again
   for (int64_t grp = blockIdx.x; grp < a.n_groups; grp += gridDim.x) {
     const int64_t j = a.group_source[grp], first = a.group_ptr[grp], last = a.group_ptr[grp + 1];
     __syncthreads();
-    for (int x = threadIdx.x; x < K * C; x += blockDim.x) {
-      const int t = x / C, c = x - t * C;
-      z_s[x] = c < wc2 ? a.zc[(j * K + t) * wc2 + c] : a.zr[(j * K + t) * a.wr + (c - wc2)];
+    for (int x = threadIdx.x; x < K * CP; x += blockDim.x) {
+      const int t = x / CP, c = x - t * CP;
+      z_s[x] = c < wc2 ? a.zc[(j * K + t) * wc2 + c] : (c < C ? a.zr[(j * K + t) * a.wr + (c - wc2)] : T(0));
     }
-    T acc[MAX_OWNED];
+    T acc[MAX_PATCH][V];
 #pragma unroll
-    for (int x = 0; x < MAX_OWNED; ++x) acc[x] = T(0);
+    for (int o = 0; o < MAX_PATCH; ++o)
+#pragma unroll
+      for (int v = 0; v < V; ++v) acc[o][v] = T(0);
     for (int64_t base = first; base < last; base += TILE) {
       const int n_tile = (int)min((int64_t)TILE, last - base);
       __syncthreads();
@@ -218,7 +228,7 @@ __global__ void __launch_bounds__(FTHREADS) factored_backward_kernel(FArgs<T> a,
         const bool take_real = d[7] != 0;
         const T scale = a.weights ? a.weights[e] : T(1);
         const T* g = a.target ? a.g + a.target[e] * a.d_out : a.g + e * a.d_out;
-        T* w = w_s + le * WS;
+        T* w = w_s + le * CP;
         if (kind == 0) {
           for (int c = 0; c < bm; ++c) w[wc2 + zoff + c] = scale * g[ooff + c];
         } else {
@@ -250,31 +260,45 @@ __global__ void __launch_bounds__(FTHREADS) factored_backward_kernel(FArgs<T> a,
       // dh(e, t) = <W(e), Z_t>, t >= 1
       for (int x = threadIdx.x; x < n_tile * (K - 1); x += blockDim.x) {
         const int le = x / (K - 1), t = x - le * (K - 1) + 1;
-        const T* w = w_s + le * WS;
-        const T* z = z_s + t * C;
+        const T* w = w_s + le * CP;
+        const T* z = z_s + t * CP;
         T s = T(0);
-        for (int c = 0; c < C; ++c) s += w[c] * z[c];
+        for (int c = 0; c < CP; c += V) {
+          T wv[V], zv[V];
+          *reinterpret_cast<uint4*>(wv) = *reinterpret_cast<const uint4*>(w + c);
+          *reinterpret_cast<uint4*>(zv) = *reinterpret_cast<const uint4*>(z + c);
+#pragma unroll
+          for (int v = 0; v < V; ++v) s += wv[v] * zv[v];
+        }
         a.dh[a.order[base + le] * (K - 1) + t - 1] = s;
       }
-      // dZ(t, c) += h~_t(e) W_c(e): pair x = threadIdx.x + owned * blockDim.x stays with this thread
+      // dZ(t, c) += h~_t(e) W_c(e): patch x = threadIdx.x + o * blockDim.x stays with this thread
 #pragma unroll
-      for (int owned = 0; owned < MAX_OWNED; ++owned) {
-        const int x = threadIdx.x + owned * FTHREADS;
-        if (x < K * C) {
-          const int t = x / C, c = x - t * C;
-          T s = acc[owned];
-          for (int le = 0; le < n_tile; ++le) s += h_s[le * K + t] * w_s[le * WS + c];
-          acc[owned] = s;
+      for (int o = 0; o < MAX_PATCH; ++o) {
+        const int x = threadIdx.x + o * FTHREADS;
+        if (x < patches) {
+          const int t = x / (CP / V), c = (x - t * (CP / V)) * V;
+          for (int le = 0; le < n_tile; ++le) {
+            const T hv = h_s[le * K + t];
+            T wv[V];
+            *reinterpret_cast<uint4*>(wv) = *reinterpret_cast<const uint4*>(w_s + le * CP + c);
+#pragma unroll
+            for (int v = 0; v < V; ++v) acc[o][v] += hv * wv[v];
+          }
         }
       }
     }
 #pragma unroll
-    for (int owned = 0; owned < MAX_OWNED; ++owned) {
-      const int x = threadIdx.x + owned * FTHREADS;
-      if (x < K * C) {
-        const int t = x / C, c = x - t * C;
-        if (c < wc2) a.dzc[(j * K + t) * wc2 + c] = acc[owned];
-        else a.dzr[(j * K + t) * a.wr + (c - wc2)] = acc[owned];
+    for (int o = 0; o < MAX_PATCH; ++o) {
+      const int x = threadIdx.x + o * FTHREADS;
+      if (x < patches) {
+        const int t = x / (CP / V), c0 = (x - t * (CP / V)) * V;
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+          const int c = c0 + v;
+          if (c < wc2) a.dzc[(j * K + t) * wc2 + c] = acc[o][v];
+          else if (c < C) a.dzr[(j * K + t) * a.wr + (c - wc2)] = acc[o][v];
+        }
       }
     }
   }
@@ -349,7 +373,7 @@ extern "C" int gm_factored_backward(const void* g, const int64_t* target, const 
   const bool aggregated = target != nullptr;
   GM_REQUIRE(!aggregated || (weights && rows && dweights), GM_ERR_ARGUMENT, "gm_factored_backward: the aggregated form needs weights, rows and dweights");
   const int C = 2 * wc + wr;
-  GM_REQUIRE(k * C <= MAX_OWNED * FTHREADS, GM_ERR_LIMIT, "gm_factored_backward: k * (2 wc + wr) = %d exceeds %d", k * C, MAX_OWNED * FTHREADS);
+  GM_REQUIRE(k * ((C + 3) / 4 * 4) <= MAX_OWNED * FTHREADS, GM_ERR_LIMIT, "gm_factored_backward: k * (2 wc + wr) = %d exceeds %d", k * C, MAX_OWNED * FTHREADS);
   auto run = [&](auto tag) {
     using T = decltype(tag);
     FArgs<T> a{};
@@ -358,12 +382,12 @@ extern "C" int gm_factored_backward(const void* g, const int64_t* target, const 
     a.rho = (const T*)rho; a.desc = desc; a.source = source; a.order = order; a.group_ptr = group_ptr; a.group_source = group_source;
     a.g = (const T*)g; a.target = target; a.weights = aggregated ? (const T*)weights : nullptr; a.rows = aggregated ? (const T*)rows : nullptr;
     a.dh = (T*)dh; a.dzc = (T*)dzc; a.dzr = (T*)dzr; a.dweights = aggregated ? (T*)dweights : nullptr;
-    const int WS = C + 1;  // odd-ish stride: the dZ walk reads a column across the tile's rows
-    const size_t smem = ((size_t)k * C + (size_t)TILE * WS + (size_t)TILE * k) * sizeof(T);
+    const int V = 16 / (int)sizeof(T), CP = (C + V - 1) / V * V;  // packed columns padded to whole 16-byte vectors
+    const size_t smem = ((size_t)k * CP + (size_t)TILE * CP + (size_t)TILE * k) * sizeof(T);
     int st = allow_smem(factored_backward_kernel<T>, smem, "gm_factored_backward");
     if (st != GM_OK) return st;
     const unsigned blocks = (unsigned)(n_groups < (1 << 20) ? n_groups : (1 << 20));
-    factored_backward_kernel<T><<<blocks, FTHREADS, smem, (cudaStream_t)stream>>>(a, C, WS);
+    factored_backward_kernel<T><<<blocks, FTHREADS, smem, (cudaStream_t)stream>>>(a, C, CP);
     return launch_status("gm_factored_backward");
   };
   return dtype == GM_F32 ? run(float()) : run(double());

@@ -405,8 +405,12 @@ __global__ void __launch_bounds__(32 * WARPS, WARPS == 4 ? 3 : 2) lattice_tn_ker
   __shared__ __align__(16) TnRowPair pairs_s[TC_MAX_WIN];
   __shared__ int n_pairs_s;
   const TcPlan& P = a.plan;
-  // two buffers, each: field 1 sub-tiles | field 2 sub-tiles | entries (TN_ROWS + TL, 8) fp32 | stats (TN_ROWS, 2) fp32 (pass S)
+  // two buffers, each: field 1 sub-tiles | field 2 sub-tiles | entries 2 x (TN_ROWS + TL, 4) fp32 | stats (TN_ROWS, 2) fp32 (pass S)
   constexpr int buf_bytes = L::BUFFER_BYTES;
+  // a staged table entry (8 floats) is split into two arrays of 4 floats: the 16-byte reads of the phases then sit at a
+  // 16-byte pitch (no bank conflicts between neighbouring offsets); the bias is float 2 NCF of the entry
+  constexpr int ENT_HALF = 4 * (TN_ROWS + TL);
+  constexpr int bias_at = 2 * NCF < 4 ? 2 * NCF : ENT_HALF + 2 * NCF - 4;  // the tables hold exactly the orders 1 .. NCF (host-checked)
   auto tile1 = [&](int buf) { return smem_raw + buf * buf_bytes; };
   auto tile2 = [&](int buf) { return smem_raw + buf * buf_bytes + L::FIELD_BYTES; };
   auto entry = [&](int buf) { return reinterpret_cast<float*>(smem_raw + buf * buf_bytes + 2 * L::FIELD_BYTES); };
@@ -591,7 +595,7 @@ __global__ void __launch_bounds__(32 * WARPS, WARPS == 4 ? 3 : 2) lattice_tn_ker
       if (idx < 2 * (n_rows + TL - 1)) {
         const int xi = idx >> 1, part = idx & 1;
         const int x = min(max(xi + p0 - (TL - 1), 0), cnt - 1);
-        cp_async16(de + 8 * xi + 4 * part, ent + 8 * x + 4 * part, 16);
+        cp_async16(de + 4 * xi + part * ENT_HALF, ent + 8 * x + 4 * part, 16);  // the two halves of an entry go to separate arrays
       }
     }
     if constexpr (PASS_S) {
@@ -641,14 +645,14 @@ __global__ void __launch_bounds__(32 * WARPS, WARPS == 4 ? 3 : 2) lattice_tn_ker
       // element x of a fragment: position pl + g + 8 (x >> 1), owner own_c + (x & 1)
       float lg[4], tr[NF][4], ti[NF][4];
       bool valid[4];
-      const float* e_lane = e_s + 8 * (pl + g - own_c + (TL - 1));  // staged entry of the offset p - owner, element 0
+      const float* e_lane = e_s + 4 * (pl + g - own_c + (TL - 1));  // staged entry (first half) of the offset p - owner, element 0
       const int off0 = p0 + pl + g - own_c;
       {
         float s0[4], sr[NF][4], si[NF][4];
         gram_step<KS0, NCF, KSC, TL>(f1, s1, t1, pl, lane_off, s0, sr, si);
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
-          const float* e = e_lane + 8 * (8 * (x >> 1) - (x & 1));
+          const float* e = e_lane + 4 * (8 * (x >> 1) - (x & 1));
           valid[x] = (unsigned)(off0 + 8 * (x >> 1) - (x & 1)) < (unsigned)cnt;
           float sum = s0[x];
           float tau[2 * NF];
@@ -656,7 +660,7 @@ __global__ void __launch_bounds__(32 * WARPS, WARPS == 4 ? 3 : 2) lattice_tn_ker
             const float4 t = *reinterpret_cast<const float4*>(e);
             tau[0] = t.x; tau[1] = t.y; tau[2] = t.z; tau[3] = t.w;
             if constexpr (NCF == 3) {
-              const float2 t3 = *reinterpret_cast<const float2*>(e + 4);
+              const float2 t3 = *reinterpret_cast<const float2*>(e + ENT_HALF);
               tau[4] = t3.x; tau[5] = t3.y;
             }
           } else if constexpr (NCF == 1) {
@@ -670,7 +674,7 @@ __global__ void __launch_bounds__(32 * WARPS, WARPS == 4 ? 3 : 2) lattice_tn_ker
             sum = fmaf(tau[2 * f], sr[f][x], sum);
             sum = fmaf(-tau[2 * f + 1], si[f][x], sum);
           }
-          lg[x] = valid[x] ? fmaf(cscale, sum, TC_LOG2E * e[2 * a.NORD]) : -INFINITY;  // -inf: outside the window
+          lg[x] = valid[x] ? fmaf(cscale, sum, TC_LOG2E * e[bias_at]) : -INFINITY;  // -inf: outside the window
         }
       }
       float w1[4], w2[4];  // the weights the two accumulations use: forward p | pass T ds | pass S ds, p
@@ -922,6 +926,7 @@ int dispatch_tc(TcArgs& a, int n_order_rows, int64_t batch, cudaStream_t cs) {
   const int ks0 = a.plan.a0 > 0 ? 1 : 0, ksc = a.plan.ac > 8 ? 2 : 1, ncf = a.plan.n_cf;
   for (int f = 0; f < ncf; ++f)
     GM_REQUIRE(a.plan.cf_order[f] == f + 1, GM_ERR_UNSUPPORTED, "gm_lattice_attention (tensor cores): complex frequencies must be the orders 1 .. %d", ncf);
+  GM_REQUIRE(a.NORD == ncf, GM_ERR_UNSUPPORTED, "gm_lattice_attention (tensor cores): the tables must hold exactly the orders 1 .. %d (they hold %d)", ncf, a.NORD);
   if (ks0 == 1 && ncf == 2 && ksc == 2) return launch_tn<1, 2, 2, MODE>(a, n_order_rows, batch, cs);
   if (ks0 == 1 && ncf == 2 && ksc == 1) return launch_tn<1, 2, 1, MODE>(a, n_order_rows, batch, cs);
   if (ks0 == 1 && ncf == 3 && ksc == 1) return launch_tn<1, 3, 1, MODE>(a, n_order_rows, batch, cs);

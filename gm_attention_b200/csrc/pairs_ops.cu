@@ -32,26 +32,81 @@ struct PArgs {
   T *grad_u, *grad_hidden, *grad_k;
 };
 
+// n consecutive values at p into v[0..n) (n <= N): 16-byte loads when the address and n allow it
+template <typename T, int N>
+__device__ __forceinline__ void load_run(const T* p, int n, T (&v)[N]) {
+  constexpr int V = 16 / sizeof(T);
+  if ((reinterpret_cast<uintptr_t>(p) & 15) == 0 && n % V == 0) {
+#pragma unroll
+    for (int k0 = 0; k0 < N; k0 += V)
+      if (k0 < n) *reinterpret_cast<uint4*>(&v[k0]) = *reinterpret_cast<const uint4*>(p + k0);
+  } else {
+#pragma unroll
+    for (int k = 0; k < N; ++k)
+      if (k < n) v[k] = p[k];
+  }
+}
+// p[0..n) += v[0..n), same access pattern
+template <typename T, int N>
+__device__ __forceinline__ void add_run(T* p, int n, const T (&v)[N]) {
+  constexpr int V = 16 / sizeof(T);
+  if ((reinterpret_cast<uintptr_t>(p) & 15) == 0 && n % V == 0) {
+#pragma unroll
+    for (int k0 = 0; k0 < N; k0 += V)
+      if (k0 < n) {
+        T q[V];
+        *reinterpret_cast<uint4*>(q) = *reinterpret_cast<const uint4*>(p + k0);
+#pragma unroll
+        for (int x = 0; x < V; ++x) q[x] += v[k0 + x];
+        *reinterpret_cast<uint4*>(p + k0) = *reinterpret_cast<const uint4*>(q);
+      }
+  } else {
+#pragma unroll
+    for (int k = 0; k < N; ++k)
+      if (k < n) p[k] += v[k];
+  }
+}
+// (x, y) added at p: one 2-element access when the address allows it
+template <typename T>
+__device__ __forceinline__ void add_pair(T* p, T x, T y) {
+  if ((reinterpret_cast<uintptr_t>(p) & (2 * sizeof(T) - 1)) == 0) {
+    T q[2];
+    if (sizeof(T) == 4) *reinterpret_cast<uint2*>(q) = *reinterpret_cast<const uint2*>(p);
+    else *reinterpret_cast<uint4*>(q) = *reinterpret_cast<const uint4*>(p);
+    q[0] += x; q[1] += y;
+    if (sizeof(T) == 4) *reinterpret_cast<uint2*>(p) = *reinterpret_cast<const uint2*>(q);
+    else *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(q);
+  } else {
+    p[0] += x; p[1] += y;
+  }
+}
+
 template <typename T>
 __device__ __forceinline__ void load_edge(const PArgs<T>& p, int64_t e, T (&h)[PMAX], T (&ur)[PMAX], T (&ui)[PMAX], T& s, T& pr, T& pi, T& qr, T& qi) {
 #pragma unroll
-  for (int k = 0; k < PMAX; ++k) h[k] = k < p.trunk ? p.hidden[e * p.trunk + k] : T(0);
+  for (int k = 0; k < PMAX; ++k) h[k] = T(0);
+  load_run(p.hidden + e * p.trunk, p.trunk, h);
   pr = p.pre ? p.pre[2 * e] : T(1);
   pi = p.pre ? p.pre[2 * e + 1] : T(0);
   s = p.scale ? p.scale[e] : T(1);
   qr = (p.post ? p.post[2 * e] : T(1)) * s;
   qi = (p.post ? p.post[2 * e + 1] : T(0)) * s;
+  T raw[2 * PMAX];
+#pragma unroll
+  for (int x = 0; x < 2 * PMAX; ++x) raw[x] = T(0);
+  if (p.flags & U_REAL) load_run(p.u + e * p.a, p.a, raw);
+  else load_run(p.u + 2 * e * p.a, 2 * p.a, raw);
 #pragma unroll
   for (int x = 0; x < PMAX; ++x) {
     ur[x] = ui[x] = T(0);
     if (x < p.a) {
       T re, im;
       if (p.flags & U_REAL) {
-        re = p.u[e * p.a + x];
+        re = raw[x];
         im = T(0);
       } else {
-        re = p.u[2 * (e * p.a + x)];
-        im = p.u[2 * (e * p.a + x) + 1];
+        re = raw[2 * x];
+        im = raw[2 * x + 1];
         if (p.flags & CONJ_U) im = -im;
       }
       ur[x] = pr * re - pi * im;  // uu = pre * u~
@@ -139,8 +194,7 @@ __global__ void pairs_forward_kernel(PArgs<T> p) {
       if (p.flags & OUT_REAL) {
         p.out[e * p.b + bi] += accr * s;
       } else {
-        p.out[2 * (e * p.b + bi)] += qr * accr - qi * acci;
-        p.out[2 * (e * p.b + bi) + 1] += qr * acci + qi * accr;
+        add_pair(p.out + 2 * (e * p.b + bi), qr * accr - qi * acci, qr * acci + qi * accr);
       }
     }
   }
@@ -199,13 +253,10 @@ __global__ void pairs_backward_kernel(PArgs<T> p) {
           p.grad_u[e * p.a + x] += gr;
         } else {
           if (p.flags & CONJ_U) gi = -gi;
-          p.grad_u[2 * (e * p.a + x)] += gr;
-          p.grad_u[2 * (e * p.a + x) + 1] += gi;
+          add_pair(p.grad_u + 2 * (e * p.a + x), gr, gi);
         }
       }
-#pragma unroll
-    for (int k = 0; k < PMAX; ++k)
-      if (k < p.trunk) p.grad_hidden[e * p.trunk + k] += gh[k];
+    add_run(p.grad_hidden + e * p.trunk, p.trunk, gh);
   }
 }
 

@@ -178,7 +178,7 @@ def enabled(kernel: Any, x: Any, edges: Any) -> bool:
     p = plan(kernel)
     head = kernel.complex_head if kernel.complex_head is not None else kernel.real_head
     k = head.in_features + 1
-    if k > MAX_K or p.d_out > MAX_OUT or p.max_bm > MAX_BM or k * (2 * p.wc + p.wr) > MAX_KC:
+    if k > MAX_K or p.d_out > MAX_OUT or p.max_bm > MAX_BM or k * (-(-(2 * p.wc + p.wr) // 4) * 4) > MAX_KC:  # packed width padded to whole 16-byte vectors
         return False
     return edges.n_edges > 0
 
