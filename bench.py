@@ -58,6 +58,8 @@ def parse() -> argparse.Namespace:
                    help="lattice: compact-table fast path (default); csr: general per-edge-table kernels")
     p.add_argument("--radius-rows", type=float, default=None,
                    help="neighbourhood radius in lattice row spacings (default: the workload's own, 3); other values are for profiling")
+    p.add_argument("--per-rank", action="store_true",
+                   help="every rank prints its own per-step timings (halo exchange in, forward, backward, halo sums out) to stderr")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
     return p.parse_args()
@@ -320,7 +322,11 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
     fwd_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     bwd_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
 
+    mark_ev = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(args.steps)]  # step start, step end
+
     def step(index: int | None = None):
+        if index is not None:
+            mark_ev[index][0].record()
         if halo is not None:
             halo.fill_halos(k, v)
         if index is not None:
@@ -334,6 +340,8 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
             bwd_ev[index][1].record()
         if halo is not None:
             halo.reduce_halos(dk.view(shape), dv.view(shape))
+        if index is not None:
+            mark_ev[index][1].record()
         return out, dq, dk, dv
 
     def barrier():
@@ -363,6 +371,10 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
     else:
         total_edges = local_edges
     ms_step = ms_total / args.steps
+    if args.per_rank:
+        detail = [{"halo_in": round(m[0].elapsed_time(f[0]), 3), "fwd": round(f[0].elapsed_time(f[1]), 3), "bwd": round(b[0].elapsed_time(b[1]), 3),
+                   "halo_out": round(b[1].elapsed_time(m[1]), 3)} for m, f, b in zip(mark_ev, fwd_ev, bwd_ev)]
+        print(json.dumps({"rank": rank, "rows": [plan.owned(rank)[0], plan.owned(rank)[1]] if world > 1 else [0, nlat], "steps_ms": detail}), file=sys.stderr, flush=True)
     fwd_ms = statistics.mean(a.elapsed_time(b) for a, b in fwd_ev)
     bwd_ms = statistics.mean(a.elapsed_time(b) for a, b in bwd_ev)
 

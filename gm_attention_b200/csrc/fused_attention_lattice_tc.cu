@@ -158,13 +158,16 @@ __device__ __forceinline__ int flat_column(const TcPlan& P, int h, int c) {
 
 // owners per CTA = 8 x warps: 8 warps forward, 4 in the backward passes (more registers per thread, three CTAs per SM)
 constexpr int TN_WARPS(int mode) { return mode == TC_FWD ? 8 : 4; }
-constexpr int TN_ADV = 80;           // positions a chunk advances by
-constexpr int TN_ROWS = TN_ADV + 8;  // positions staged per chunk: a step of 16 may start 8 before the chunk's end
+// positions a staged chunk advances by (a multiple of 16): 64 owners + a window of up to 17 fit one chunk of 80, 32 owners
+// + 17 one of 48 (smaller buffers: four CTAs per SM).  Staged per chunk: 8 more, a step of 16 may start 8 before the end.
+constexpr __host__ __device__ int tn_advance(int owners) { return owners >= 64 ? 80 : 48; }
+constexpr __host__ __device__ int tn_rows(int owners) { return tn_advance(owners) + 8; }
 
 template <int KS0, int NCF, int KSC, int TL>
 struct TnLayout {
   static constexpr __host__ __device__ int align1k(int x) { return (x + 1023) / 1024 * 1024; }
   static constexpr int REAL_PITCH = 32, CX_PITCH = 32 * KSC;
+  static constexpr int TN_ROWS = tn_rows(TL);
   static constexpr int REAL_BYTES = KS0 ? align1k(TN_ROWS * REAL_PITCH) : 0;
   static constexpr int CX_BYTES = align1k(TN_ROWS * CX_PITCH);
   static constexpr int FIELD_BYTES = REAL_BYTES + NCF * CX_BYTES;
@@ -392,8 +395,9 @@ struct TnRowPair {
 };
 
 template <int KS0, int NCF, int KSC, int MODE, int WARPS>
-__global__ void __launch_bounds__(32 * WARPS, WARPS == 4 ? 3 : 2) lattice_tn_kernel(const __grid_constant__ TcArgs a) {
+__global__ void __launch_bounds__(32 * WARPS, WARPS == 4 ? (MODE == TC_BWD_T ? 4 : 3) : 2) lattice_tn_kernel(const __grid_constant__ TcArgs a) {
   constexpr int TL = 8 * WARPS, THREADS = 32 * WARPS;
+  constexpr int TN_ADV = tn_advance(TL), TN_ROWS = tn_rows(TL);
   using L = TnLayout<KS0, NCF, KSC, TL>;
   constexpr int KQ = KS0 + NCF * KSC, CH = 2 * KQ, NCK = NCF * KSC > 0 ? NCF * KSC : 1;
   constexpr int NF = NCF > 0 ? NCF : 1;
@@ -893,7 +897,7 @@ bool encode_field_map(CUtensorMap* map, const void* field, int D, int nlon, int6
 
 template <int KS0, int NCF, int KSC, int MODE>
 int launch_tn(TcArgs& a, int n_order_rows, int64_t batch, cudaStream_t stream) {
-  constexpr int WARPS = TN_WARPS(MODE), TL = 8 * WARPS;
+  constexpr int WARPS = TN_WARPS(MODE), TL = 8 * WARPS, TN_ROWS = tn_rows(TL);
   using L = TnLayout<KS0, NCF, KSC, TL>;
   bool tma = !tma_disabled() && a.D % 8 == 0 && a.nlon >= TN_ROWS && batch * a.rows < (1ll << 31) && (KS0 == 0 || (a.plan.a0 == 16 && a.plan.real_off % 8 == 0)) &&
              2 * a.plan.ac == 16 * KSC && reinterpret_cast<uintptr_t>(a.nb1) % 16 == 0 && reinterpret_cast<uintptr_t>(a.nb2) % 16 == 0;
