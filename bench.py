@@ -254,6 +254,24 @@ class ClockSampler:
                 "samples": len(rows), "source": "nvidia-smi"}
 
 
+def bind_to_gpu_cpus(uuid: str | None, index: int) -> None:
+    """Pin this process to the CPU cores NVML reports as local to its GPU, so that the pinned host buffers of the
+    end-to-end measurement are allocated on the GPU's own NUMA node (one process per GPU on a multi-socket host)."""
+    try:
+        import pynvml as nv
+
+        nv.nvmlInit()
+        handle = nv.nvmlDeviceGetHandleByUUID(uuid.encode()) if uuid else nv.nvmlDeviceGetHandleByIndex(index)
+        words = (os.cpu_count() + 63) // 64
+        mask = nv.nvmlDeviceGetCpuAffinity(handle, words)
+        cpus = {64 * w + b for w, word in enumerate(mask) for b in range(64) if (int(word) >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+    except Exception:  # noqa: BLE001  (no NVML, no affinity information: stay where the launcher put us)
+        pass
+
+
 def run_ours(args: argparse.Namespace, cfg: dict) -> None:
     import numpy as np
     import torch
@@ -275,6 +293,8 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if world > 1:
+        gpu_uuid0 = getattr(torch.cuda.get_device_properties(local), "uuid", None)
+        bind_to_gpu_cpus(f"GPU-{gpu_uuid0}" if gpu_uuid0 is not None else None, local)
         dist.init_process_group("nccl", device_id=device)
     nlat, nlon, batch, heads = cfg["nlat"], cfg["nlon"], cfg["batch"], cfg["heads"]
     radius = cfg["radius_rows"] * math.pi / nlat

@@ -106,15 +106,30 @@ class BandPlan:
 
 
 class HaloExchanger:
-    """Moves halo rows of fields laid out ``(batch, extended rows, nlon, D)``."""
+    """Moves halo rows of fields laid out ``(batch, extended rows, nlon, D)``.
+
+    The peers and row ranges are fixed by the band plan, so the staging buffers of every (field shape, dtype) are
+    allocated once and reused: an exchange is a few slice copies, one batched send / receive and the landing copies."""
 
     def __init__(self, plan: BandPlan, rank: int, group: dist.ProcessGroup | None = None) -> None:
         self.plan, self.rank, self.group = plan, rank, group
         self.elo, self.ehi = plan.extended(rank)
         self.lo, self.hi = plan.owned(rank)
+        #: (peer, rows the peer needs from me, rows I need from the peer): global row ranges or None
+        self.peers = [(other, plan.needs(other, rank), plan.needs(rank, other)) for other in range(plan.world)
+                      if other != rank and (plan.needs(other, rank) is not None or plan.needs(rank, other) is not None)]
+        self._buffers: dict = {}
 
     def _local(self, rows: tuple[int, int]) -> slice:
         return slice(rows[0] - self.elo, rows[1] - self.elo)
+
+    def _staging(self, like: Tensor, slot: int, peer: int, rows: tuple[int, int], kind: str) -> Tensor:
+        key = (kind, slot, peer, rows, tuple(like.shape), like.dtype, like.device)
+        buf = self._buffers.get(key)
+        if buf is None:
+            buf = torch.empty((like.shape[0], rows[1] - rows[0], *like.shape[2:]), dtype=like.dtype, device=like.device)
+            self._buffers[key] = buf
+        return buf
 
     def _exchange(self, sends: list[tuple[int, Tensor]], recvs: list[tuple[int, Tensor]]) -> None:
         if not sends and not recvs:
@@ -127,14 +142,14 @@ class HaloExchanger:
     def fill_halos(self, *fields: Tensor) -> None:
         """Forward exchange: copy the owners' rows into this rank's halo rows of every field."""
         sends, recvs, landing = [], [], []
-        for other in range(self.plan.world):
-            theirs = self.plan.needs(other, self.rank)  # what `other` needs from me
-            mine = self.plan.needs(self.rank, other)  # what I need from `other`
-            for f in fields:
+        for other, theirs, mine in self.peers:
+            for slot, f in enumerate(fields):
                 if theirs is not None:
-                    sends.append((other, f[:, self._local(theirs)].contiguous()))
+                    out = self._staging(f, slot, other, theirs, "send")
+                    out.copy_(f[:, self._local(theirs)])
+                    sends.append((other, out))
                 if mine is not None:
-                    buf = torch.empty_like(f[:, self._local(mine)]).contiguous()
+                    buf = self._staging(f, slot, other, mine, "recv")
                     recvs.append((other, buf))
                     landing.append((f, mine, buf))
         self._exchange(sends, recvs)
@@ -145,14 +160,14 @@ class HaloExchanger:
         """Backward exchange: send the gradient rows accumulated for other ranks' nodes to their
         owners, add what the others accumulated for this rank's nodes, and zero the halo rows."""
         sends, recvs, landing = [], [], []
-        for other in range(self.plan.world):
-            mine = self.plan.needs(self.rank, other)  # halo rows I computed for `other`'s nodes
-            theirs = self.plan.needs(other, self.rank)  # rows of mine `other` computed partial sums for
-            for g in grads:
-                if mine is not None:
-                    sends.append((other, g[:, self._local(mine)].contiguous()))
-                if theirs is not None:
-                    buf = torch.empty_like(g[:, self._local(theirs)]).contiguous()
+        for other, theirs, mine in self.peers:
+            for slot, g in enumerate(grads):
+                if mine is not None:  # halo rows I computed partial sums for: they belong to `other`
+                    out = self._staging(g, slot, other, mine, "send")
+                    out.copy_(g[:, self._local(mine)])
+                    sends.append((other, out))
+                if theirs is not None:  # rows of mine `other` computed partial sums for
+                    buf = self._staging(g, slot, other, theirs, "recv")
                     recvs.append((other, buf))
                     landing.append((g, theirs, buf))
         self._exchange(sends, recvs)

@@ -87,3 +87,28 @@ def test_cpu_tensors_are_refused():
     with pytest.raises(RuntimeError):
         AttentionExtension().softmax_forward(q, q, torch.zeros(1, 1, 2), torch.zeros(1), torch.zeros(1, dtype=torch.uint8),
                                              torch.tensor([[0, 2, 0, 0, 1]]), torch.tensor([0, 1, 1]), torch.tensor([0]), 1, 1.0, 1)
+
+
+def test_tensor_core_layouts_and_row_cost():
+    """Host-side gates of the tensor-core lattice kernels: head layouts they are instantiated for (complex
+    frequencies must be the orders 1 .. n) and the per-row cost model that balances the latitude bands."""
+    import torch
+
+    from gm_attention_b200.attention import tensor_core_layout_supported
+    from gm_attention_b200.parallel import balanced_cuts, tensor_core_row_cost
+
+    row = lambda n, a, off: (n, a, off, 0, 1 if n == 0 else 2)
+    assert tensor_core_layout_supported((row(0, 16, 0), row(1, 16, 64), row(2, 16, 192)))      # headline
+    assert tensor_core_layout_supported((row(0, 8, 0), row(1, 8, 32), row(2, 8, 96), row(3, 8, 160)))
+    assert tensor_core_layout_supported((row(1, 6, 0), row(2, 6, 12)))                           # no scalar block
+    assert not tensor_core_layout_supported((row(0, 16, 0), row(1, 16, 64), row(3, 16, 192)))  # orders 1, 3
+    assert not tensor_core_layout_supported((row(0, 16, 0), row(2, 16, 64)))                    # order 2 alone
+    assert not tensor_core_layout_supported((row(0, 16, 0), row(1, 16, 64), row(2, 8, 192)))   # two multiplicities
+    assert not tensor_core_layout_supported((row(0, 32, 0), row(1, 16, 128)))                   # scalar block too wide
+    # a whole-row polar window costs more per ROW but far less per EDGE than a narrow equatorial one
+    counts = torch.tensor([[0, 512, 512, 512, 0], [7, 7, 7, 7, 7]])
+    polar, equator = tensor_core_row_cost(counts)
+    assert polar > equator
+    assert polar / (3 * 512) < 0.3 * equator / (5 * 7)
+    cuts = balanced_cuts([polar] * 4 + [equator] * 120 + [polar] * 4, 4)
+    assert cuts[0] == 0 and cuts[-1] == 128 and cuts == sorted(cuts) and len(set(cuts)) == 5
