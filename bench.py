@@ -295,6 +295,9 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
     if world > 1:
         gpu_uuid0 = getattr(torch.cuda.get_device_properties(local), "uuid", None)
         bind_to_gpu_cpus(f"GPU-{gpu_uuid0}" if gpu_uuid0 is not None else None, local)
+        # the halo messages are a few tens of MB between NVLink neighbours: give NCCL's point-to-point path more channels
+        # than its default for small peer counts (a user's own setting wins)
+        os.environ.setdefault("NCCL_MIN_P2P_NCHANNELS", "8")
         dist.init_process_group("nccl", device_id=device)
     nlat, nlon, batch, heads = cfg["nlat"], cfg["nlon"], cfg["batch"], cfg["heads"]
     radius = cfg["radius_rows"] * math.pi / nlat

@@ -123,11 +123,12 @@ class HaloExchanger:
     def _local(self, rows: tuple[int, int]) -> slice:
         return slice(rows[0] - self.elo, rows[1] - self.elo)
 
-    def _staging(self, like: Tensor, slot: int, peer: int, rows: tuple[int, int], kind: str) -> Tensor:
-        key = (kind, slot, peer, rows, tuple(like.shape), like.dtype, like.device)
+    def _staging(self, like: Tensor, count: int, peer: int, rows: tuple[int, int], kind: str) -> Tensor:
+        """One buffer per (peer, direction) for ALL fields of an exchange: (count, batch, rows, nlon, D)."""
+        key = (kind, count, peer, rows, tuple(like.shape), like.dtype, like.device)
         buf = self._buffers.get(key)
         if buf is None:
-            buf = torch.empty((like.shape[0], rows[1] - rows[0], *like.shape[2:]), dtype=like.dtype, device=like.device)
+            buf = torch.empty((count, like.shape[0], rows[1] - rows[0], *like.shape[2:]), dtype=like.dtype, device=like.device)
             self._buffers[key] = buf
         return buf
 
@@ -140,39 +141,42 @@ class HaloExchanger:
             work.wait()
 
     def fill_halos(self, *fields: Tensor) -> None:
-        """Forward exchange: copy the owners' rows into this rank's halo rows of every field."""
-        sends, recvs, landing = [], [], []
+        """Forward exchange: copy the owners' rows into this rank's halo rows of every field (one message per peer
+        and direction carries all fields)."""
+        sends, recvs = [], []
         for other, theirs, mine in self.peers:
-            for slot, f in enumerate(fields):
-                if theirs is not None:
-                    out = self._staging(f, slot, other, theirs, "send")
-                    out.copy_(f[:, self._local(theirs)])
-                    sends.append((other, out))
-                if mine is not None:
-                    buf = self._staging(f, slot, other, mine, "recv")
-                    recvs.append((other, buf))
-                    landing.append((f, mine, buf))
+            if theirs is not None:
+                out = self._staging(fields[0], len(fields), other, theirs, "send")
+                for slot, f in enumerate(fields):
+                    out[slot].copy_(f[:, self._local(theirs)])
+                sends.append((other, out))
+            if mine is not None:
+                recvs.append((other, self._staging(fields[0], len(fields), other, mine, "recv")))
         self._exchange(sends, recvs)
-        for f, rows, buf in landing:
-            f[:, self._local(rows)].copy_(buf)
+        for other, theirs, mine in self.peers:
+            if mine is not None:
+                buf = self._staging(fields[0], len(fields), other, mine, "recv")
+                for slot, f in enumerate(fields):
+                    f[:, self._local(mine)].copy_(buf[slot])
 
     def reduce_halos(self, *grads: Tensor) -> None:
         """Backward exchange: send the gradient rows accumulated for other ranks' nodes to their
         owners, add what the others accumulated for this rank's nodes, and zero the halo rows."""
-        sends, recvs, landing = [], [], []
+        sends, recvs = [], []
         for other, theirs, mine in self.peers:
-            for slot, g in enumerate(grads):
-                if mine is not None:  # halo rows I computed partial sums for: they belong to `other`
-                    out = self._staging(g, slot, other, mine, "send")
-                    out.copy_(g[:, self._local(mine)])
-                    sends.append((other, out))
-                if theirs is not None:  # rows of mine `other` computed partial sums for
-                    buf = self._staging(g, slot, other, theirs, "recv")
-                    recvs.append((other, buf))
-                    landing.append((g, theirs, buf))
+            if mine is not None:  # halo rows I computed partial sums for: they belong to `other`
+                out = self._staging(grads[0], len(grads), other, mine, "send")
+                for slot, g in enumerate(grads):
+                    out[slot].copy_(g[:, self._local(mine)])
+                sends.append((other, out))
+            if theirs is not None:  # rows of mine `other` computed partial sums for
+                recvs.append((other, self._staging(grads[0], len(grads), other, theirs, "recv")))
         self._exchange(sends, recvs)
-        for g, rows, buf in landing:
-            g[:, self._local(rows)].add_(buf)
+        for other, theirs, mine in self.peers:
+            if theirs is not None:
+                buf = self._staging(grads[0], len(grads), other, theirs, "recv")
+                for slot, g in enumerate(grads):
+                    g[:, self._local(theirs)].add_(buf[slot])
         for g in grads:
             g[:, : self.lo - self.elo].zero_()
             g[:, self.hi - self.elo:].zero_()
