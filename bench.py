@@ -138,7 +138,7 @@ def run_reference(args: argparse.Namespace, cfg: dict) -> None:
     times = []
     for _ in range(max(0, min(args.warmup, 1))):
         cpu_layer_rate(cfg)
-    for _ in range(min(steps, 3)):
+    for _ in range(min(steps, 10)):  # every step is a bounded sample (a few seconds on all host cores); at most ten of them
         base = cpu_layer_rate(cfg)
         times.append(base["seconds"])
     assert base is not None
@@ -146,7 +146,7 @@ def run_reference(args: argparse.Namespace, cfg: dict) -> None:
     value = base["value"] * base["seconds"] / sec
     line = {
         "impl": "reference", "metric": "gauge-attn fwd+bwd neighbour-edges/sec", "value": value, "unit": "edges/s", "n_gpus": args.gpus,
-        "steps": min(steps, 3), "warmup": min(args.warmup, 1), "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "steps": min(steps, 10), "warmup": min(args.warmup, 1), "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(cfg, args, 1),
         "cpu_baseline": {k: base[k] for k in ("unit", "cores", "kind", "sample")} | {"value": value},
