@@ -378,6 +378,7 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     gpu_uuid = getattr(torch.cuda.get_device_properties(local), "uuid", None)
     with ClockSampler(local, f"GPU-{gpu_uuid}" if gpu_uuid is not None else None) as clocks:
+        barrier()  # the samplers start at different times on different ranks: line the ranks up again before the clock starts
         start.record()
         for s in range(args.steps):
             step(s)
@@ -410,7 +411,8 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
         ws = [torch.empty_like(flat(q)) for _ in range(3)] + [torch.empty((n_rows_local, heads), dtype=torch.float32, device=device)]
         attention_backward(flat(g), flat(q), flat(k), flat(v), out0, lse0, tables, passes=7, workspace=tuple(ws))
         per_pass = {}
-        for name, mask in (("delta", 1), ("pass_t", 2), ("pass_s", 4)):
+        launches = 3  # forward, target-major pass (forms Delta = <dO, O> itself), source-major pass
+        for name, mask in (("pass_t", 3), ("pass_s", 4)):  # mask 3: Delta + dq in one kernel
             ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(5)]
             for a_ev, b_ev in ev:
                 a_ev.record()

@@ -31,15 +31,16 @@
 // One CTA = 8 owners x WARPS warps x one head x one sample.  The neighbour rows of one lattice row and the table
 // entries they need are copied into shared memory as raw bf16 / fp32, double-buffered: the copy of the next
 // (row pair, chunk) runs while the current one is consumed.  A staged field is one sub-tile per frequency block
-// (88 positions x 32 or 64 bytes) in the 32-byte / 64-byte shared-memory swizzle, so that ldmatrix is conflict-free
+// (88 or 56 positions x 32 or 64 bytes) in the 32-byte / 64-byte shared-memory swizzle, so that ldmatrix is conflict-free
 // without padding and a whole sub-tile is ONE TMA tensor copy (cp.async.bulk.tensor.3d over (column, longitude,
 // sample * row), completion on an mbarrier, issued by one thread).  Chunks that wrap the longitude seam, and head
 // layouts whose blocks are not exactly 16 / 32 columns, are staged with per-thread cp.async into the same swizzled
 // layout.  Tensor-core instruction: mma.sync m16n8k16 (bf16 inputs, fp32 accumulate); fragments via ldmatrix.
 //
 // Backward, two deterministic passes (no atomics):
-//   pass T: owners = targets.  Gram blocks of (q, k) and of (dO, v) give the logits and d alpha;
-//           ds = scale p (d alpha - Delta) weights (ds o tau) K -> dq.
+//   pass T: owners = targets.  Delta = <dO, O> per (target, head) from the owners' own rows (written out for pass S);
+//           Gram blocks of (q, k) and of (dO, v) give the logits and d alpha; ds = scale p (d alpha - Delta)
+//           weights (ds o tau) K -> dq.
 //   pass S: owners = SOURCES, neighbours = the targets that see them (transposed tables, their lse / Delta
 //           staged with them).  Same Gram blocks with the roles swapped, then (ds o conj tau) Q -> dk and
 //           (p o conj tau) dO -> dv.
@@ -70,6 +71,8 @@ struct TcArgs {
   const __nv_bfloat16 *own1, *own2;   // owners' fields:     q, -  |  q, dO  |  k, v
   const __nv_bfloat16 *nb1, *nb2;     // neighbours' fields: k, v  |  k, v   |  q, dO
   const float *lse, *delta;           // (nodes, H), backward
+  const __nv_bfloat16* out_fwd;       // pass T with delta_out: the forward's output, Delta = <dO, O> is formed here
+  float* delta_out;                   // pass T: where Delta is written for the source-major pass (null: read `delta`)
   __nv_bfloat16 *res1, *res2;         // out | dq | dk, dv
   float* lse_out;                     // forward
   const int *win_cnt, *win_lo, *win_off;
@@ -484,13 +487,34 @@ __global__ void __launch_bounds__(32 * WARPS, WARPS == 4 ? (MODE == TC_BWD_T ? 4
       for (int r = 0; r < 2; ++r) s2[kc][r] = PASS_S ? swap_neg(f2[KS0 + kc][r]) : swap_neg_lo(f2[KS0 + kc][r]);
   }
   float lse_o[2] = {0.f, 0.f}, dl_o[2] = {0.f, 0.f};  // pass T: the two accumulator-column owners' lse (base 2) and Delta
-  if (MODE == TC_BWD_T) {
+  if constexpr (MODE == TC_BWD_T) {
 #pragma unroll
     for (int e = 0; e < 2; ++e)
-      if (c0 + own_c + e < a.nlon) {
-        lse_o[e] = a.lse[(node0 + c0 + own_c + e) * a.H + h] * TC_LOG2E;
-        dl_o[e] = a.delta[(node0 + c0 + own_c + e) * a.H + h];
-      }
+      if (c0 + own_c + e < a.nlon) lse_o[e] = a.lse[(node0 + c0 + own_c + e) * a.H + h] * TC_LOG2E;
+    if (a.delta_out != nullptr) {
+      // Delta = <dO, O> over the head's columns of owner own_b: this thread holds 2 of every 8 columns of dO (f2);
+      // the same columns of O, then the four lanes of the owner add up.  Written for the source-major pass, and handed
+      // to the lanes that hold the owner as an accumulator column.
+      unsigned of[KQ][2];
+      load_owner_columns<KS0, NCF, KSC>(P, a.out_fwd + own_b_base, own_b_present, exact, words, h, c, of);
+      float d = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < KQ; ++ks)
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          d = fmaf(__uint_as_float(f2[ks][r] << 16), __uint_as_float(of[ks][r] << 16), d);
+          d = fmaf(__uint_as_float(f2[ks][r] & 0xffff0000u), __uint_as_float(of[ks][r] & 0xffff0000u), d);
+        }
+      d += __shfl_xor_sync(0xffffffffu, d, 1);
+      d += __shfl_xor_sync(0xffffffffu, d, 2);
+      if (c == 0 && own_b_present) a.delta_out[(node0 + c0 + own_b) * a.H + h] = d;
+#pragma unroll
+      for (int e = 0; e < 2; ++e) dl_o[e] = __shfl_sync(0xffffffffu, d, (2 * c + e) << 2);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 2; ++e)
+        if (c0 + own_c + e < a.nlon) dl_o[e] = a.delta[(node0 + c0 + own_c + e) * a.H + h];
+    }
   }
   float a1_0[4] = {0.f, 0.f, 0.f, 0.f}, a1_r[NCK][4], a1_i[NCK][4];
   float a2_0[4] = {0.f, 0.f, 0.f, 0.f}, a2_r[PASS_S ? NCK : 1][4], a2_i[PASS_S ? NCK : 1][4];
@@ -1000,7 +1024,8 @@ extern "C" int gm_lattice_attention_backward_tc(const void* dout, const void* q,
 }
 
 // passes: bit 0 = Delta, bit 1 = the target-major pass (dq), bit 2 = the source-major pass (dk, dv).  Running a
-// subset is for timing the passes separately; pass T and pass S read the Delta an earlier call left in `delta`.
+// subset is for timing the passes separately.  Bits 0 and 1 together: pass T forms Delta itself; without bit 0 the
+// passes read the Delta an earlier call left in `delta`.
 extern "C" int gm_lattice_attention_backward_tc_passes(const void* dout, const void* q, const void* k, const void* v, const void* out,
                                                        const float* lse, const int* win_cnt, const int* win_lo, const int* win_off,
                                                        const float* entries, const int* row_order, int n_order_rows,
@@ -1021,7 +1046,9 @@ extern "C" int gm_lattice_attention_backward_tc_passes(const void* dout, const v
   bool chunked = D % 8 == 0 && D <= 512 && a.plan.a0 % 8 == 0 && (2 * a.plan.ac) % 8 == 0 && a.plan.real_off % 8 == 0 &&
                  reinterpret_cast<uintptr_t>(dout) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
   for (int f = 0; f < a.plan.n_cf; ++f) chunked = chunked && a.plan.cf_off[f] % 8 == 0;
-  if (!(passes & 1)) {
+  // Delta = <dO, O>: formed inside the target-major pass when that pass runs in this call; by its own kernel otherwise
+  const bool fused_delta = (passes & 2) != 0 && n_order_rows > 0;
+  if (!(passes & 1) || fused_delta) {
   } else if (chunked)
     tc_delta_vec_kernel<<<(unsigned)((n_nodes + 7) / 8), 256, 0, cs>>>((const B*)dout, (const B*)out, delta, n_nodes, D, H, a.plan);
   else
@@ -1031,12 +1058,14 @@ extern "C" int gm_lattice_attention_backward_tc_passes(const void* dout, const v
   a.lse = lse; a.delta = delta;
   if (n_order_rows > 0 && (passes & 2)) {
     a.own1 = (const B*)q; a.own2 = (const B*)dout; a.nb1 = (const B*)k; a.nb2 = (const B*)v; a.res1 = (B*)dq; a.res2 = nullptr;
+    a.out_fwd = (const B*)out; a.delta_out = (passes & 1) ? delta : nullptr;
     a.win_cnt = win_cnt; a.win_lo = win_lo; a.win_off = win_off; a.entries = entries; a.row_order = row_order;
     status = dispatch_tc<TC_BWD_T>(a, n_order_rows, batch, cs);
     if (status != GM_OK) return status;
   }
   if (t_n_order_rows > 0 && (passes & 4)) {
     a.own1 = (const B*)k; a.own2 = (const B*)v; a.nb1 = (const B*)q; a.nb2 = (const B*)dout; a.res1 = (B*)dk; a.res2 = (B*)dv;
+    a.out_fwd = nullptr; a.delta_out = nullptr;
     a.win_cnt = t_win_cnt; a.win_lo = t_win_lo; a.win_off = t_win_off; a.entries = t_entries; a.row_order = t_row_order;
     status = dispatch_tc<TC_BWD_S>(a, t_n_order_rows, batch, cs);
   }

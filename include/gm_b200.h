@@ -290,7 +290,9 @@ int gm_lattice_attention_backward_tc(const void* dout, const void* q, const void
                                      int NORD, double scale, void* dq, void* dk, void* dv, float* delta, void* stream);
 
 /* The same with a pass mask (bit 0: Delta = <dO, O>; bit 1: target-major pass -> dq; bit 2: source-major pass ->
- * dk, dv), for timing the passes one by one; passes 2 and 4 read the Delta an earlier call left in `delta`. */
+ * dk, dv), for timing the passes one by one.  With bits 0 and 1 both set the target-major pass forms Delta itself and
+ * writes it to `delta` (no separate launch); bit 0 alone runs the stand-alone Delta kernel; passes 2 and 4 without bit 0
+ * read the Delta an earlier call left in `delta`. */
 int gm_lattice_attention_backward_tc_passes(const void* dout, const void* q, const void* k, const void* v, const void* out,
                                             const float* lse, const int* win_cnt, const int* win_lo, const int* win_off,
                                             const float* entries, const int* row_order, int n_order_rows, const int* t_win_cnt,
