@@ -58,6 +58,8 @@ def parse() -> argparse.Namespace:
                    help="lattice: compact-table fast path (default); csr: general per-edge-table kernels")
     p.add_argument("--radius-rows", type=float, default=None,
                    help="neighbourhood radius in lattice row spacings (default: the workload's own, 3); other values are for profiling")
+    p.add_argument("--no-overlap", action="store_true",
+                   help="N > 1: exchange the halos before / after the layer instead of running the layer around the exchange")
     p.add_argument("--per-rank", action="store_true",
                    help="every rank prints its own per-step timings (halo exchange in, forward, backward, halo sums out) to stderr")
     p.add_argument("--no-cpu-baseline", action="store_true")
@@ -283,7 +285,7 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
     from gm_attention_b200.fields import FieldType
     from gm_attention_b200.geometry import midpoint_lattice
     from gm_attention_b200.nn import fused_attention as fa
-    from gm_attention_b200.parallel import (BandPlan, HaloExchanger, band_geometry, row_degrees, row_pair_counts,
+    from gm_attention_b200.parallel import (BandPlan, HaloExchanger, band_geometry, overlap_tables, row_degrees, row_pair_counts,
                                             tensor_core_row_cost)
 
     _lib.lib()
@@ -347,9 +349,37 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
 
     mark_ev = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(args.steps)]  # step start, step end
 
+    # With latitude bands on the tensor-core path the layer runs AROUND the halo exchange: the forward of the rows that
+    # need no halo while the K / V halos travel, the source-major backward of the rank's own rows while the dK / dV halo
+    # sums travel (the halo rows' sums are formed first).
+    split = overlap_tables(tables, plan, rank) if (world > 1 and args.kernel == "lattice" and args.dtype == "bf16" and not args.no_overlap) else None
+
     def step(index: int | None = None):
         if index is not None:
             mark_ev[index][0].record()
+        if split is not None:
+            pending = halo.start_fill(k, v)
+            if index is not None:
+                fwd_ev[index][0].record()
+            out, lse = attention_forward(flat(q), flat(k), flat(v), split.interior)
+            halo.finish_fill(pending)
+            attention_forward(flat(q), flat(k), flat(v), split.boundary, out=out, lse=lse)
+            if index is not None:
+                fwd_ev[index][1].record()
+                bwd_ev[index][0].record()
+            ws = (torch.zeros_like(flat(q)), torch.zeros_like(flat(q)), torch.zeros_like(flat(q)),
+                  torch.empty((batch * n_ext, heads), dtype=torch.float32, device=device))
+            attention_backward(flat(g), flat(q), flat(k), flat(v), out, lse, split.full, passes=3, workspace=ws)
+            attention_backward(flat(g), flat(q), flat(k), flat(v), out, lse, split.halo_sources, passes=4, workspace=ws)
+            dq, dk, dv = ws[:3]
+            pending = halo.start_reduce(dk.view(shape), dv.view(shape))
+            attention_backward(flat(g), flat(q), flat(k), flat(v), out, lse, split.owned_sources, passes=4, workspace=ws)
+            if index is not None:
+                bwd_ev[index][1].record()
+            halo.finish_reduce(pending)
+            if index is not None:
+                mark_ev[index][1].record()
+            return out, dq, dk, dv
         if halo is not None:
             halo.fill_halos(k, v)
         if index is not None:
@@ -411,7 +441,9 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
         ws = [torch.empty_like(flat(q)) for _ in range(3)] + [torch.empty((n_rows_local, heads), dtype=torch.float32, device=device)]
         attention_backward(flat(g), flat(q), flat(k), flat(v), out0, lse0, tables, passes=7, workspace=tuple(ws))
         per_pass = {}
-        launches = 3  # forward, target-major pass (forms Delta = <dO, O> itself), source-major pass
+        # forward, target-major pass (forms Delta = <dO, O> itself), source-major pass; around a halo exchange the forward and
+        # the source-major pass are two launches each
+        launches = 5 if split is not None else 3
         for name, mask in (("pass_t", 3), ("pass_s", 4)):  # mask 3: Delta + dq in one kernel
             ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(5)]
             for a_ev, b_ev in ev:

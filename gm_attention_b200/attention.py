@@ -289,14 +289,19 @@ def tensor_core_layout_supported(rows: tuple[tuple[int, int, int, int, int], ...
 TENSOR_CORES = os.environ.get("GM_LATTICE_TENSOR_CORES", "auto")
 
 
-def lattice_attention_forward(q: Tensor, k: Tensor, v: Tensor, t: LatticeTables, tensor_cores: bool | None = None) -> tuple[Tensor, Tensor]:
+def lattice_attention_forward(q: Tensor, k: Tensor, v: Tensor, t: LatticeTables, tensor_cores: bool | None = None,
+                              out: Tensor | None = None, lse: Tensor | None = None) -> tuple[Tensor, Tensor]:
+    """``(out, lse)`` for the target rows in ``t.row_order``.  ``out`` / ``lse`` of an earlier call can be passed in to
+    have another set of rows written into the same buffers (rows outside every set keep 0 / -inf)."""
     device, batch = _check_lattice(q, k, v, t)
     if tensor_cores is None:
         tensor_cores = TENSOR_CORES != "0" and q.dtype == torch.bfloat16 and tensor_core_layout_supported(t.desc_rows)
     full = t.row_order.numel() == t.rows
-    out = torch.empty_like(q) if full else torch.zeros_like(q)
-    lse = torch.empty((q.shape[0], t.heads), dtype=torch.float32, device=device) if full else \
-        torch.full((q.shape[0], t.heads), float("-inf"), dtype=torch.float32, device=device)
+    if out is None:
+        out = torch.empty_like(q) if full else torch.zeros_like(q)
+    if lse is None:
+        lse = torch.empty((q.shape[0], t.heads), dtype=torch.float32, device=device) if full else \
+            torch.full((q.shape[0], t.heads), float("-inf"), dtype=torch.float32, device=device)
     desc = t.host_descriptor()
     common = (_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(t.win_cnt), _lib.ptr(t.win_lo), _lib.ptr(t.win_off), _lib.ptr(t.entries),
               _lib.ptr(t.row_order), t.row_order.numel(), ctypes.addressof(desc), len(t.desc_rows), t.rows, t.nlon, batch, q.shape[1],

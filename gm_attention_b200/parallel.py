@@ -132,17 +132,16 @@ class HaloExchanger:
             self._buffers[key] = buf
         return buf
 
-    def _exchange(self, sends: list[tuple[int, Tensor]], recvs: list[tuple[int, Tensor]]) -> None:
+    def _post(self, sends: list[tuple[int, Tensor]], recvs: list[tuple[int, Tensor]]) -> list:
         if not sends and not recvs:
-            return
+            return []
         ops = [dist.P2POp(dist.isend, t, peer, self.group) for peer, t in sends]
         ops += [dist.P2POp(dist.irecv, t, peer, self.group) for peer, t in recvs]
-        for work in dist.batch_isend_irecv(ops):
-            work.wait()
+        return dist.batch_isend_irecv(ops)
 
-    def fill_halos(self, *fields: Tensor) -> None:
-        """Forward exchange: copy the owners' rows into this rank's halo rows of every field (one message per peer
-        and direction carries all fields)."""
+    def start_fill(self, *fields: Tensor):
+        """Forward exchange, first half: stage the rows the neighbours need and enqueue the messages.  Work that does
+        not read the halo rows can be launched before :meth:`finish_fill` and runs while the messages travel."""
         sends, recvs = [], []
         for other, theirs, mine in self.peers:
             if theirs is not None:
@@ -152,16 +151,27 @@ class HaloExchanger:
                 sends.append((other, out))
             if mine is not None:
                 recvs.append((other, self._staging(fields[0], len(fields), other, mine, "recv")))
-        self._exchange(sends, recvs)
+        return self._post(sends, recvs), fields
+
+    def finish_fill(self, handle) -> None:
+        """Second half: wait for the messages and copy the owners' rows into this rank's halo rows."""
+        works, fields = handle
+        for work in works:
+            work.wait()
         for other, theirs, mine in self.peers:
             if mine is not None:
                 buf = self._staging(fields[0], len(fields), other, mine, "recv")
                 for slot, f in enumerate(fields):
                     f[:, self._local(mine)].copy_(buf[slot])
 
-    def reduce_halos(self, *grads: Tensor) -> None:
-        """Backward exchange: send the gradient rows accumulated for other ranks' nodes to their
-        owners, add what the others accumulated for this rank's nodes, and zero the halo rows."""
+    def fill_halos(self, *fields: Tensor) -> None:
+        """Forward exchange: copy the owners' rows into this rank's halo rows of every field (one message per peer
+        and direction carries all fields)."""
+        self.finish_fill(self.start_fill(*fields))
+
+    def start_reduce(self, *grads: Tensor):
+        """Backward exchange, first half: send the gradient rows accumulated for other ranks' nodes (they must be
+        final) to their owners.  The rank's own rows may still be written until :meth:`finish_reduce`."""
         sends, recvs = [], []
         for other, theirs, mine in self.peers:
             if mine is not None:  # halo rows I computed partial sums for: they belong to `other`
@@ -171,7 +181,13 @@ class HaloExchanger:
                 sends.append((other, out))
             if theirs is not None:  # rows of mine `other` computed partial sums for
                 recvs.append((other, self._staging(grads[0], len(grads), other, theirs, "recv")))
-        self._exchange(sends, recvs)
+        return self._post(sends, recvs), grads
+
+    def finish_reduce(self, handle) -> None:
+        """Second half: add what the others accumulated for this rank's nodes, and zero the halo rows."""
+        works, grads = handle
+        for work in works:
+            work.wait()
         for other, theirs, mine in self.peers:
             if theirs is not None:
                 buf = self._staging(grads[0], len(grads), other, theirs, "recv")
@@ -180,6 +196,52 @@ class HaloExchanger:
         for g in grads:
             g[:, : self.lo - self.elo].zero_()
             g[:, self.hi - self.elo:].zero_()
+
+    def reduce_halos(self, *grads: Tensor) -> None:
+        """Backward exchange: send the gradient rows accumulated for other ranks' nodes to their
+        owners, add what the others accumulated for this rank's nodes, and zero the halo rows."""
+        self.finish_reduce(self.start_reduce(*grads))
+
+
+@dataclass(frozen=True)
+class OverlapTables:
+    """Row subsets of a rank's lattice tables for running the layer around the halo exchange."""
+
+    full: object           # all owned target rows, all sources (as built)
+    interior: object       # target rows whose neighbour rows are all owned: need no halo
+    boundary: object       # the other target rows
+    halo_sources: object   # source-major pass over the halo rows only (their dk, dv are what the owners are sent)
+    owned_sources: object  # source-major pass over the rank's own rows
+
+
+def overlap_tables(tables, plan: BandPlan, rank: int) -> OverlapTables:
+    """Split the row lists of ``tables`` (built by :func:`band_geometry` + ``build_lattice_tables`` for ``rank``) so that
+    the forward of the interior rows can run while the K / V halos travel and the source-major backward of the rank's own
+    rows while the dK / dV halo sums travel."""
+    import dataclasses
+
+    lo, hi = plan.owned(rank)
+    elo, ehi = plan.extended(rank)
+    a, b, w = lo - elo, hi - elo, plan.halo  # owned rows in extended-row indices
+    device = tables.row_order.device
+
+    def pick(rows: Tensor, keep) -> Tensor:
+        values = rows.cpu().tolist()
+        return torch.tensor([r for r in values if keep(r)], dtype=rows.dtype, device=device)
+
+    def is_interior(r: int) -> bool:
+        return (elo == lo or r - w >= a) and (ehi == hi or r + w < b)
+
+    def is_halo(r: int) -> bool:
+        return r < a or r >= b
+
+    return OverlapTables(
+        full=tables,
+        interior=dataclasses.replace(tables, row_order=pick(tables.row_order, is_interior)),
+        boundary=dataclasses.replace(tables, row_order=pick(tables.row_order, lambda r: not is_interior(r))),
+        halo_sources=dataclasses.replace(tables, t_row_order=pick(tables.t_row_order, is_halo)),
+        owned_sources=dataclasses.replace(tables, t_row_order=pick(tables.t_row_order, lambda r: not is_halo(r))),
+    )
 
 
 def band_geometry(lattice, plan: BandPlan, rank: int, radius: float, *, max_frequency: int = 4, dtype: torch.dtype = torch.float32):

@@ -210,3 +210,47 @@ def test_host_pipeline_equals_the_device_path():
     want = (out, *lattice_attention_backward(G, Q, K, V, out, lse, lat))
     for got, ref in zip(outs, want):
         assert torch.equal(got, ref.cpu())
+
+
+def test_layer_split_around_a_halo_exchange_equals_one_call():
+    """The row subsets used to overlap the halo exchange (interior / boundary target rows; halo / owned source rows)
+    reproduce the unsplit forward and backward of a rank's band bit for bit (one GPU, no exchange: the band of rank 1
+    of 3 with its halo rows filled from the full fields)."""
+    import dataclasses
+
+    from gm_attention_b200.attention import AttentionTables, build_lattice_tables, lattice_attention_backward, lattice_attention_forward
+    from gm_attention_b200.fields import FieldType
+    from gm_attention_b200.geometry import midpoint_lattice
+    from gm_attention_b200.nn import fused_attention as fa
+    from gm_attention_b200.parallel import BandPlan, band_geometry, overlap_tables
+
+    dev = torch.device("cuda", 0)
+    nlat, nlon, heads, batch = 24, 64, 2, 2
+    radius = 2.5 * math.pi / nlat
+    attn = FieldType({0: 16, 1: 16, 2: 16})
+    full = attn.scaled(heads)
+    lattice = midpoint_lattice(nlat, nlon, dev)
+    plan = BandPlan(nlat, nlon, lattice.band(radius), (0, 7, 16, 24))
+    rank = 1
+    elo, ehi = plan.extended(rank)
+    edges = band_geometry(lattice, plan, rank, radius, max_frequency=2, dtype=torch.float32)
+    geo = fa.geometry(edges, radius, "hard", torch.float32)
+    p = fa._plan(type("Layer", (), {})(), attn, full, heads)
+    gen = AttentionTables(geo.transport, geo.bias, geo.inside, geo.row_ptr, geo.source, p.rows, heads, 1 / math.sqrt(attn.dimension))
+    t = build_lattice_tables(gen, ehi - elo, nlon, p.rows, heads, gen.scale)
+    split = overlap_tables(t, plan, rank)
+    assert split.interior.row_order.numel() > 0 and split.boundary.row_order.numel() > 0
+    assert split.interior.row_order.numel() + split.boundary.row_order.numel() == t.row_order.numel()
+    assert split.halo_sources.t_row_order.numel() + split.owned_sources.t_row_order.numel() == t.t_row_order.numel()
+    n = batch * (ehi - elo) * nlon
+    Q, K, V, G = (torch.from_numpy(x).bfloat16().to(dev) for x in seeded((n, full.dimension), 61, np.float32, 4))
+    out, lse = lattice_attention_forward(Q, K, V, t)
+    want = (out, lse, *lattice_attention_backward(G, Q, K, V, out, lse, t))
+    out2, lse2 = lattice_attention_forward(Q, K, V, split.interior)
+    lattice_attention_forward(Q, K, V, split.boundary, out=out2, lse=lse2)
+    ws = (torch.zeros_like(Q), torch.zeros_like(Q), torch.zeros_like(Q), torch.empty((n, heads), dtype=torch.float32, device=dev))
+    lattice_attention_backward(G, Q, K, V, out2, lse2, split.full, passes=3, workspace=ws)
+    lattice_attention_backward(G, Q, K, V, out2, lse2, split.halo_sources, passes=4, workspace=ws)
+    lattice_attention_backward(G, Q, K, V, out2, lse2, split.owned_sources, passes=4, workspace=ws)
+    for a, b in zip(want, (out2, lse2, *ws[:3])):
+        assert torch.equal(a, b)
