@@ -457,7 +457,7 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
         top_ms = per_pass["pass_s"]
         top_bytes = 6 * n_rows_local * D * elem + 2 * n_rows_local * heads * 4
         # DRAM read + write of this kernel per node, from the ncu capture on the 128x256x4 workload (profiles/), scaled by nodes
-        top_traffic = int(4851 * n_rows_local)
+        top_traffic = int(4926 * n_rows_local)
         del out0, lse0, ws
     else:
         per_pass = None
