@@ -6,14 +6,16 @@
 // (scores :145-165, softmax :295-316, softmax backward :320-348, depthwise
 // message :174-206, its backward :211-232); the kernels themselves are new:
 //
-//  * scores: one block per target, one WARP per edge with the lanes striding
-//    the key row (coalesced 128-byte reads of k_j), per-head sums by warp
-//    shuffle; the row's logits live in shared memory (or, for very large
-//    neighbourhoods, in the alpha output itself) and are normalised there.
-//  * every per-column walk (softmax backward, conv forward/backward) runs one
-//    thread per flat column with the column's slot (frequency, head, copy,
-//    real/imaginary part, partner column) decoded ONCE per block into shared
-//    memory instead of once per (column, edge).
+//  * scores, head-grouped (H a power of two, the usual case): one warp per target, the lanes split into H head
+//    groups, every lane owning a few copies of every frequency; four edges' gathers of k_j are in flight; the raw
+//    logits go to alpha and the same warp normalises the row in place.
+//  * scores, general: one block per target, one WARP per edge with the lanes striding the key row (coalesced
+//    128-byte reads of k_j), per-head sums by warp shuffle; the row's logits live in shared memory (or, for very
+//    large neighbourhoods, in the alpha output itself) and are normalised there.
+//  * softmax backward, conv forward / backward: one warp per target and one LANE per work item -- a (head,
+//    frequency, copy) or (frequency, copy): a scalar column or a (re, im) column pair -- listed once per CTA in
+//    shared memory; a lane walks the node's edges in order (sequential sums per output) with four edges' loads in
+//    flight, 8-byte accesses for the pairs where the address allows, atomics only for the scattered dk / dv.
 #include "common.cuh"
 
 namespace gmb {
