@@ -159,8 +159,9 @@ __device__ __forceinline__ int flat_column(const TcPlan& P, int h, int c) {
   return (f < P.n_cf && r < 2 * P.ac) ? P.cf_off[f] + 2 * h * P.ac + r : -1;
 }
 
-// owners per CTA = 8 x warps: 8 warps forward, 4 in the backward passes (more registers per thread, three CTAs per SM)
-constexpr int TN_WARPS(int mode) { return mode == TC_FWD ? 8 : 4; }
+// owners per CTA = 8 x warps.  4 warps (32 owners) in every pass: four CTAs per SM at 128 registers (forward, pass T),
+// three at 168 (pass S); 8 warps (64 owners, 80-position chunks) stay instantiable
+constexpr int TN_WARPS(int mode) { return 4; }
 // positions a staged chunk advances by (a multiple of 16): 64 owners + a window of up to 17 fit one chunk of 80, 32 owners
 // + 17 one of 48 (smaller buffers: four CTAs per SM).  Staged per chunk: 8 more, a step of 16 may start 8 before the end.
 constexpr __host__ __device__ int tn_advance(int owners) { return owners >= 64 ? 80 : 48; }
@@ -398,7 +399,7 @@ struct TnRowPair {
 };
 
 template <int KS0, int NCF, int KSC, int MODE, int WARPS>
-__global__ void __launch_bounds__(32 * WARPS, WARPS == 4 ? (MODE == TC_BWD_T ? 4 : 3) : 2) lattice_tn_kernel(const __grid_constant__ TcArgs a) {
+__global__ void __launch_bounds__(32 * WARPS, WARPS == 4 ? (MODE == TC_BWD_S ? 3 : 4) : 2) lattice_tn_kernel(const __grid_constant__ TcArgs a) {
   constexpr int TL = 8 * WARPS, THREADS = 32 * WARPS;
   constexpr int TN_ADV = tn_advance(TL), TN_ROWS = tn_rows(TL);
   using L = TnLayout<KS0, NCF, KSC, TL>;

@@ -305,10 +305,10 @@ def row_pair_counts(lattice, radius: float) -> Tensor:
 def tensor_core_row_cost(pair_counts: Tensor) -> list[float]:
     """Relative cost of one lattice row under the tensor-core lattice kernels (forward + both backward passes).
     A warp owns 8 consecutive owners and walks, for every neighbour row, the 7 + cnt positions their windows cover in
-    steps of 16; a CTA stages the neighbour row in chunks of 80 positions (64 owners forward, 32 in the backward
-    passes) and pays a fixed cost per owner tile.  The weights are a fit to measured times of row groups from the pole
-    to the equator of a 256 x 512 lattice (within 15 % for every group).  Narrow equatorial windows cost several times
-    more PER EDGE than whole-row polar windows, which an edge-count balance ignores."""
+    steps of 16; a CTA stages the neighbour row in chunks and pays a fixed cost per owner tile.  The weights are a
+    fit to measured times of row groups from the pole to the equator of a 256 x 512 lattice (within 15 % for every
+    group; the bands of an 8-way split, each timed alone, come out within 3 % of one another).  Narrow equatorial
+    windows cost several times more PER EDGE than whole-row polar windows, which an edge-count balance ignores."""
     cnt = pair_counts.to(torch.float64)
     present = cnt > 0
     steps = torch.ceil((7 + cnt) / 16)
