@@ -87,6 +87,15 @@ def test_factored_against_reference_driver(reference_modules, case, dtype):
         lhs = float((g_rows.astype(np.float64) * rows_np).sum())
         zsum = float((dzc.cpu().numpy().astype(np.float64) * zc).sum() + (dzr.cpu().numpy().astype(np.float64) * zr).sum())
         assert abs(zsum - lhs) <= 1e-3 * abs(lhs) + 1e-6  # rows are linear in Z
+        # ... and the numpy restatement of the reference arithmetic, which has no width limit
+        from oracle import ops_np
+
+        mag = lambda x: max(1.0, float(np.abs(x).max())) if x.size else 1.0
+        rows_np2 = ops_np.factored_forward(h, zc, zr, c.angular, c.transport, c.rho, desc, c.source, p.d_out)
+        assert_close(rows.cpu().numpy(), rows_np2, 10 * rtol, 10 * atol * mag(rows_np2), "rows vs restatement")
+        for name, got, ref_np in zip(("dh", "dzc", "dzr"), (dh, dzc, dzr),
+                                     ops_np.factored_backward(g_rows, h, zc, zr, c.angular, c.transport, c.rho, desc, c.source)):
+            assert_close(got.cpu().numpy(), ref_np, 10 * rtol, 100 * atol * mag(ref_np), name + " vs restatement")
         return
     ref = reference_modules["gm_factored_cpu"]
     cpu = [t(x) for x in (h, zc, zr, c.angular, c.transport, c.rho, desc, c.source)]
