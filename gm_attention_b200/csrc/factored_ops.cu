@@ -81,8 +81,10 @@ __device__ __forceinline__ void stage_node(const FArgs<T>& a, int64_t j, T* zc_s
   for (int x = threadIdx.x; x < nr; x += blockDim.x) zr_s[x] = a.zr[j * nr + x];
 }
 
-template <typename T>
+// KT: the trunk width + 1 when it is known at compile time (17: the reference's default radial trunk), 0 = any k <= FMAX_K
+template <typename T, int KT>
 __global__ void __launch_bounds__(FTHREADS) factored_forward_kernel(FArgs<T> a, int pitch) {
+  constexpr int KMAX = KT ? KT : FMAX_K;
   extern __shared__ __align__(16) unsigned char raw[];
   T* zc_s = reinterpret_cast<T*>(raw);
   T* zr_s = zc_s + a.k * a.wc * 2;
@@ -100,10 +102,10 @@ __global__ void __launch_bounds__(FTHREADS) factored_forward_kernel(FArgs<T> a, 
       const bool mine = x < last;
       const int64_t e = mine ? a.order[x] : -1;
       if (mine) {
-        T hh[FMAX_K];
+        T hh[KMAX];
         hh[0] = T(1);
 #pragma unroll
-        for (int t = 1; t < FMAX_K; ++t) hh[t] = t < a.k ? a.h[e * (a.k - 1) + t - 1] : T(0);
+        for (int t = 1; t < KMAX; ++t) hh[t] = (KT || t < a.k) ? a.h[e * (a.k - 1) + t - 1] : T(0);
         // Blocks are sorted by output offset; blocks of one offset add into the same columns.  The
         // first block of a group writes, the following ones add to the edge's row.
         int open_offset = -1;
@@ -117,8 +119,8 @@ __global__ void __launch_bounds__(FTHREADS) factored_forward_kernel(FArgs<T> a, 
             for (int c = 0; c < bm; ++c) {
               T s = T(0);
 #pragma unroll
-              for (int t = 0; t < FMAX_K; ++t)
-                if (t < a.k) s += hh[t] * zr_s[t * a.wr + zoff + c];
+              for (int t = 0; t < KMAX; ++t)
+                if (KT || t < a.k) s += hh[t] * zr_s[t * a.wr + zoff + c];
               row[ooff + c] = first_of_group ? s : row[ooff + c] + s;
             }
             continue;
@@ -140,8 +142,8 @@ __global__ void __launch_bounds__(FTHREADS) factored_forward_kernel(FArgs<T> a, 
             for (; c + 2 <= bm; c += 2) {
               T ur0 = T(0), ui0 = T(0), ur1 = T(0), ui1 = T(0);
 #pragma unroll
-              for (int t = 0; t < FMAX_K; ++t)
-                if (t < a.k) {
+              for (int t = 0; t < KMAX; ++t)
+                if (KT || t < a.k) {
                   const float4 z = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(zc_s) + (t * a.wc + zoff + c) * 2);
                   ur0 += hh[t] * (T)z.x; ui0 += hh[t] * (T)z.y;
                   ur1 += hh[t] * (T)z.z; ui1 += hh[t] * (T)z.w;
@@ -153,8 +155,8 @@ __global__ void __launch_bounds__(FTHREADS) factored_forward_kernel(FArgs<T> a, 
           for (; c < bm; ++c) {
             T ur = T(0), ui = T(0);
 #pragma unroll
-            for (int t = 0; t < FMAX_K; ++t)
-              if (t < a.k) {
+            for (int t = 0; t < KMAX; ++t)
+              if (KT || t < a.k) {
                 ur += hh[t] * zc_s[(t * a.wc + zoff + c) * 2];
                 ui += hh[t] * zc_s[(t * a.wc + zoff + c) * 2 + 1];
               }
@@ -338,10 +340,12 @@ extern "C" int gm_factored_forward(const void* h, const void* zc, const void* zr
     a.out = (T*)out;
     const int pitch = d_out | 1;  // per-thread output rows in shared memory, odd pitch
     const size_t smem = ((size_t)k * 2 * wc + ((size_t)k * wr + 3) / 4 * 4 + (size_t)FTHREADS * pitch) * sizeof(T);
-    int st = allow_smem(factored_forward_kernel<T>, smem, "gm_factored_forward");
+    int st = k == 17 ? allow_smem(factored_forward_kernel<T, 17>, smem, "gm_factored_forward")
+                     : allow_smem(factored_forward_kernel<T, 0>, smem, "gm_factored_forward");
     if (st != GM_OK) return st;
     const unsigned blocks = (unsigned)(n_groups < (1 << 20) ? n_groups : (1 << 20));
-    factored_forward_kernel<T><<<blocks, FTHREADS, smem, (cudaStream_t)stream>>>(a, pitch);
+    if (k == 17) factored_forward_kernel<T, 17><<<blocks, FTHREADS, smem, (cudaStream_t)stream>>>(a, pitch);
+    else factored_forward_kernel<T, 0><<<blocks, FTHREADS, smem, (cudaStream_t)stream>>>(a, pitch);
     return launch_status("gm_factored_forward");
   };
   return dtype == GM_F32 ? run(float()) : run(double());
