@@ -162,18 +162,20 @@ __device__ __forceinline__ void row_axpy(const T* w_s, int r, int trunk, T s, T 
 
 // M_idx = <W rows, h> + b
 template <typename T>
-__device__ __forceinline__ void entry(const PArgs<T>& p, const T* w_s, const T* b_s, int idx, const T (&h)[PMAX], T& mr, T& mi) {
+__device__ __forceinline__ void entry(const PArgs<T>& p, const T* w_s, const T* b_s, int trunk, int idx, const T (&h)[PMAX], T& mr, T& mi) {
   if (p.flags & MATRIX_COMPLEX) {
-    mr = b_s[2 * idx] + row_dot(w_s, 2 * idx, p.trunk, h);
-    mi = b_s[2 * idx + 1] + row_dot(w_s, 2 * idx + 1, p.trunk, h);
+    mr = b_s[2 * idx] + row_dot(w_s, 2 * idx, trunk, h);
+    mi = b_s[2 * idx + 1] + row_dot(w_s, 2 * idx + 1, trunk, h);
   } else {
-    mr = b_s[idx] + row_dot(w_s, idx, p.trunk, h);
+    mr = b_s[idx] + row_dot(w_s, idx, trunk, h);
     mi = T(0);
   }
 }
 
-template <typename T>
+// FULL: the trunk is exactly PMAX wide (the usual 16): the trunk loops carry no bound checks
+template <typename T, bool FULL>
 __global__ void pairs_forward_kernel(PArgs<T> p) {
+  const int trunk = FULL ? PMAX : p.trunk;
   extern __shared__ __align__(16) unsigned char pairs_smem[];
   T* w_s = reinterpret_cast<T*>(pairs_smem);
   T* b_s = w_s + ((p.flags & MATRIX_COMPLEX) ? 2 : 1) * p.a * p.b * PMAX;
@@ -187,7 +189,7 @@ __global__ void pairs_forward_kernel(PArgs<T> p) {
       for (int x = 0; x < PMAX; ++x)
         if (x < p.a) {
           T mr, mi;
-          entry(p, w_s, b_s, bi * p.a + x, h, mr, mi);
+          entry(p, w_s, b_s, trunk, bi * p.a + x, h, mr, mi);
           accr += mr * ur[x] - mi * ui[x];
           acci += mr * ui[x] + mi * ur[x];
         }
@@ -200,8 +202,10 @@ __global__ void pairs_forward_kernel(PArgs<T> p) {
   }
 }
 
-template <typename T>
+// FULL: the trunk is exactly PMAX wide (the usual 16): the trunk loops carry no bound checks
+template <typename T, bool FULL>
 __global__ void pairs_backward_kernel(PArgs<T> p) {
+  const int trunk = FULL ? PMAX : p.trunk;
   extern __shared__ __align__(16) unsigned char pairs_smem[];
   T* w_s = reinterpret_cast<T*>(pairs_smem);
   T* b_s = w_s + ((p.flags & MATRIX_COMPLEX) ? 2 : 1) * p.a * p.b * PMAX;
@@ -229,16 +233,16 @@ __global__ void pairs_backward_kernel(PArgs<T> p) {
           const int idx = bi * p.a + x;
           const T gmr = gqr * ur[x] + gqi * ui[x], gmi = gqi * ur[x] - gqr * ui[x];  // gm = gq conj(uu)
           T mr, mi;
-          entry(p, w_s, b_s, idx, h, mr, mi);
+          entry(p, w_s, b_s, trunk, idx, h, mr, mi);
           gur[x] += mr * gqr + mi * gqi;  // guu += conj(m) gq
           gui[x] += mr * gqi - mi * gqr;
           if (p.flags & MATRIX_COMPLEX) {
-            row_axpy(w_s, 2 * idx, p.trunk, gmr, gh);
-            row_axpy(w_s, 2 * idx + 1, p.trunk, gmi, gh);
+            row_axpy(w_s, 2 * idx, trunk, gmr, gh);
+            row_axpy(w_s, 2 * idx + 1, trunk, gmi, gh);
             p.grad_k[(int64_t)(2 * idx) * p.n_edges + e] = gmr;
             p.grad_k[(int64_t)(2 * idx + 1) * p.n_edges + e] = gmi;
           } else {
-            row_axpy(w_s, idx, p.trunk, gmr, gh);
+            row_axpy(w_s, idx, trunk, gmr, gh);
             p.grad_k[(int64_t)idx * p.n_edges + e] = gmr;
           }
         }
@@ -288,10 +292,11 @@ extern "C" int gm_pairs_forward(const void* hidden, const void* weight, const vo
                (const T*)post, (const T*)scale, (T*)out, nullptr, nullptr, nullptr, nullptr};
     const int rows = ((flags & MATRIX_COMPLEX) ? 2 : 1) * a * b;
     const size_t smem = (size_t)rows * (PMAX + 1) * sizeof(T);
-    int st = allow_smem(pairs_forward_kernel<T>, smem, "gm_pairs_forward");
+    int st = trunk == PMAX ? allow_smem(pairs_forward_kernel<T, true>, smem, "gm_pairs_forward") : allow_smem(pairs_forward_kernel<T, false>, smem, "gm_pairs_forward");
     if (st != GM_OK) return st;
     const int64_t want = (n_edges + 127) / 128, cap = (int64_t)sm_count() * 8;  // each CTA stages the weights once and strides the edges
-    pairs_forward_kernel<T><<<(unsigned)(want < cap ? want : cap), 128, smem, (cudaStream_t)stream>>>(p);
+    if (trunk == PMAX) pairs_forward_kernel<T, true><<<(unsigned)(want < cap ? want : cap), 128, smem, (cudaStream_t)stream>>>(p);
+    else pairs_forward_kernel<T, false><<<(unsigned)(want < cap ? want : cap), 128, smem, (cudaStream_t)stream>>>(p);
     return launch_status("gm_pairs_forward");
   };
   return dtype == GM_F32 ? run(float()) : run(double());
@@ -309,10 +314,11 @@ extern "C" int gm_pairs_backward(const void* hidden, const void* weight, const v
                (const T*)post, (const T*)scale, nullptr, (const T*)grad_out, (T*)grad_u, (T*)grad_hidden, (T*)grad_k};
     const int rows = ((flags & MATRIX_COMPLEX) ? 2 : 1) * a * b;
     const size_t smem = (size_t)rows * (PMAX + 1) * sizeof(T);
-    int st = allow_smem(pairs_backward_kernel<T>, smem, "gm_pairs_backward");
+    int st = trunk == PMAX ? allow_smem(pairs_backward_kernel<T, true>, smem, "gm_pairs_backward") : allow_smem(pairs_backward_kernel<T, false>, smem, "gm_pairs_backward");
     if (st != GM_OK) return st;
     const int64_t want = (n_edges + 127) / 128, cap = (int64_t)sm_count() * 8;  // each CTA stages the weights once and strides the edges
-    pairs_backward_kernel<T><<<(unsigned)(want < cap ? want : cap), 128, smem, (cudaStream_t)stream>>>(p);
+    if (trunk == PMAX) pairs_backward_kernel<T, true><<<(unsigned)(want < cap ? want : cap), 128, smem, (cudaStream_t)stream>>>(p);
+    else pairs_backward_kernel<T, false><<<(unsigned)(want < cap ? want : cap), 128, smem, (cudaStream_t)stream>>>(p);
     return launch_status("gm_pairs_backward");
   };
   return dtype == GM_F32 ? run(float()) : run(double());
