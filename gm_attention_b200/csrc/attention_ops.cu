@@ -112,20 +112,22 @@ __global__ void __launch_bounds__(SM_THREADS) softmax_forward_kernel(SoftmaxArgs
 // R per frequency).  Per edge every lane reads its own columns of k_j (the groups together read the whole row once),
 // the group reduces with log2(L) xor-shuffles, and all H logits of the edge appear at once.  The raw logits go to
 // alpha, the row is then normalised in place by the same warp (masked edges never enter the shift or the sum).
-template <typename T, int R>
+// NF: the number of descriptor rows when known at compile time (3 or 4 frequencies: the usual head types), 0 = up to MAX_F
+template <typename T, int R, int NF>
 __global__ void __launch_bounds__(128) softmax_forward_grouped_kernel(SoftmaxArgs<T> a) {
+  constexpr int FN = NF ? NF : MAX_F;
   const int lane = threadIdx.x & 31;
   const int64_t i = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (i >= a.n_nodes) return;
   const int L = 32 / a.H, h = lane / L, s = lane % L;
-  int col[MAX_F][R], order[MAX_F];
-  T qr[MAX_F][R], qi[MAX_F][R];
+  int col[FN][R], order[FN];
+  T qr[FN][R], qi[FN][R];
 #pragma unroll
-  for (int f = 0; f < MAX_F; ++f) {
+  for (int f = 0; f < FN; ++f) {
     order[f] = -1;
 #pragma unroll
     for (int r = 0; r < R; ++r) { col[f][r] = -1; qr[f][r] = qi[f][r] = T(0); }
-    if (f < a.F) {
+    if (NF || f < a.F) {
       const int n = (int)a.desc[f * DESC], a_n = (int)a.desc[f * DESC + 1], off = (int)a.desc[f * DESC + 2];
       order[f] = n;
 #pragma unroll
@@ -145,8 +147,8 @@ __global__ void __launch_bounds__(128) softmax_forward_grouped_kernel(SoftmaxArg
   auto dot = [&](const T* k_j, const T* tau) -> T {
     T part = T(0);
 #pragma unroll
-    for (int f = 0; f < MAX_F; ++f) {
-      if (order[f] < 0) continue;
+    for (int f = 0; f < FN; ++f) {
+      if (!NF && order[f] < 0) continue;
       const T tr = order[f] ? tau[2 * order[f]] : T(1), ti = order[f] ? tau[2 * order[f] + 1] : T(0);
 #pragma unroll
       for (int r = 0; r < R; ++r) {
@@ -572,9 +574,12 @@ int softmax_forward_t(SoftmaxArgs<T> a, int64_t deg_max, int max_mult, cudaStrea
   if ((a.H == 1 || a.H == 2 || a.H == 4 || a.H == 8) && max_mult > 0 && max_mult <= 4 * (32 / a.H)) {
     const int per_lane = (max_mult + 32 / a.H - 1) / (32 / a.H);
     const unsigned blocks = (unsigned)((a.n_nodes + 3) / 4);
-    if (per_lane <= 1) softmax_forward_grouped_kernel<T, 1><<<blocks, 128, 0, stream>>>(a);
-    else if (per_lane <= 2) softmax_forward_grouped_kernel<T, 2><<<blocks, 128, 0, stream>>>(a);
-    else softmax_forward_grouped_kernel<T, 4><<<blocks, 128, 0, stream>>>(a);
+    if (per_lane <= 1 && a.F == 3) softmax_forward_grouped_kernel<T, 1, 3><<<blocks, 128, 0, stream>>>(a);
+    else if (per_lane <= 1 && a.F == 4) softmax_forward_grouped_kernel<T, 1, 4><<<blocks, 128, 0, stream>>>(a);
+    else if (per_lane <= 1) softmax_forward_grouped_kernel<T, 1, 0><<<blocks, 128, 0, stream>>>(a);
+    else if (per_lane <= 2 && a.F == 3) softmax_forward_grouped_kernel<T, 2, 3><<<blocks, 128, 0, stream>>>(a);
+    else if (per_lane <= 2) softmax_forward_grouped_kernel<T, 2, 0><<<blocks, 128, 0, stream>>>(a);
+    else softmax_forward_grouped_kernel<T, 4, 0><<<blocks, 128, 0, stream>>>(a);
     return launch_status("gm_softmax_forward");
   }
   // Logits in shared memory when the largest neighbourhood fits ~96 KiB; else kept in alpha.
