@@ -16,10 +16,15 @@ the sphere is cut into edge-balanced latitude bands (one per rank), the key /
 value halos are exchanged before the forward and the gradient halos after the
 backward, all inside the timed region.
 
+Before anything is timed the step's results are compared with the CPU oracle on
+sampled targets and sources of the workload's own lattice (``"parity"`` in the
+line); a failed check prints no number and exits non-zero.
+
 ``--impl reference`` times the reference's own CPU implementation of the same
-layer on the host cores: its compiled scores+softmax driver (oracle/_ref, built
-from the reference's sources) plus a C port of its eager value path, one
-sample per worker process.
+layer, on the same lattice and batch, on the host cores: its compiled
+scores+softmax driver (oracle/_ref, built from the reference's sources) plus a C
+port of its eager value path, the target rows dealt to one worker process per
+core (``oracle/cpu_arm.py``).
 """
 
 from __future__ import annotations
@@ -51,7 +56,7 @@ def parse() -> argparse.Namespace:
     p.add_argument("--dtype", choices=["bf16", "f32"], default="bf16")
     p.add_argument("--impl", choices=["ours", "reference"], default="ours")
     p.add_argument("--workload", choices=["headline", "mid", "small", "ops"], default="headline",
-                   help="headline (default): the BASELINE workload; mid / small: profiling and smoke sizes; "
+                   help="headline (default): 256 x 512, batch 8; mid / small: 128 x 256 x 4 and 64 x 128 x 2 (profiling and smoke sizes); "
                         "ops: times every op-level entry point (scores+softmax, depthwise conv, factored kernel, pair term) "
                         "against its own interface bytes and prints one JSON object")
     p.add_argument("--kernel", choices=["lattice", "csr"], default="lattice",
@@ -65,94 +70,50 @@ def parse() -> argparse.Namespace:
                    help="every rank prints its own per-step timings (halo exchange in, forward, backward, halo sums out) to stderr")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--no-parity", action="store_true", help="skip the oracle check of the step's results (for profiler captures)")
     return p.parse_args()
 
 
 # ----------------------------------------------------------------------------- CPU legs (oracle = checker / baseline only)
 
-def _cpu_sample_step(job: tuple) -> float:
-    """One sample's forward + backward on one core: reference C++ scores+softmax driver
-    (oracle/_ref) when present, C port of the value path; returns seconds."""
-    nlat, nlon, radius, head_type, heads, seed, use_ref = job
-    import numpy as np
-    import torch
+def cpu_pool(cfg: dict):
+    """Worker pool over the workload's own lattice (built once: geometry, per-worker sub-tables, the reference's driver)."""
+    from oracle import cpu_arm
 
-    from oracle import oracle as O
-    from tests.helpers import make_case, seeded
-
-    torch.set_num_threads(1)
-    c = make_case(nlat, nlon, radius, head_type, heads, dtype=np.float32)
-    q, k, v, g = seeded((c.n_nodes, c.width), seed, np.float32, 4)
-    ref = None
-    if use_ref:
-        from oracle import build_ref
-        ref = build_ref.load("gm_fused_attention_cpu")
-    t0 = time.perf_counter()
-    if ref is not None:
-        t = torch.from_numpy
-        tables = (t(c.transport), t(c.bias), t(c.inside), t(c.desc), t(c.row_ptr), t(c.source))
-        alpha = ref.softmax_forward(t(q), t(k), *tables, c.heads, c.scale, c.max_degree)
-        O.value_forward(alpha.numpy(), v, c.transport, c.desc, c.row_ptr, c.source, c.heads)
-        dalpha, _ = O.value_backward(g, alpha.numpy(), v, c.transport, c.desc, c.row_ptr, c.source, c.heads)
-        ref.softmax_backward(t(dalpha), t(q), t(k), *tables, alpha, c.heads, c.scale, c.max_degree)
-    else:
-        O.attention_forward(q, k, v, c.transport, c.bias, c.inside, c.desc, c.row_ptr, c.source, c.heads, c.scale, 1)
-        O.attention_backward(g, q, k, v, c.transport, c.bias, c.inside, c.desc, c.row_ptr, c.source, c.heads, c.scale, 1)
-    return time.perf_counter() - t0
+    workers = cpu_arm.host_cores()
+    info = cpu_arm.prepare(cfg["nlat"], cfg["nlon"], cfg["radius_rows"] * math.pi / cfg["nlat"], cfg["head_type"], cfg["heads"], workers)
+    return cpu_arm.Pool(info)
 
 
-def cpu_layer_rate(cfg: dict, repeats: int = 1) -> dict:
-    """Edges/s of the layer on the host cores, on a bounded sample: the workload's head
-    layout on a 32 x 64 lattice at the same radius in rows, one sample per core."""
-    import multiprocessing as mp
-
-    import numpy as np
-
-    from oracle import build_ref
-    from tests.helpers import make_case
-
-    nlat, nlon = 64, 128
-    radius = cfg["radius_rows"] * math.pi / nlat
-    cores = os.cpu_count() or 1
-    per_core = 3
-    use_ref = (build_ref.OUT / "gm_fused_attention_cpu.so").exists()
-    edges = int(make_case(nlat, nlon, radius, cfg["head_type"], cfg["heads"], dtype=np.float32).source.shape[0])
-    jobs = [(nlat, nlon, radius, cfg["head_type"], cfg["heads"], s, use_ref) for s in range(cores * per_core)]
-    best = float("inf")
-    with mp.get_context("fork").Pool(cores) as pool:
-        pool.map(_cpu_sample_step, jobs[:cores])  # warm: builds the geometry cache, loads the libraries
-        for _ in range(repeats):
-            t0 = time.perf_counter()
-            pool.map(_cpu_sample_step, jobs)
-            best = min(best, time.perf_counter() - t0)
-    return {"value": len(jobs) * edges / best, "unit": "edges/s", "cores": cores, "kind": "reference" if use_ref else "port",
-            "sample": f"{len(jobs)} samples ({per_core} per core) of the workload's head layout on a {nlat}x{nlon} lattice, radius {cfg['radius_rows']}pi/{nlat}, "
-                      f"{edges} edges each, fp32; scores+softmax fwd/bwd = "
-                      + ("the reference's compiled C++ driver" if use_ref else "C port") + ", value path = C port of the reference's eager path",
-            "seconds": best}
+def cpu_sample_text(cfg: dict, info: dict, samples: int) -> str:
+    part = ("scores+softmax fwd/bwd = the reference's compiled C++ driver (single-threaded by construction), value path fwd/bwd = C port of "
+            "the reference's eager transport + segment sum" if info["kind"] == "reference+port" else "C port of the reference's drivers and eager value path")
+    return (f"{samples} of the batch's {cfg['batch']} samples on the workload's own {cfg['nlat']}x{cfg['nlon']} lattice ({info['edges_per_sample']} edges each), fp32, "
+            f"target rows dealt to {info['workers']} worker processes (one per host core); {part}; seconds = the slowest worker's time inside the layer")
 
 
 def run_reference(args: argparse.Namespace, cfg: dict) -> None:
+    """The reference's CPU path on the workload's own lattice and batch.  One step = the whole batch; a step is
+    tens of seconds of all host cores, so at most three steps are timed and none is spent on warm-up."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = max(1, args.steps)
-    base = None
-    times = []
-    for _ in range(max(0, min(args.warmup, 1))):
-        cpu_layer_rate(cfg)
-    for _ in range(min(steps, 10)):  # every step is a bounded sample (a few seconds on all host cores); at most ten of them
-        base = cpu_layer_rate(cfg)
-        times.append(base["seconds"])
-    assert base is not None
-    sec = statistics.median(times)
-    value = base["value"] * base["seconds"] / sec
+    pool = cpu_pool(cfg)
+    steps = max(1, min(args.steps, 3))
+    results = [pool.step(list(range(cfg["batch"]))) for _ in range(steps)]
+    pool.close()
+    sec = statistics.median(r["seconds"] for r in results)
+    value = results[0]["edges"] / sec
+    info = pool.info
     line = {
         "impl": "reference", "metric": "gauge-attn fwd+bwd neighbour-edges/sec", "value": value, "unit": "edges/s", "n_gpus": args.gpus,
-        "steps": min(steps, 10), "warmup": min(args.warmup, 1), "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
+        "steps": steps, "warmup": 0, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(cfg, args, 1),
-        "cpu_baseline": {k: base[k] for k in ("unit", "cores", "kind", "sample")} | {"value": value},
+        "cpu_baseline": {"value": value, "unit": "edges/s", "cores": info["workers"], "kind": info["kind"],
+                         "sample": cpu_sample_text(cfg, info, cfg["batch"]),
+                         "seconds_wall_per_step": statistics.median(r["seconds_wall"] for r in results),
+                         "pure_pytorch_path": "unavailable on this box: the reference's Python package is not present on the benchmark host"},
         "e2e": {"value": value, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
@@ -278,6 +239,8 @@ def bind_to_gpu_cpus(uuid: str | None, index: int) -> None:
 def run_ours(args: argparse.Namespace, cfg: dict) -> None:
     import numpy as np
     import torch
+
+    Tensor4 = torch.Tensor  # (4, batch, nlon, D): q, k, v, dO of one lattice row
     import torch.distributed as dist
 
     from gm_attention_b200 import _lib
@@ -290,6 +253,11 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
                                             tensor_core_row_cost)
 
     _lib.lib()
+    peaks_path = ROOT / "MEASURED_PEAKS.json"
+    if peaks_path.exists():
+        peak, peak_kind = float(json.loads(peaks_path.read_text())["hbm_gbs"]), "measured"
+    else:
+        peak, peak_kind = 6650.0, "fallback"
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -338,10 +306,19 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
     local_edges = edges.n_edges * batch
     n_ext = rows_ext * nlon
 
-    # ---- inputs: seeded N(0, 1), generated on the host, resident on the device for `value`
-    gen = torch.Generator().manual_seed(1234 + rank)
+    # ---- inputs: seeded N(0, 1), generated on the host, resident on the device for `value`.  A lattice row's values
+    # depend on its GLOBAL row index only, so every rank holds the same sphere whatever the cut, and the parity check
+    # below can regenerate any row it needs.
+    def row_fields(row: int) -> Tensor4:
+        gen = torch.Generator().manual_seed(1234 + 7919 * row)
+        return torch.randn((4, batch, nlon, D), generator=gen, dtype=torch.float32).to(dtype)
+
     shape = (batch, rows_ext, nlon, D)
-    host = [torch.randn(shape, generator=gen, dtype=torch.float32).to(dtype).pin_memory() for _ in range(4)]
+    host = [torch.empty(shape, dtype=dtype).pin_memory() for _ in range(4)]
+    for r in range(elo, ehi):
+        block = row_fields(r)
+        for f in range(4):
+            host[f][:, r - elo] = block[f]
     q, k, v, g = (h.to(device, non_blocking=True) for h in host)
     flat = lambda t: t.view(batch * n_ext, D)
     halo = HaloExchanger(plan, rank) if world > 1 else None
@@ -406,6 +383,67 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
+
+    # ---- parity self-check at the workload's own size: one more step, compared with the CPU oracle on sampled targets
+    # (out, dq) and sources (dk, dv) of this rank's rows -- complete CSR rows cut out of the GLOBAL lattice, so with
+    # latitude bands the sums that cross a cut (halo exchange and reduction) are checked too.  Nothing is timed here.
+    parity = None
+    if not args.no_parity:
+        from oracle import geometry_np as GN
+        from oracle import sampled as SP
+
+        result = step()
+        torch.cuda.synchronize()
+        near_pole = args.workload != "headline"  # a source next to the pole is ~1.5 M edges of oracle work at 256 x 512
+        t_nodes, s_nodes = SP.default_sample_nodes(nlat, nlon, lo, hi, polar_source_row=2 if near_pole else None)
+        sample = SP.sample_problem(GN.midpoint_lattice(nlat, nlon), radius, t_nodes, s_nodes, max(cfg["head_type"]), np.float32)
+        b_chk = batch - 1
+        cache: dict[int, torch.Tensor] = {}
+
+        def gather(nodes):
+            rows_needed = sorted(set((nodes // nlon).tolist()))
+            for r in rows_needed:
+                if r not in cache:
+                    cache[r] = row_fields(r)[:, b_chk].float()  # (4, nlon, D)
+            out4 = [np.empty((nodes.shape[0], D), np.float32) for _ in range(4)]
+            for r in rows_needed:
+                sel = np.flatnonzero(nodes // nlon == r)
+                cols = torch.from_numpy(nodes[sel] % nlon)
+                for f in range(4):
+                    out4[f][sel] = cache[r][f][cols].numpy()
+            return tuple(out4)
+
+        want = SP.run(sample, gather, np.array(p.rows, np.int64), heads, tables.scale)
+
+        def local_rows(x, nodes):
+            idx = torch.from_numpy(nodes)
+            return x.view(shape)[b_chk, (idx // nlon - elo).to(device), (idx % nlon).to(device)].float().cpu().numpy()
+
+        got = {"out": local_rows(result[0], sample.targets), "dq": local_rows(result[1], sample.targets),
+               "dk": local_rows(result[2], sample.sources), "dv": local_rows(result[3], sample.sources)}
+        errs = [float(np.abs(got[n] - want[n]).max() / max(float(np.abs(want[n]).max()), 1e-30)) for n in ("out", "dq", "dk", "dv")]
+        if world > 1:
+            t = torch.tensor(errs, device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            errs = t.tolist()
+            cnt = torch.tensor([sample.targets.shape[0], sample.sources.shape[0], sample.n_edges], device=device, dtype=torch.int64)
+            dist.all_reduce(cnt)
+            n_t, n_s, n_e = cnt.tolist()
+        else:
+            n_t, n_s, n_e = sample.targets.shape[0], sample.sources.shape[0], sample.n_edges
+        tolerance = 2e-2 if args.dtype == "bf16" else 2e-5
+        parity = {"max_rel": max(errs), "per_tensor": dict(zip(("out", "dq", "dk", "dv"), errs)), "tolerance": tolerance,
+                  "targets": n_t, "sources": n_s, "oracle_edges": n_e, "sample_of_batch": b_chk,
+                  "against": "CPU oracle (reference Softmax op + eager value path restated in C) in fp32 on the same "
+                             + ("bf16-rounded " if args.dtype == "bf16" else "") + "inputs; error = max |a - b| / max |b| per tensor"}
+        del result, cache
+        if not max(errs) <= tolerance:
+            if rank == 0:
+                print(json.dumps({"error": "parity check failed: no number is reported", "parity": parity}), file=sys.stderr, flush=True)
+            if world > 1:
+                dist.destroy_process_group()
+            sys.exit(3)
+
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     gpu_uuid = getattr(torch.cuda.get_device_properties(local), "uuid", None)
     with ClockSampler(local, f"GPU-{gpu_uuid}" if gpu_uuid is not None else None) as clocks:
@@ -481,7 +519,7 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
         torch.cuda.synchronize()
         f_ms, b_ms = ev32[0].elapsed_time(ev32[1]) / 3, ev32[1].elapsed_time(ev32[2]) / 3
         f32_line = {"dtype": "f32", "fwd_ms": f_ms, "bwd_ms": b_ms, "value": total_edges / ((f_ms + b_ms) * 1e-3), "unit": "edges/s",
-                    "hbm_frac": (12 * n_rows_local * D * 4 + 2 * n_rows_local * heads * 4) / ((f_ms + b_ms) * 1e-3) / 1e9 / 6548.2}
+                    "hbm_frac": (12 * n_rows_local * D * 4 + 2 * n_rows_local * heads * 4) / ((f_ms + b_ms) * 1e-3) / 1e9 / peak}
         del q32, k32, v32, g32, o32, l32
 
     # ---- end to end from pinned host buffers (copies inside the timed region)
@@ -531,12 +569,15 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
         e2e = {"value": total_edges / (ms / n_e2e * 1e-3), "unit": "edges/s", "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
                "ms_per_step": ms / n_e2e, "steps": n_e2e}
 
+    # a wait on a TMA completion barrier that ran out is recorded by the kernels instead of hanging: results would be invalid
+    import ctypes
+    expired = ctypes.c_int(0)
+    _lib.call("gm_lattice_attention_tc_wait_expired", ctypes.byref(expired))
+    if expired.value:
+        print(json.dumps({"error": "a wait on a copy barrier ran out inside the tensor-core lattice kernels: no number is reported", "rank": rank}),
+              file=sys.stderr, flush=True)
+        sys.exit(4)
     if rank == 0:
-        peaks_path = ROOT / "MEASURED_PEAKS.json"
-        if peaks_path.exists():
-            peak, peak_kind = json.loads(peaks_path.read_text())["hbm_gbs"], "measured"
-        else:
-            peak, peak_kind = 6650.0, "fallback"
         n_rows = batch * n_ext
         bwd_bytes = top_bytes if top_bytes is not None else 8 * n_rows * D * elem + n_rows * heads * 4
         layer_bytes = 12 * n_rows * D * elem + 2 * n_rows * heads * 4
@@ -553,10 +594,18 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
             "gpu_launches": args.steps * launches,
             "clocks": clocks.summary(),
             "e2e": e2e,
+            "tma_wait_expired": expired.value,
             "other_dtypes": f32_line,
         }
+        line["parity"] = parity
         if not args.no_cpu_baseline and world == 1:
-            line["cpu_baseline"] = {k: val for k, val in cpu_layer_rate(cfg).items() if k != "seconds"}
+            # one sample of the batch on the workload's own lattice, all host cores (tens of core-seconds)
+            pool = cpu_pool(cfg)
+            res = pool.step([0])
+            pool.close()
+            line["cpu_baseline"] = {"value": res["value"], "unit": "edges/s", "cores": pool.info["workers"], "kind": pool.info["kind"],
+                                    "sample": cpu_sample_text(cfg, pool.info, 1), "seconds": res["seconds"],
+                                    "pure_pytorch_path": "unavailable on this box: the reference's Python package is not present on the benchmark host"}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -598,7 +647,7 @@ def run_ops(args: argparse.Namespace) -> None:
         results[name] = {"ms": ms, "interface_bytes": nbytes, "GB/s": nbytes / ms / 1e6, "frac_of_hbm_peak": nbytes / ms / 1e6 / peak,
                          "edges_per_s": e / (ms * 1e-3)}
 
-    # scores + softmax: 4 heads of 8 x (m = 0..3), D = 224 (BASELINE config 2 layout)
+    # scores + softmax: 4 heads of 8 x (m = 0..3), D = 224 (the 128 x 256 configuration's head layout)
     heads, attn = 4, FieldType({0: 8, 1: 8, 2: 8, 3: 8})
     owner = type("Layer", (), {})()
     p = fa._plan(owner, attn, attn.scaled(heads), heads)
@@ -626,7 +675,7 @@ def run_ops(args: argparse.Namespace) -> None:
     timed("conv_forward", lambda: ext.conv_forward(v, *cv), 2 * n * p2.width * 4 + coeff + tab2)
     timed("conv_backward", lambda: ext.conv_backward(g, v, *cv), 3 * n * p2.width * 4 + 2 * coeff + tab2)
     del rc, cc, v, g
-    # factored value kernel {8, 8, 8} -> {4, 4, 4}, trunk 16 (BASELINE config 1 value kernel: 13 blocks, wc 48, wr 4)
+    # factored value kernel {8, 8, 8} -> {4, 4, 4}, trunk 16 (value kernel of the 32 x 64 configuration: 13 blocks, wc 48, wr 4)
     tin, tout, kk = {0: 8, 1: 8, 2: 8}, {0: 4, 1: 4, 2: 4}, 17
     blocks, powers = [(0, 0, "real")], {}
     for a_n in sorted(tin):

@@ -190,6 +190,32 @@ def build_lattice_tables(geometry: Any, rows: int, nlon: int, desc_rows: tuple[t
     if nlon % 2:
         raise ValueError("the lattice path needs an even number of longitudes")
     row_ptr = geometry.row_ptr.reshape(-1)
+    if row_ptr.numel() != rows * nlon + 1:
+        raise ValueError(f"row_ptr describes {row_ptr.numel() - 1} nodes, not a {rows} x {nlon} lattice")
+    per_node = (row_ptr[1:] - row_ptr[:-1]).reshape(rows, nlon)
+    if not bool((per_node == per_node[:, :1]).all()):
+        raise ValueError("the degree varies along a lattice row: not a longitude-symmetric lattice")
+    # the tables below are read off column 0; a second column must hold the same runs shifted by its longitude
+    # (frames that are not longitude-equivariant give the same edge set but different transport phases)
+    probe = max(1, nlon // 3) if nlon > 1 else 0
+    if probe:
+        a0, b0 = row_ptr[torch.arange(rows, device=device) * nlon], row_ptr[torch.arange(rows, device=device) * nlon + probe]
+        deg = per_node[:, 0]
+        within = torch.arange(int(deg.sum()), device=device) - torch.repeat_interleave(torch.cumsum(deg, 0) - deg, deg)
+        e0 = torch.repeat_interleave(a0, deg) + within
+        e1 = torch.repeat_interleave(b0, deg) + within
+        s0, s1 = geometry.source[e0], geometry.source[e1]
+        key0 = (s0 // nlon) * nlon + (s0 % nlon + probe) % nlon  # column 0's sources moved to the probe column ...
+        owner = torch.repeat_interleave(torch.arange(rows, device=device), deg)
+        o0 = torch.argsort(owner * (rows * nlon) + key0)            # ... in the probe column's (sorted-source) order
+        if not torch.equal(key0[o0], s1):
+            raise ValueError("neighbourhoods are not the same longitude offsets in every column: not a longitude-symmetric lattice")
+        n_ord = max((n for n, *_ in desc_rows), default=0)
+        tau_gap = (geometry.transport[e0][o0][:, 1:n_ord + 1] - geometry.transport[e1][:, 1:n_ord + 1]).abs().max() if n_ord and e0.numel() else 0.0
+        inside0 = geometry.inside[e0][o0] > 0
+        bias_gap = (geometry.bias[e0][o0] - geometry.bias[e1])[inside0 & (geometry.inside[e1] > 0)].abs().max() if bool(inside0.any()) else 0.0
+        if float(tau_gap) > 1e-3 or float(bias_gap) > 1e-3 or not torch.equal(inside0, geometry.inside[e1] > 0):
+            raise ValueError("transport phases / bias differ between columns: the frames are not longitude-equivariant; use the general kernels")
     col0 = torch.arange(rows, device=device) * nlon
     starts, stops = row_ptr[col0].cpu().numpy(), row_ptr[col0 + 1].cpu().numpy()
     degree = stops - starts
@@ -360,6 +386,8 @@ class HostPipeline:
         """``halo``: a :class:`gm_attention_b200.parallel.HaloExchanger` when the lattice is sharded into latitude
         bands: every chunk's key / value halos are filled before its forward and its dk / dv halo sums are handed
         back after its backward, on the compute stream (all ranks walk the chunks in the same order)."""
+        if chunk < 1 or batch % chunk:
+            raise ValueError(f"the batch of {batch} samples is not a whole number of chunks of {chunk}")
         self.tables, self.batch, self.chunk, self.device, self.halo = tables, batch, chunk, device, halo
         n = (tables.rows * tables.nlon) if isinstance(tables, LatticeTables) else tables.n_nodes
         self.n_nodes = n

@@ -25,6 +25,8 @@
 // Backward: per (target, sample) warp again, with the row's log-sum-exp saved
 // by the forward and Delta = <dO_i, O_i> per head: dq_i in registers, dk_j and
 // dv_j by atomic adds (fp32 accumulators for bf16 storage).
+#include <mutex>
+
 #include "common.cuh"
 
 namespace gmb {
@@ -423,6 +425,11 @@ extern "C" int gm_attention_backward(const void* dout, const void* q, const void
 // it still holds the previous call's sums, so each call clears it first, and
 // two calls that overlap on the GPU (different streams) race on it -- order
 // them.  Problems larger than the array are refused with GM_ERR_LIMIT.
+// The array is part of the library's device image: the driver sets its 32 MiB
+// aside when the image is loaded onto a device (with lazy module loading, at
+// the first kernel launch or symbol lookup of this library there), so an
+// embedder that claims all remaining memory for its arena must make one call
+// into this library on each device BEFORE it does so.
 // ---------------------------------------------------------------------------
 namespace gmb {
 namespace {
@@ -432,12 +439,17 @@ constexpr int MAX_DEVICES = 64;
 
 static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
 
+// Device address of the array per device ordinal, looked up under a lock (two host threads may make their first calls
+// at once).  An address stays valid for the life of the device's primary context: a process that destroys the context
+// (cudaDeviceReset) must not call this entry point again.
 void* g_static_scratch_address[MAX_DEVICES] = {nullptr};
+std::mutex g_static_scratch_lock;
 
 int static_scratch(void** out) {
   int device = -1;
   GM_CUDA(cudaGetDevice(&device));
   GM_REQUIRE(device >= 0 && device < MAX_DEVICES, GM_ERR_LIMIT, "gm_attention_backward_static: device index %d beyond %d", device, MAX_DEVICES);
+  std::lock_guard<std::mutex> guard(g_static_scratch_lock);
   if (g_static_scratch_address[device] == nullptr) {
     void* address = nullptr;
     GM_CUDA(cudaGetSymbolAddress(&address, g_static_scratch));
@@ -458,7 +470,10 @@ extern "C" int gm_attention_backward_static(const void* dout, const void* q, con
                                             int64_t n_nodes, int64_t n_edges, int64_t batch, int D, int F, int orders, int H,
                                             double scale, int dtype, void* dq, void* dk, void* dv, void* stream) {
   GM_REQUIRE(n_nodes >= 0 && batch >= 1 && D >= 1, GM_ERR_ARGUMENT, "gm_attention_backward_static: bad sizes");
-  const int64_t need = gm_attention_backward_scratch_bytes(n_nodes, batch, D, dtype);
+  // sizes whose product would overflow 64 bits must not slip under the limit: bound the factors by division first
+  const int64_t element_limit = STATIC_SCRATCH_BYTES / 8;
+  const bool representable = n_nodes <= element_limit / D / batch || dtype != GM_BF16;
+  const int64_t need = representable ? gm_attention_backward_scratch_bytes(n_nodes, batch, D, dtype) : INT64_MAX;
   GM_REQUIRE(need <= STATIC_SCRATCH_BYTES, GM_ERR_LIMIT,
              "gm_attention_backward_static: this problem needs %lld bytes of accumulation space, the built-in buffer holds %lld "
              "(batch * n_nodes * D <= %lld); use gm_attention_backward with a caller-provided buffer",

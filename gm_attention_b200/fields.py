@@ -11,6 +11,7 @@ are head-major (head ``h`` owns copies ``h a_n .. (h + 1) a_n - 1``).
 from __future__ import annotations
 
 from collections.abc import Iterable, Mapping
+from typing import Any
 
 
 class FieldType:
@@ -72,3 +73,35 @@ class FieldType:
 
     def __repr__(self) -> str:
         return "FieldType({" + ", ".join(f"{n}: {a}" for n, a in self._items) + "})"
+
+
+class FeatureField:
+    """Coefficients of a field by frequency: ``(..., a_0)`` reals for frequency 0 and ``(..., a_n, 2)`` real pairs
+    ``(re, im)`` for ``n >= 1`` -- the container the driver entries take and return, constructed like the
+    reference's ``SO2FeatureField(field_type, coefficients)`` (``representations/field_type.py:370-488``)."""
+
+    def __init__(self, field_type: FieldType, coefficients: Mapping[int, Any]) -> None:
+        if set(coefficients) != set(field_type.frequencies):
+            raise ValueError(f"coefficients for frequencies {sorted(coefficients)} do not match {field_type!r}")
+        for n, a in field_type.items():
+            shape = tuple(coefficients[n].shape)
+            tail = (a,) if n == 0 else (a, 2)
+            if shape[-len(tail):] != tail:
+                raise ValueError(f"frequency {n}: trailing shape {shape[-len(tail):]} is not {tail}")
+        self.field_type, self.coefficients = field_type, dict(coefficients)
+
+    def __getitem__(self, frequency: int) -> Any:
+        return self.coefficients[frequency]
+
+    @classmethod
+    def from_flat(cls, field_type: FieldType, flat: Any) -> FeatureField:
+        parts = {}
+        for n, sl in field_type.slices().items():
+            block = flat[..., sl]
+            parts[n] = block if n == 0 else block.reshape(*block.shape[:-1], field_type.multiplicity(n), 2)
+        return cls(field_type, parts)
+
+    def to_flat(self) -> Any:
+        import torch
+
+        return torch.cat([self.coefficients[n] if n == 0 else self.coefficients[n].flatten(-2) for n in self.field_type.frequencies], -1)

@@ -121,6 +121,52 @@ class EdgeGeometry:
     def transport_harmonic(self, order: int) -> Tensor:
         return self._harmonic(self.transport_phases, order)
 
+    _PER_EDGE = ("log_coordinates", "distances", "polar_angles", "transport_angles", "tangent_quadrature_weights", "angular_phases",
+                 "transport_phases")
+
+    def _with_tables(self, edge_index: Tensor, row_ptr: Tensor, per_edge) -> EdgeGeometry:
+        return type(self)(edge_index, row_ptr, *(per_edge(getattr(self, name)) for name in self._PER_EDGE))
+
+    def select(self, selection: Tensor, *, n_nodes: int | None = None) -> EdgeGeometry:
+        """The edges picked by a Boolean mask (one entry per edge) or by ascending edge indices, in their present
+        order, with a ``row_ptr`` over ``n_nodes`` targets (default: as many as now; a smaller count restricts the
+        targets to ``0 .. n_nodes - 1``, which every kept edge must respect).  Reference: ``edge_geometry.py:159-214``."""
+        if selection.dim() != 1:
+            raise ValueError("Edge selection must be one-dimensional.")
+        if selection.dtype == torch.bool:
+            if selection.shape[0] != self.n_edges:
+                raise ValueError("A Boolean edge mask must have one entry per edge.")
+        elif selection.dtype != torch.long:
+            raise TypeError("Edge selection must have dtype torch.bool or torch.long.")
+        kept = self.edge_index[:, selection].contiguous()
+        n = self.row_ptr.shape[0] - 1 if n_nodes is None else int(n_nodes)
+        row_ptr = torch.zeros(n + 1, dtype=torch.long, device=kept.device)
+        if kept.shape[1]:
+            torch.cumsum(torch.bincount(kept[0], minlength=n)[:n], 0, out=row_ptr[1:])
+        return self._with_tables(kept, row_ptr, lambda table: table[selection].contiguous())
+
+    def tile(self, count: int, *, n_sources: int) -> EdgeGeometry:
+        """``count`` disjoint copies of the edge set as ONE graph: copy ``b`` joins sources ``b * n_sources + j`` to
+        targets ``b * n_targets + i`` (the reference's batching, ``edge_geometry.py:216-252``; the kernels of this
+        package share one copy across the batch instead, this is for callers that want the union graph)."""
+        count = int(count)
+        if count < 1:
+            raise ValueError(f"count must be at least 1, got {count}.")
+        if count == 1:
+            return self
+        n_targets, n_edges = self.row_ptr.shape[0] - 1, self.n_edges
+        copy = torch.arange(count, dtype=torch.long, device=self.edge_index.device)[:, None]
+        index = torch.stack([(self.edge_index[0][None] + copy * n_targets).reshape(-1), (self.edge_index[1][None] + copy * int(n_sources)).reshape(-1)])
+        row_ptr = torch.cat([self.row_ptr[:1], (self.row_ptr[1:][None] + copy * n_edges).reshape(-1)])
+        return self._with_tables(index, row_ptr, lambda table: table.repeat(count, *([1] * (table.dim() - 1))))
+
+    def target_range(self, first: int, last: int) -> tuple[EdgeGeometry, int, int]:
+        """The whole neighbourhoods of the targets ``first .. last - 1`` as an edge set of their own, plus the edge
+        span ``(e_first, e_last)`` it occupies here -- what ``forward_chunked`` (reference ``nn/attention.py:344-402``)
+        selects per chunk and hands to ``fused_attention.register_chunk`` so that the chunk's constants are views."""
+        e_first, e_last = int(self.row_ptr[first]), int(self.row_ptr[last])
+        return self.select(torch.arange(e_first, e_last, device=self.edge_index.device)), e_first, e_last
+
 
 def compute_edge_geometry(grid: Any, frames: Tensor, coverage_radius: float, *, max_frequency: int = DEFAULT_MAX_FREQUENCY,
                           dtype: torch.dtype | None = None, candidates: tuple[Tensor, Tensor] | None = None) -> EdgeGeometry:

@@ -168,7 +168,10 @@ int gm_geometry_fill(const double* nodes, const double* frames, const double* we
  * (2 * batch * n_nodes * D * 4 bytes > capacity) return GM_ERR_LIMIT.
  * Same arguments as gm_attention_backward minus `scratch`.  The first call on
  * a device resolves the array's device address: issue it before any stream
- * capture.  Calls on one device share the array; it is cleared at the start of
+ * capture, and before the embedder claims the rest of the device's memory (the
+ * driver sets the array aside when the library's image is loaded onto the
+ * device).  The resolved address is valid for the life of the device's primary
+ * context.  Calls on one device share the array; it is cleared at the start of
  * each call, and calls that overlap on the GPU race on it.
  * ------------------------------------------------------------------------ */
 int64_t gm_attention_backward_static_capacity(void);
@@ -290,7 +293,8 @@ int gm_lattice_attention_backward_tc(const void* dout, const void* q, const void
                                      int NORD, double scale, void* dq, void* dk, void* dv, float* delta, void* stream);
 
 /* The same with a pass mask (bit 0: Delta = <dO, O>; bit 1: target-major pass -> dq; bit 2: source-major pass ->
- * dk, dv), for timing the passes one by one.  With bits 0 and 1 both set the target-major pass forms Delta itself and
+ * dk, dv).  The band-parallel layer uses it to run the source-major pass of its halo rows first (their sums are sent
+ * to the owners while the pass over its own rows runs); the benchmark uses it to time the passes one by one.  With bits 0 and 1 both set the target-major pass forms Delta itself and
  * writes it to `delta` (no separate launch); bit 0 alone runs the stand-alone Delta kernel; passes 2 and 4 without bit 0
  * read the Delta an earlier call left in `delta`. */
 int gm_lattice_attention_backward_tc_passes(const void* dout, const void* q, const void* k, const void* v, const void* out,

@@ -24,7 +24,7 @@ CASES = [
     (8, 16, 2 * math.pi / 8, {0: 3, 1: 2, 2: 1}, 2, "hard"),
     (8, 16, 2.5 * math.pi / 8, {0: 2, 1: 2}, 4, "quartic"),
     (6, 12, 2 * math.pi / 6, {1: 3, 3: 2}, 1, "hard"),
-    (16, 32, 2 * math.pi / 16, {0: 4, 1: 4, 2: 4}, 2, "hard"),  # BASELINE config 1 types on a half-size grid
+    (16, 32, 2 * math.pi / 16, {0: 4, 1: 4, 2: 4}, 2, "hard"),  # 4 x (m = 0, 1, 2) per head, 2 heads, on a half-size grid
     (12, 24, 3 * math.pi / 12, {0: 5, 1: 3}, 3, "quartic"),  # odd offsets, H = 3
 ]
 
@@ -175,3 +175,37 @@ def test_autograd_functions_run_end_to_end(ext):
                                         c.row_ptr, c.source, alpha.detach().cpu().numpy(), c.heads, c.scale)
     assert_close(q.grad.cpu().numpy(), dq_ref, 1e-10, 1e-11, "dq through autograd")
     assert_close(k.grad.cpu().numpy(), dk_ref, 1e-10, 1e-11, "dk through autograd")
+
+
+def test_chunked_scores_equal_the_whole_edge_set(ext):
+    """Exact chunking over contiguous target ranges (reference ``nn/attention.py:344-402``): every chunk holds whole
+    neighbourhoods, its constants are views of the parent's, and the softmax stays a partition of unity inside it --
+    the op over the chunks, concatenated, equals the op over the whole edge set bit for bit."""
+    from gm_attention_b200.fields import FieldType
+    from gm_attention_b200.geometry import compute_edge_geometry, midpoint_lattice
+    from gm_attention_b200.nn import fused_attention as fa
+
+    dev = torch.device("cuda", 0)
+    lattice = midpoint_lattice(12, 24, dev)
+    cutoff = 2 * math.pi / 12
+    edges = compute_edge_geometry(lattice, lattice.frames, cutoff, max_frequency=2, dtype=torch.float32)
+    heads, attn = 2, FieldType({0: 4, 1: 4, 2: 4})
+    owner = type("Layer", (), {})()
+    p = fa._plan(owner, attn, attn.scaled(heads), heads)
+    desc = fa.descriptors(owner, p, dev)
+    q, k = (cuda(x) for x in seeded((lattice.n_nodes, p.width), 21, np.float32, 2))
+    scale = 1.0 / math.sqrt(attn.dimension)
+    whole = fa.geometry(edges, cutoff, "quartic", torch.float32)
+    alpha = ext.softmax_forward(q, k, whole.transport, whole.bias, whole.inside, desc, whole.row_ptr, whole.source, heads, scale, whole.max_degree)
+    pieces = []
+    for first in range(0, lattice.n_nodes, 37):
+        last = min(lattice.n_nodes, first + 37)
+        chunk, e_first, e_last = edges.target_range(first, last)
+        fa.register_chunk(chunk, edges, e_first, e_last)
+        g = fa.geometry(chunk, cutoff, "quartic", torch.float32)
+        assert g.base is whole and g.transport.data_ptr() == whole.transport[e_first:e_last].data_ptr()
+        part = ext.softmax_forward(q, k, g.transport, g.bias, g.inside, desc, g.row_ptr, g.source, heads, scale, max(g.max_degree, 1))
+        sums = torch.zeros(lattice.n_nodes, heads, device=dev).index_add_(0, chunk.target_index, part)
+        assert torch.allclose(sums[first:last], torch.ones_like(sums[first:last]), atol=1e-5)
+        pieces.append(part)
+    assert torch.equal(torch.cat(pieces), alpha)

@@ -36,7 +36,7 @@ def blocks_for(type_in: dict[int, int], type_out: dict[int, int]):
 
 FACTORED_CASES = [
     ({0: 2, 1: 2}, {0: 2, 1: 3}, 5),
-    ({0: 8, 1: 8, 2: 8}, {0: 4, 1: 4, 2: 4}, 17),  # BASELINE config 1 value kernel: 13 blocks, wc 48, wr 4
+    ({0: 8, 1: 8, 2: 8}, {0: 4, 1: 4, 2: 4}, 17),  # value kernel of the 32 x 64 configuration: 13 blocks, wc 48, wr 4
     ({1: 3}, {0: 2, 2: 2}, 4),                       # no real block
     ({0: 32, 1: 32, 2: 32, 3: 32}, {0: 8, 1: 8, 2: 8, 3: 8}, 17),  # config 2: packed width 392 > the reference's 320
 ]
@@ -207,3 +207,53 @@ def test_pairs_plan_order():
     assert [(t.n, t.m, t.role) for t in terms] == [(0, 0, "real"), (1, 0, "linear"), (0, 1, "linear"), (1, 1, "linear"), (1, 1, "antilinear")]
     assert [t.flags for t in terms] == [2 | 8, 1 | 4 | 8, 1 | 2, 1, 1 | 4]
     assert [(t.pre_order, t.post_order) for t in terms] == [(None, None), (1, None), (None, 1), (0, None), (2, None)]
+
+
+# ----------------------------------------------------------------------------- the pair-term driver (_FusedPairs, forward_general)
+
+DRIVER_CASES = [
+    ({0: 2, 1: 2, 2: 1}, {0: 1, 1: 2, 2: 2}, True),
+    ({0: 2, 1: 2, 2: 1}, {0: 1, 1: 2, 2: 2}, False),
+    ({0: 3}, {0: 2}, True),
+    ({1: 2, 2: 1}, {1: 1, 2: 2}, True),
+    ({0: 2, 1: 1}, {1: 2}, True),
+    ({1: 2}, {0: 2}, True),
+    ({1: 16}, {1: 16}, True),
+    ({0: 5, 1: 7}, {0: 6, 2: 5}, True),  # block sides outside the reference's CPU size list
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float64, torch.float32])
+@pytest.mark.parametrize("field_in, field_out, bias", DRIVER_CASES)
+def test_pairs_driver_matches_the_pair_loop(field_in, field_out, bias, dtype):
+    """``forward_general`` (one launch per term, blocked readout gradient) against the plain-PyTorch pair loop on the
+    same device: values and every gradient (input field, trunk, both heads), the logic of the reference's
+    ``tests/nn/test_fused_pairs.py:73-93``.  float64 1e-11 / 1e-10; float32 1e-5 relative to the tensor's magnitude."""
+    from gm_attention_b200.fields import FeatureField
+    from gm_attention_b200.geometry import compute_edge_geometry, midpoint_lattice
+    from gm_attention_b200.nn import fused_pairs as fp
+
+    from tests.helpers import StandInKernel
+
+    dev = torch.device("cuda", 0)
+    lattice = midpoint_lattice(6, 12, dev)
+    cutoff = 1.4 * math.pi / 6
+    edges = compute_edge_geometry(lattice, lattice.frames, cutoff, max_frequency=4, dtype=dtype)
+    kernel = StandInKernel(field_in, field_out, cutoff, trunk=16, bias=bias, dtype=dtype).to(dev)
+    flat0 = torch.randn(lattice.n_nodes, kernel.field_type_in.dimension, generator=torch.Generator().manual_seed(5), dtype=dtype).to(dev)
+
+    def run(fused: bool):
+        flat = flat0.clone().requires_grad_(True)
+        x = FeatureField.from_flat(kernel.field_type_in, flat)
+        out = fp.forward_general(kernel, x, edges).coefficients if fused else kernel.pair_loop(x, edges)
+        loss = sum((out[m] * torch.linspace(0.1, 1.0, out[m].numel(), dtype=dtype, device=dev).reshape(out[m].shape)).sum() for m in out)
+        return {m: v.detach() for m, v in out.items()}, [g.detach() for g in torch.autograd.grad(loss, [flat, *kernel.parameters()])]
+
+    y_plain, g_plain = run(False)
+    y_fused, g_fused = run(True)
+    tol_y, tol_g = (1e-11, 1e-10) if dtype == torch.float64 else (1e-5, 1e-5)
+    for m in y_plain:
+        scale = max(1.0, float(y_plain[m].abs().max()))
+        assert float((y_fused[m] - y_plain[m]).abs().max()) <= tol_y * scale, m
+    for a, b in zip(g_fused, g_plain):
+        assert float((a - b).abs().max()) <= tol_g * max(1.0, float(b.abs().max()))

@@ -19,10 +19,10 @@ pytestmark = pytest.mark.gpu
 
 CASES = [
     # nlat, nlon, radius, head type, heads, window, batch
-    (16, 32, 2 * math.pi / 16, {0: 4, 1: 4, 2: 4}, 2, "hard", 2),         # BASELINE config 1 layout
+    (16, 32, 2 * math.pi / 16, {0: 4, 1: 4, 2: 4}, 2, "hard", 2),         # 2 heads of 4 x (m = 0, 1, 2)
     (12, 24, 3 * math.pi / 12, {0: 16, 1: 16, 2: 16}, 4, "hard", 1),      # headline layout; polar windows are whole rows
     (8, 16, 2.5 * math.pi / 8, {0: 2, 1: 2}, 4, "quartic", 2),             # pairs outside the quartic window's support
-    (10, 20, 2 * math.pi / 10, {0: 8, 1: 8, 2: 8, 3: 8}, 4, "hard", 1),   # BASELINE config 2 layout
+    (10, 20, 2 * math.pi / 10, {0: 8, 1: 8, 2: 8, 3: 8}, 4, "hard", 1),   # 4 heads of 8 x (m = 0..3)
     (8, 256, 1.2 * math.pi / 8, {0: 4, 1: 4, 2: 4}, 2, "hard", 1),        # wide windows: several staged chunks per row
     (8, 16, 2 * math.pi / 8, {1: 6, 2: 6}, 1, "hard", 2),                 # no scalar block, runs of 2 with idle slots
     (8, 16, 2 * math.pi / 8, {0: 3, 2: 5}, 2, "hard", 1),                 # odd multiplicities: unaligned runs

@@ -112,3 +112,50 @@ def test_tensor_core_layouts_and_row_cost():
     assert polar / (3 * 512) < 0.3 * equator / (5 * 7)
     cuts = balanced_cuts([polar] * 4 + [equator] * 120 + [polar] * 4, 4)
     assert cuts[0] == 0 and cuts[-1] == 128 and cuts == sorted(cuts) and len(set(cuts)) == 5
+
+
+def header_prototypes() -> dict[str, list[str]]:
+    """name -> parameter declarations of every prototype in include/gm_b200.h."""
+    text = (REPO / "include" / "gm_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    out = {}
+    for name, params in re.findall(r"\b(gm_[a-z0-9_]+)\s*\(([^)]*)\)\s*;", text):
+        params = " ".join(params.split())
+        out[name] = [] if params in ("", "void") else [x.strip() for x in params.split(",")]
+    return out
+
+
+def test_header_compiles_as_c(tmp_path):
+    """include/gm_b200.h is a C header: a C99 translation unit that includes it and takes the address of an entry
+    point compiles with gcc (no C++ leaks into the boundary)."""
+    import subprocess
+
+    src = tmp_path / "use_header.c"
+    src.write_text('#include "gm_b200.h"\n'
+                   "typedef int (*forward_fn)(const void*, const void*, const void*, const void*, const void*, const uint8_t*, const int64_t*,\n"
+                   "                          const int64_t*, const int64_t*, int64_t, int64_t, int64_t, int, int, int, int, double, int, void*, void*, void*);\n"
+                   "forward_fn pick(void) { return &gm_attention_forward; }\n"
+                   "int version(void) { return gm_abi_version() + GM_OK; }\n")
+    done = subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-pedantic", "-I", str(REPO / "include"), "-c", str(src), "-o", str(tmp_path / "use_header.o")],
+                          capture_output=True, text=True)
+    assert done.returncode == 0, done.stderr
+
+
+def test_ctypes_signatures_match_the_header():
+    """The hand-written ctypes argument lists have the arity and the kinds (pointer / int / int64 / double) of the
+    header's prototypes: a mismatch would otherwise pass garbage silently."""
+    from gm_attention_b200 import _lib
+
+    protos = header_prototypes()
+    kinds = {ctypes.c_void_p: "pointer", ctypes.c_int: "int", ctypes.c_int64: "int64", ctypes.c_double: "double"}
+
+    def kind_of(decl: str) -> str:
+        if "*" in decl:
+            return "pointer"
+        base = decl.rsplit(" ", 1)[0].replace("const ", "").strip()
+        return {"int": "int", "int64_t": "int64", "double": "double"}[base]
+
+    for name, argtypes in {**_lib.SIGNATURES, **_lib.SIZE_QUERIES}.items():
+        assert name in protos, name
+        want = [kind_of(d) for d in protos[name]]
+        assert [kinds[a] for a in argtypes] == want, f"{name}: ctypes {[kinds[a] for a in argtypes]} vs header {want}"
