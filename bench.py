@@ -94,12 +94,12 @@ def cpu_sample_text(cfg: dict, info: dict, samples: int) -> str:
 
 def run_reference(args: argparse.Namespace, cfg: dict) -> None:
     """The reference's CPU path on the workload's own lattice and batch.  One step = the whole batch; a step is
-    tens of seconds of all host cores, so at most three steps are timed and none is spent on warm-up."""
+    tens of seconds of all host cores, so at most two steps are timed and none is spent on warm-up."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     pool = cpu_pool(cfg)
-    steps = max(1, min(args.steps, 3))
+    steps = max(1, min(args.steps, 2))
     results = [pool.step(list(range(cfg["batch"]))) for _ in range(steps)]
     pool.close()
     sec = statistics.median(r["seconds"] for r in results)
