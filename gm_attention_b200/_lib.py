@@ -15,7 +15,7 @@ from typing import Any
 import torch
 
 LIBRARY = Path(__file__).resolve().parent / "libgmb200.so"
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 GM_F32, GM_F64, GM_BF16 = 0, 1, 2
 _DTYPES = {torch.float32: GM_F32, torch.float64: GM_F64, torch.bfloat16: GM_BF16}
@@ -43,6 +43,9 @@ SIGNATURES: dict[str, list[Any]] = {
     "gm_pairs_forward": [_P] * 8 + [_L, _I, _I, _I, _I, _I, _P],
     "gm_pairs_backward": [_P] * 11 + [_L, _I, _I, _I, _I, _I, _P],
     "gm_lattice_attention_tc_wait_expired": [_P],
+    "gm_lattice_attention_forward_tc4": [_P] * 8 + [_I, _P, _I, _I, _I, _L, _I, _I, _I, _I, _I, _D, _P, _P, _P],
+    "gm_lattice_attention_backward_tc4_passes": [_P] * 11 + [_I] + [_P] * 5 + [_I, _P, _I, _I, _I, _L, _I, _I, _I, _I, _I, _D, _P, _P, _P, _P, _I, _P],
+    "gm_lattice_attention_tc4_wait_expired": [_P],
     "gm_attention_backward_static": [_P] * 12 + [_L, _L, _L, _I, _I, _I, _I, _D, _I, _P, _P, _P, _P],
 }
 #: entry points that return a size instead of a status

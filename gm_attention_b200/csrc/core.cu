@@ -18,5 +18,5 @@ int fail(int code, const char* fmt, ...) {
 
 }  // namespace gmb
 
-extern "C" int gm_abi_version(void) { return 2; }
+extern "C" int gm_abi_version(void) { return 3; }
 extern "C" const char* gm_last_error(void) { return gmb::error_buffer(); }

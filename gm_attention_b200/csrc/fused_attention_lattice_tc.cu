@@ -81,6 +81,7 @@ struct TcArgs {
   int rows, nlon, D, H, W, NORD;
   int exact;    // every block is exactly 16 (scalar) / 16 KSC (complex) columns wide and starts on an even column: no padding, 4-byte accesses
   int use_tma;  // the neighbours' fields have tensor maps (exact 16 / 32-column blocks, aligned, at least one chunk of longitudes)
+  int aligned16;  // the neighbours' fields start on 16-byte boundaries (16-byte per-thread copies allowed)
   float scale;
   TcPlan plan;
   // tensor maps over the neighbours' fields as (D, nlon, batch * rows): [field][0 = 16-column box, 1 = complex-block box]
@@ -112,13 +113,14 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned 
                : "=r"(done) : "r"((unsigned)__cvta_generic_to_shared(bar)), "r"(parity) : "memory");
   return done != 0;
 }
-// bounded wait: gives up after TC_WAIT_LIMIT polls and records it
-__device__ __forceinline__ void mbar_wait(unsigned long long* bar, unsigned parity) {
+// bounded wait: gives up after TC_WAIT_LIMIT polls, records it in the device-wide flag and returns false
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
   for (unsigned tries = 0; tries < TC_WAIT_LIMIT; ++tries) {
-    if (mbar_try_wait(bar, parity)) return;
+    if (mbar_try_wait(bar, parity)) return true;
     if (tries > 64) __nanosleep(64);
   }
   atomicOr(&g_tc_wait_expired, 1);
+  return false;
 }
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, unsigned long long* bar, int x, int y, int z) {
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
@@ -411,7 +413,7 @@ __global__ void __launch_bounds__(32 * WARPS, WARPS == 4 ? (MODE == TC_BWD_S ? 3
   unsigned char* const smem_raw = smem_dyn + ((1024u - ((unsigned)__cvta_generic_to_shared(smem_dyn) & 1023u)) & 1023u);
   __shared__ __align__(8) unsigned long long copy_bar[2];  // completion of the TMA copies into buffer 0 / 1
   __shared__ __align__(16) TnRowPair pairs_s[TC_MAX_WIN];
-  __shared__ int n_pairs_s;
+  __shared__ int n_pairs_s, failed_s;
   const TcPlan& P = a.plan;
   // two buffers, each: field 1 sub-tiles | field 2 sub-tiles | entries 2 x (TN_ROWS + TL, 4) fp32 | stats (TN_ROWS, 2) fp32 (pass S)
   constexpr int buf_bytes = L::BUFFER_BYTES;
@@ -465,6 +467,7 @@ __global__ void __launch_bounds__(32 * WARPS, WARPS == 4 ? (MODE == TC_BWD_S ? 3
   if (!a.use_tma)  // per-thread staging leaves rows beyond a window and padding columns untouched: they must be finite
     for (int x = threadIdx.x; x < 2 * buf_bytes / 16; x += THREADS) reinterpret_cast<uint4*>(smem_raw)[x] = make_uint4(0, 0, 0, 0);
   if (threadIdx.x == 0) {
+    failed_s = 0;
     mbar_init(&copy_bar[0], 1);
     mbar_init(&copy_bar[1], 1);
     fence_mbar_init();
@@ -573,7 +576,7 @@ __global__ void __launch_bounds__(32 * WARPS, WARPS == 4 ? (MODE == TC_BWD_S ? 3
       }
     } else if (st_active) {
       const int st_g0 = flat_column<KS0, NCF, KSC>(P, h, 8 * st_ch), st_g7 = flat_column<KS0, NCF, KSC>(P, h, 8 * st_ch + 7);
-      const bool whole = st_g0 >= 0 && st_g7 == st_g0 + 7 && (a.D % 8 == 0) && (st_g0 % 8 == 0);  // one aligned 16-byte chunk of real columns
+      const bool whole = st_g0 >= 0 && st_g7 == st_g0 + 7 && (a.D % 8 == 0) && (st_g0 % 8 == 0) && a.aligned16;  // one aligned 16-byte chunk of real columns
       const bool pad = st_g0 < 0 && st_g7 < 0 && flat_column<KS0, NCF, KSC>(P, h, 8 * st_ch + 3) < 0;  // all padding (stays zero)
       if (!pad) {
         // this thread's chunk of every row: block base + row * pitch + 16 (chunk ^ swizzle(row))
@@ -656,7 +659,7 @@ __global__ void __launch_bounds__(32 * WARPS, WARPS == 4 ? (MODE == TC_BWD_S ? 3
       cp_async_wait<0>();
     }
     if (cur.tma) {  // one warp watches the copy barrier; the others block in the CTA barrier below without issuing
-      if (warp == 0) mbar_wait(&copy_bar[buf], (parity >> buf) & 1u);
+      if (warp == 0 && !mbar_wait(&copy_bar[buf], (parity >> buf) & 1u)) failed_s = 1;
       parity ^= 1u << buf;
     }
     __syncthreads();
@@ -711,13 +714,16 @@ __global__ void __launch_bounds__(32 * WARPS, WARPS == 4 ? (MODE == TC_BWD_S ? 3
         // online softmax over the 16 positions: column maxima over this thread's rows, then across the 8 row groups.
         // The reference maximum of an owner only moves when the new maximum exceeds it by more than 2^8 (weights stay
         // below 256: exact in the normalised result), so most steps skip the rescaling of the accumulators.
-        float mx[2] = {fmaxf(lg[0], lg[2]), fmaxf(lg[1], lg[3])};
+        // whether some owner's maximum has to move can be told from each thread's own four logits: most steps skip the
+        // column maxima (six shuffles) as well as the rescaling
+        const bool grow = fmaxf(lg[0], lg[2]) > m_o[0] + 8.f || fmaxf(lg[1], lg[3]) > m_o[1] + 8.f;
+        if (__any_sync(0xffffffffu, grow)) {
+          float mx[2] = {fmaxf(lg[0], lg[2]), fmaxf(lg[1], lg[3])};
 #pragma unroll
-        for (int d = 4; d < 32; d <<= 1) {
-          mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], d));
-          mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], d));
-        }
-        if (__any_sync(0xffffffffu, mx[0] > m_o[0] + 8.f || mx[1] > m_o[1] + 8.f)) {
+          for (int d = 4; d < 32; d <<= 1) {
+            mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], d));
+            mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], d));
+          }
           const float nm[2] = {mx[0] > m_o[0] + 8.f ? mx[0] : m_o[0], mx[1] > m_o[1] + 8.f ? mx[1] : m_o[1]};
           const float corr[2] = {fast_exp2(m_o[0] - nm[0]), fast_exp2(m_o[1] - nm[1])};
           m_o[0] = nm[0]; m_o[1] = nm[1];
@@ -809,6 +815,8 @@ __global__ void __launch_bounds__(32 * WARPS, WARPS == 4 ? (MODE == TC_BWD_S ? 3
         a.lse_out[(node0 + c0 + own_c + e) * a.H + h] = l_o[e] > 0.f ? (m_o[e] + log2f(l_o[e])) * TC_LN2 : -INFINITY;
     }
   }
+  // a wait that ran out anywhere in this CTA poisons its results (NaN) instead of passing half-filled tiles on as numbers
+  if (*(volatile int*)&failed_s != 0) inv[0] = inv[1] = __int_as_float(0x7fc00000);
   store_result<KS0, NCF, KSC, PASS_S>(P, a.res1 + own_b_base, own_b_present, exact, words, h, g, c, inv, a1_0, a1_r, a1_i);
   if constexpr (PASS_S) store_result<KS0, NCF, KSC, true>(P, a.res2 + own_b_base, own_b_present, exact, words, h, g, c, inv, a2_0, a2_r, a2_i);
 }
@@ -924,6 +932,7 @@ template <int KS0, int NCF, int KSC, int MODE>
 int launch_tn(TcArgs& a, int n_order_rows, int64_t batch, cudaStream_t stream) {
   constexpr int WARPS = TN_WARPS(MODE), TL = 8 * WARPS, TN_ROWS = tn_rows(TL);
   using L = TnLayout<KS0, NCF, KSC, TL>;
+  a.aligned16 = reinterpret_cast<uintptr_t>(a.nb1) % 16 == 0 && reinterpret_cast<uintptr_t>(a.nb2) % 16 == 0;
   bool tma = !tma_disabled() && a.D % 8 == 0 && a.nlon >= TN_ROWS && batch * a.rows < (1ll << 31) && (KS0 == 0 || (a.plan.a0 == 16 && a.plan.real_off % 8 == 0)) &&
              2 * a.plan.ac == 16 * KSC && reinterpret_cast<uintptr_t>(a.nb1) % 16 == 0 && reinterpret_cast<uintptr_t>(a.nb2) % 16 == 0;
   for (int f = 0; f < a.plan.n_cf; ++f) tma = tma && a.plan.cf_off[f] % 8 == 0;

@@ -316,6 +316,50 @@ int gm_lattice_attention_forward_tc(const void* q, const void* k, const void* v,
                                     const int64_t* desc_host, int F, int rows, int nlon, int64_t batch, int D, int H, int W, int ES,
                                     int NORD, double scale, void* out, float* lse, void* stream);
 
+/* ------------------------------------------------------------------------
+ * The tensor-core lattice kernels with ALL FOUR HEADS of an owner tile in one
+ * CTA (no counterpart in the reference).  Same arithmetic; a neighbour row
+ * reaches shared memory as five tensor copies of 128-byte rows (four heads'
+ * scalar blocks; two heads' complex blocks) instead of three copies of 32- and
+ * 64-byte rows per head, which is what bounds the one-head kernels.  One
+ * persistent CTA per SM: twelve consumer warps (head x group of 8 owners) and
+ * four producer warps that keep a ring of three stages and the next item's
+ * owner rows filled; bounded waits, results poisoned with NaN if one runs out
+ * (gm_lattice_attention_tc4_wait_expired reads the device's flag).
+ * Serves: 4 heads of 16 scalar + 16 complex copies of each of the orders
+ * 1 .. n, n <= 3, every block on a 16-byte boundary, D a multiple of 8, at most
+ * 32 neighbour rows, nlon >= 40, fields on 16-byte boundaries; otherwise
+ * GM_ERR_UNSUPPORTED (use the one-head entry points above).
+ *
+ * These entry points read their OWN entry table, ES = 12 (orders <= 2) or 20
+ * words per longitude offset x of a row pair (win_off / t_win_off index it):
+ *   [0..3] fp32 cos, sin of 1 * gamma and 2 * gamma
+ *   [4..7] the same rounded to bf16 and packed in pairs, entry x in the low and
+ *          entry x - 1 in the high half of a word
+ *   [8] bias * log2(e); with order 3: [9..10] its cos, sin, [12..13] their pairs
+ * Every row pair's run of cnt entries must be preceded by 8 and followed by 24
+ * padding entries whose bias is -inf (phases 0): the kernels read the entry of
+ * every (position, owner) pair of a 16 x 8 tile without a bounds test, and the
+ * padding's bias is what gives pairs outside an owner's window the logit -inf.
+ * (gm_attention_b200.attention.tensor_core_entries builds the table.)
+ * `passes` as in gm_lattice_attention_backward_tc_passes, except that bit 0
+ * always runs the stand-alone Delta kernel.
+ * ------------------------------------------------------------------------ */
+int gm_lattice_attention_forward_tc4(const void* q, const void* k, const void* v, const int* win_cnt, const int* win_lo,
+                                     const int* win_off, const float* entries, const int* row_order, int n_order_rows,
+                                     const int64_t* desc_host, int F, int rows, int nlon, int64_t batch, int D, int H, int W, int ES,
+                                     int NORD, double scale, void* out, float* lse, void* stream);
+
+int gm_lattice_attention_backward_tc4_passes(const void* dout, const void* q, const void* k, const void* v, const void* out,
+                                             const float* lse, const int* win_cnt, const int* win_lo, const int* win_off,
+                                             const float* entries, const int* row_order, int n_order_rows, const int* t_win_cnt,
+                                             const int* t_win_lo, const int* t_win_off, const float* t_entries, const int* t_row_order,
+                                             int t_n_order_rows, const int64_t* desc_host, int F, int rows, int nlon, int64_t batch,
+                                             int D, int H, int W, int ES, int NORD, double scale, void* dq, void* dk, void* dv,
+                                             float* delta, int passes, void* stream);
+
+int gm_lattice_attention_tc4_wait_expired(int* expired);
+
 #ifdef __cplusplus
 }
 #endif

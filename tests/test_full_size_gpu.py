@@ -179,5 +179,13 @@ def test_sampled_targets_bf16_tensor_cores(name):
     sampled_check(name, torch.bfloat16, "lattice")
 
 
+def test_sampled_targets_bf16_four_head_kernels_256x512(monkeypatch):
+    """The opt-in four-heads-per-CTA kernels at the headline size."""
+    from gm_attention_b200 import attention
+
+    monkeypatch.setattr(attention, "FOUR_HEADS", "1")
+    sampled_check("256x512", torch.bfloat16, "lattice")
+
+
 def test_sampled_targets_float32_general_kernels_128x256():
     sampled_check("128x256", torch.float32, "csr")

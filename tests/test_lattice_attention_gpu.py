@@ -119,6 +119,66 @@ TMA_CASE = (6, 256, 1.2 * math.pi / 6, {0: 16, 1: 16, 2: 16}, 2, "hard", 2)
 TC_CASES = [CASES[0], CASES[1], CASES[2], CASES[3], CASES[4], (8, 16, 2 * math.pi / 8, {1: 6, 2: 6}, 1, "hard", 2), TMA_CASE]
 
 
+@pytest.fixture(params=["one-head", "four-heads"])
+def kernel_family(request, monkeypatch):
+    """The two tensor-core kernel families: one head per CTA (default) and all four heads of a tile per CTA (opt-in;
+    layouts it does not serve fall through to the first)."""
+    from gm_attention_b200 import attention
+
+    monkeypatch.setattr(attention, "FOUR_HEADS", "1" if request.param == "four-heads" else "0")
+    return request.param
+
+
+FOUR_HEAD_CASES = [
+    (12, 48, 3 * math.pi / 12, {0: 16, 1: 16, 2: 16}, 4, "hard", 2),      # headline layout: whole-row polar windows, tiles across the seam
+    (6, 256, 1.2 * math.pi / 6, {0: 16, 1: 16, 2: 16}, 4, "hard", 2),     # wide windows: several chunks per row pair, tensor copies and seam chunks
+    (10, 64, 2 * math.pi / 10, {0: 16, 1: 16}, 4, "quartic", 1),          # one complex frequency, masked pairs inside the windows
+    (8, 40, 2 * math.pi / 8, {0: 16, 1: 16, 2: 16, 3: 16}, 4, "hard", 1), # three complex frequencies (20-word entries), the smallest row length served
+]
+
+
+@pytest.mark.parametrize("case", FOUR_HEAD_CASES)
+def test_four_head_kernels_match_the_oracle_and_the_one_head_kernels(case, monkeypatch):
+    """The persistent four-heads-per-CTA kernels (128-byte rows, producer / consumer warps): forward and both backward
+    passes against the oracle (2e-2 of each tensor's magnitude) and against the one-head kernels on the same inputs;
+    bit-identical reruns; no wait on a barrier ran out."""
+    import ctypes
+
+    from gm_attention_b200 import _lib, attention
+    from gm_attention_b200.attention import four_head_layout_supported, lattice_attention_backward, lattice_attention_forward
+
+    batch = case[6]
+    c = make_case(*case[:5], dtype=np.float32, window=case[5])
+    rounded = [torch.from_numpy(x).bfloat16() for x in seeded((batch * c.n_nodes, c.width), 62, np.float32, 4)]
+    q, k, v, g = (x.float().numpy() for x in rounded)
+    want = O.attention_forward(q, k, v, c.transport, c.bias, c.inside, c.desc, c.row_ptr, c.source, c.heads, c.scale, batch)
+    grads = O.attention_backward(g, q, k, v, c.transport, c.bias, c.inside, c.desc, c.row_ptr, c.source, c.heads, c.scale, batch)
+    _, lat = tables_for(c)
+    assert four_head_layout_supported(lat, c.width)
+    Q, K, V, G = (x.cuda() for x in rounded)
+    results = {}
+    # the other family: the one-head tensor-core kernels, or the FMA lattice kernels where those have no instantiation
+    # (16 copies of three complex frequencies)
+    other_tc = attention.tensor_core_layout_supported(lat.desc_rows)
+    for family in ("1", "0"):
+        monkeypatch.setattr(attention, "FOUR_HEADS", family)
+        tc = True if family == "1" else other_tc
+        out, lse = lattice_attention_forward(Q, K, V, lat, tensor_cores=tc)
+        results[family] = (out, lse, *lattice_attention_backward(G, Q, K, V, out, lse, lat, tensor_cores=tc))
+    monkeypatch.setattr(attention, "FOUR_HEADS", "1")
+    out, lse = lattice_attention_forward(Q, K, V, lat, tensor_cores=True)
+    again = (out, lse, *lattice_attention_backward(G, Q, K, V, out, lse, lat, tensor_cores=True))
+    for a, b in zip(results["1"], again):
+        assert torch.equal(a, b)
+    for name, a, b in zip(("out", "dq", "dk", "dv"), (results["1"][0], *results["1"][2:]), (want, *grads)):
+        assert rel_err(a.float().cpu().numpy(), b) < 2e-2, name
+    for name, a, b in zip(("out", "lse", "dq", "dk", "dv"), results["1"], results["0"]):
+        assert rel_err(a.float().cpu().numpy(), b.float().cpu().numpy()) < 2e-2, name
+    expired = ctypes.c_int(-1)
+    _lib.call("gm_lattice_attention_tc4_wait_expired", ctypes.byref(expired))
+    assert expired.value == 0
+
+
 @pytest.mark.parametrize("case", TC_CASES)
 def test_tensor_core_forward_bf16(case):
     """mma.sync Gram / value tiles against the oracle (2e-2 of the output's magnitude) and against the FMA

@@ -159,3 +159,41 @@ def test_ctypes_signatures_match_the_header():
         assert name in protos, name
         want = [kind_of(d) for d in protos[name]]
         assert [kinds[a] for a in argtypes] == want, f"{name}: ctypes {[kinds[a] for a in argtypes]} vs header {want}"
+
+
+def test_tensor_core_entry_table_layout():
+    """The padded entry table of the tensor-core lattice kernels: runs keep their order, padding carries bias -inf,
+    the bias is pre-multiplied by log2(e), and the packed words hold (entry x | entry x - 1) in bf16."""
+    import numpy as np
+    import torch
+
+    from gm_attention_b200.attention import TC_PAD_AFTER, TC_PAD_BEFORE, tensor_core_entries, tensor_core_entry_words
+
+    rng = np.random.default_rng(0)
+    for norders in (2, 3):
+        win_cnt = np.array([[0, 3, 2], [5, 0, 1]], np.int32)
+        win_off = np.array([[0, 0, 3], [5, 0, 10]], np.int32)
+        entries = rng.standard_normal((11, 8)).astype(np.float32)
+        entries[4, 2 * norders] = -np.inf  # a masked pair inside a window
+        table, off = tensor_core_entries(entries, win_cnt, win_off, norders)
+        assert table.shape[1] == tensor_core_entry_words(norders) and (table.shape[1] // 4) % 2 == 1 and off.shape == win_off.shape
+        assert table.shape[0] == int((win_cnt[win_cnt > 0] + TC_PAD_BEFORE + TC_PAD_AFTER).sum()) + 1
+        bf16 = lambda x: torch.from_numpy(np.ascontiguousarray(x)).bfloat16().view(torch.int16).numpy().astype(np.uint16).astype(np.uint32)
+        words = lambda x: np.ascontiguousarray(x).view(np.uint32)
+        for (i, c), cnt in np.ndenumerate(win_cnt):
+            if cnt == 0:
+                continue
+            o, src = int(off[i, c]), int(win_off[i, c])
+            run = table[o:o + cnt]
+            assert np.array_equal(run[:, 0:4], entries[src:src + cnt, 0:4])
+            assert np.array_equal(run[:, 8], entries[src:src + cnt, 2 * norders] * np.float32(1.4426950408889634))
+            before, after = table[o - TC_PAD_BEFORE:o], table[o + cnt:o + cnt + TC_PAD_AFTER]
+            assert np.isneginf(before[:, 8]).all() and np.isneginf(after[:, 8]).all()
+            assert not before[:, 0:4].any() and not after[:, 0:4].any() and not words(before[:, 4:8]).any()
+            assert np.array_equal(words(run[:, 4:8]) & 0xFFFF, bf16(entries[src:src + cnt, 0:4]))
+            previous = np.vstack([np.zeros((1, 4), np.float32), entries[src:src + cnt - 1, 0:4]])
+            assert np.array_equal(words(run[:, 4:8]) >> 16, bf16(previous))
+            if norders == 3:
+                assert np.array_equal(run[:, 9:11], entries[src:src + cnt, 4:6])
+                assert np.array_equal(words(run[:, 12:14]) & 0xFFFF, bf16(entries[src:src + cnt, 4:6]))
+        assert not table[:, 11].any() and not table[:, 14:].any()
