@@ -66,6 +66,8 @@ def parse() -> argparse.Namespace:
     p.add_argument("--overlap", action="store_true",
                    help="N > 1: run the layer around the halo exchange (interior rows while the halos travel) instead of exchanging "
                         "before / after it; measured equal within 1 %% at N = 8 (the exchange is latency, not bandwidth), so off by default")
+    p.add_argument("--halo", choices=["native", "torch"], default="native",
+                   help="N > 1: native = the library's own NCCL groups issued from C (default); torch = torch.distributed point-to-point with staging buffers")
     p.add_argument("--per-rank", action="store_true",
                    help="every rank prints its own per-step timings (halo exchange in, forward, backward, halo sums out) to stderr")
     p.add_argument("--no-cpu-baseline", action="store_true")
@@ -249,8 +251,8 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
     from gm_attention_b200.fields import FieldType
     from gm_attention_b200.geometry import midpoint_lattice
     from gm_attention_b200.nn import fused_attention as fa
-    from gm_attention_b200.parallel import (BandPlan, HaloExchanger, band_geometry, overlap_tables, row_degrees, row_pair_counts,
-                                            tensor_core_row_cost)
+    from gm_attention_b200.parallel import (BandPlan, HaloExchanger, NativeHaloExchanger, band_geometry, overlap_tables, row_degrees,
+                                            row_pair_counts, tensor_core_row_cost)
 
     _lib.lib()
     peaks_path = ROOT / "MEASURED_PEAKS.json"
@@ -321,7 +323,11 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
             host[f][:, r - elo] = block[f]
     q, k, v, g = (h.to(device, non_blocking=True) for h in host)
     flat = lambda t: t.view(batch * n_ext, D)
-    halo = HaloExchanger(plan, rank) if world > 1 else None
+    # the library's own NCCL groups (sends / receives in place, nothing on the host); --halo torch: torch.distributed with staging
+    halo = None
+    if world > 1:
+        halo = NativeHaloExchanger(plan, rank, device) if args.halo == "native" else HaloExchanger(plan, rank)
+    reduce_kw = {"zero_halo": False} if args.halo == "native" else {}  # the halo rows of dk / dv are not part of the rank's result
     fwd_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     bwd_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
 
@@ -354,7 +360,7 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
             attention_backward(flat(g), flat(q), flat(k), flat(v), out, lse, split.owned_sources, passes=4, workspace=ws)
             if index is not None:
                 bwd_ev[index][1].record()
-            halo.finish_reduce(pending)
+            halo.finish_reduce(pending, **reduce_kw)
             if index is not None:
                 mark_ev[index][1].record()
             return out, dq, dk, dv
@@ -370,7 +376,7 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
         if index is not None:
             bwd_ev[index][1].record()
         if halo is not None:
-            halo.reduce_halos(dk.view(shape), dv.view(shape))
+            halo.reduce_halos(dk.view(shape), dv.view(shape), **reduce_kw)
         if index is not None:
             mark_ev[index][1].record()
         return out, dq, dk, dv
@@ -526,13 +532,38 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
     e2e = None
     if not args.no_e2e:
         outs_host = [torch.empty(shape, dtype=dtype).pin_memory() for _ in range(4)]
+        e2e_rows, e2e_cuts, pipeline = rows_ext, None, None
         if args.kernel == "lattice":
             # host-resident fields through the public host API: sample chunks pipelined over three streams
             # (with latitude bands, every chunk's halos are exchanged inside the pipeline)
             from gm_attention_b200.attention import HostPipeline
-            pipeline = HostPipeline(tables, batch, D, dtype, device, chunk=1, halo=halo)
-            host_flat = [x.view(batch * n_ext, D) for x in host]
-            outs_flat = [x.view(batch * n_ext, D) for x in outs_host]
+            e_tables, e_halo, e_host = tables, halo, host
+            if world > 1:
+                # End to end a rank is bound by its copies, not its kernels: cut the sphere so that the slowest rank's
+                # (copy time + compute time) is smallest, instead of compute alone.  Copies: one lattice row of the four
+                # fields each way at the ~25 GB/s per direction a GPU gets when all GPUs of the host copy at once.
+                copy_ms_row = 4 * batch * nlon * D * elem / 25e9 * 1e3
+                unit = world * (fwd_ms + bwd_ms) / max(sum(row_cost), 1e-30)  # ms of kernel time per unit of the cost model
+                plan2 = BandPlan.balanced(nlat, nlon, w, [copy_ms_row + unit * c for c in row_cost], world)
+                e2e_cuts = list(plan2.cuts)
+                lo2, hi2 = plan2.extended(rank)
+                e2e_rows = hi2 - lo2
+                edges2 = band_geometry(lattice, plan2, rank, radius, max_frequency=2, dtype=torch.float32)
+                geo2 = fa.geometry(edges2, radius, "hard", torch.float32)
+                gen2 = AttentionTables(geo2.transport, geo2.bias, geo2.inside, geo2.row_ptr, geo2.source, p.rows, heads, 1.0 / math.sqrt(attn.dimension))
+                e_tables = build_lattice_tables(gen2, e2e_rows, nlon, p.rows, heads, gen2.scale)
+                e_halo = NativeHaloExchanger(plan2, rank, device) if args.halo == "native" else HaloExchanger(plan2, rank)
+                shape2 = (batch, e2e_rows, nlon, D)
+                e_host = [torch.empty(shape2, dtype=dtype).pin_memory() for _ in range(4)]
+                for r in range(lo2, hi2):
+                    block = row_fields(r)
+                    for f in range(4):
+                        e_host[f][:, r - lo2] = block[f]
+                outs_host = [torch.empty(shape2, dtype=dtype).pin_memory() for _ in range(4)]
+            pipeline = HostPipeline(e_tables, batch, D, dtype, device, chunk=1, halo=e_halo)
+            pipeline.profile = True
+            host_flat = [x.view(batch * e2e_rows * nlon, D) for x in e_host]
+            outs_flat = [x.view(batch * e2e_rows * nlon, D) for x in outs_host]
             def e2e_step():  # enqueue only: consecutive steps overlap their first / last copies; joined before the clock stops
                 pipeline.run(*host_flat, *outs_flat, wait=False)
             e2e_join = pipeline.join
@@ -565,9 +596,20 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
             t = torch.tensor([ms], device=device)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t)
-        nbytes = 4 * batch * n_ext * D * elem
+        nbytes = 4 * batch * e2e_rows * D * nlon * elem
+        phases = pipeline.phase_ms() if pipeline is not None else None
+        if world > 1:
+            # bytes: the largest share of a rank (what bounds the step) and the whole job's; phases: the slowest rank's
+            every = [None] * world
+            dist.all_gather_object(every, {"bytes": nbytes, "phases": phases})
+            slowest = max(every, key=lambda x: max(x["phases"].values()) if x["phases"] else 0.0)
+            nbytes, total_bytes, phases = max(x["bytes"] for x in every), sum(x["bytes"] for x in every), slowest["phases"]
+        else:
+            total_bytes = nbytes
         e2e = {"value": total_edges / (ms / n_e2e * 1e-3), "unit": "edges/s", "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
-               "ms_per_step": ms / n_e2e, "steps": n_e2e}
+               "ms_per_step": ms / n_e2e, "steps": n_e2e, "bytes_counted": "the largest share of a rank" if world > 1 else "the whole job's",
+               "job_bytes_per_direction": total_bytes, "band_cuts": e2e_cuts,
+               "last_step_phases_ms_slowest_rank": phases}
 
     # a wait on a TMA completion barrier that ran out is recorded by the kernels instead of hanging: results would be invalid
     import ctypes

@@ -46,6 +46,13 @@ SIGNATURES: dict[str, list[Any]] = {
     "gm_lattice_attention_forward_tc4": [_P] * 8 + [_I, _P, _I, _I, _I, _L, _I, _I, _I, _I, _I, _D, _P, _P, _P],
     "gm_lattice_attention_backward_tc4_passes": [_P] * 11 + [_I] + [_P] * 5 + [_I, _P, _I, _I, _I, _L, _I, _I, _I, _I, _I, _D, _P, _P, _P, _P, _I, _P],
     "gm_lattice_attention_tc4_wait_expired": [_P],
+    "gm_halo_unique_id": [_P],
+    "gm_halo_comm_create": [_P, _I, _I, _P],
+    "gm_halo_comm_destroy": [_P],
+    "gm_halo_comm_error": [_P, _P],
+    "gm_halo_exchange": [_P, _I, _P, _P, _P, _P, _P],
+    "gm_halo_accumulate": [_P, _P, _L, _L, _L, _L, _I, _P],
+    "gm_halo_move": [_I, _P, _I, _L, _L, _L, _P, _I, _P],
     "gm_attention_backward_static": [_P] * 12 + [_L, _L, _L, _I, _I, _I, _I, _D, _I, _P, _P, _P, _P],
 }
 #: entry points that return a size instead of a status

@@ -500,6 +500,8 @@ class HostPipeline:
         self.streams = [torch.cuda.Stream(device) for _ in range(3)]  # h2d, compute, d2h
         self.consumed: list[Any] = [None, None]  # per staging slot: the compute that last read it has finished
         self.lattice = isinstance(tables, LatticeTables)
+        self.profile = False  # True: every run records when each of the three streams starts and ends its share
+        self._marks: list[tuple[Any, Any]] = []
 
     def run(self, q: Tensor, k: Tensor, v: Tensor, dout: Tensor, out: Tensor, dq: Tensor, dk: Tensor, dv: Tensor,
             wait: bool = True) -> None:
@@ -518,6 +520,10 @@ class HostPipeline:
             s.wait_stream(main)
         loaded = [torch.cuda.Event() for _ in range(n_chunks)]
         computed = [torch.cuda.Event() for _ in range(n_chunks)]
+        if self.profile:
+            self._marks = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in self.streams]
+            for (first, _), st in zip(self._marks, self.streams):
+                first.record(st)
         for i in range(n_chunks):
             sl = slice(i * rows, (i + 1) * rows)
             slot = self.inputs[i % 2]
@@ -543,8 +549,18 @@ class HostPipeline:
                 for dst, src in zip((out, dq, dk, dv), (o, *grads)):
                     dst[sl].copy_(src, non_blocking=True)
                     src.record_stream(d2h)
+        if self.profile:
+            for (_, last), st in zip(self._marks, self.streams):
+                last.record(st)
         if wait:
             self.join()
+
+    def phase_ms(self) -> dict[str, float]:
+        """Of the last profiled run (after a synchronise): how long each stream was busy or waiting between its first and
+        last operation -- host-to-device copies, compute (with the halo exchanges), device-to-host copies.  The three
+        overlap; the run takes about as long as the longest."""
+        names = ("h2d", "compute", "d2h")
+        return {n: first.elapsed_time(last) for n, (first, last) in zip(names, self._marks)}
 
     def join(self) -> None:
         """Make the caller's current stream wait for everything enqueued so far."""

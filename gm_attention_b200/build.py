@@ -56,7 +56,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         objects = list(pool.map(lambda s: _compile(s, force, verbose), srcs))
     if LIBRARY.exists() and not force and all(LIBRARY.stat().st_mtime >= o.stat().st_mtime for o in objects):
         return LIBRARY
-    cmd = [NVCC, *ARCH, "-shared", "-o", str(LIBRARY), *map(str, objects), "-lcudart"]
+    cmd = [NVCC, *ARCH, "-shared", "-o", str(LIBRARY), *map(str, objects), "-lcudart", "-ldl"]
     subprocess.run(cmd, check=True)
     return LIBRARY
 

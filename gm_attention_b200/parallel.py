@@ -17,18 +17,29 @@ narrower than ``w`` rows makes a rank's halo reach past its direct neighbour,
 so the exchange is written for arbitrary overlaps of "rows I need" with "rows
 you own".
 
-Communication is ``torch.distributed`` point-to-point (NCCL over NVLink on
-GPUs, gloo on CPU for the tests).  Received halos land in the rank's own
-memory; kernels never read a peer's memory.
+Two exchangers share one interface.  :class:`NativeHaloExchanger` (GPUs) hands an
+exchange to the library as a list of (peer, direction, pointer, bytes) operations that
+become ONE NCCL group on the current stream: sends read the field's slabs in place,
+receives land in the halo rows themselves -- no staging copies, no per-operation
+interpreter work, nothing blocks the host.  :class:`HaloExchanger` goes through
+``torch.distributed`` point-to-point (gloo on CPU for the tests, NCCL on GPUs) with
+staging buffers; every wait of it has a timeout and raises :class:`HaloTimeout`.
+Received halos land in the rank's own memory; kernels never read a peer's memory.
 """
 
 from __future__ import annotations
 
+import ctypes
+import datetime
 from dataclasses import dataclass
 
 import torch
 import torch.distributed as dist
 from torch import Tensor
+
+
+class HaloTimeout(RuntimeError):
+    """A halo message did not arrive in time (a peer never posted its side of the exchange)."""
 
 
 def balanced_cuts(row_cost: list[int] | list[float], parts: int) -> list[int]:
@@ -111,8 +122,10 @@ class HaloExchanger:
     The peers and row ranges are fixed by the band plan, so the staging buffers of every (field shape, dtype) are
     allocated once and reused: an exchange is a few slice copies, one batched send / receive and the landing copies."""
 
-    def __init__(self, plan: BandPlan, rank: int, group: dist.ProcessGroup | None = None) -> None:
-        self.plan, self.rank, self.group = plan, rank, group
+    def __init__(self, plan: BandPlan, rank: int, group: dist.ProcessGroup | None = None, timeout: float = 60.0) -> None:
+        """``timeout``: seconds a wait for a message may take before :class:`HaloTimeout` is raised (host-side waits of
+        CPU process groups; on NCCL a wait only orders streams, and the process group's own timeout covers a dead peer)."""
+        self.plan, self.rank, self.group, self.timeout = plan, rank, group, timeout
         self.elo, self.ehi = plan.extended(rank)
         self.lo, self.hi = plan.owned(rank)
         #: (peer, rows the peer needs from me, rows I need from the peer): global row ranges or None
@@ -153,11 +166,19 @@ class HaloExchanger:
                 recvs.append((other, self._staging(fields[0], len(fields), other, mine, "recv")))
         return self._post(sends, recvs), fields
 
+    def _wait(self, works: list, what: str) -> None:
+        for work in works:
+            try:
+                done = work.wait(datetime.timedelta(seconds=self.timeout))
+            except RuntimeError as exc:  # gloo reports an expired wait as a RuntimeError
+                raise HaloTimeout(f"rank {self.rank}: {what} did not complete within {self.timeout} s: {exc}") from exc
+            if done is False:
+                raise HaloTimeout(f"rank {self.rank}: {what} did not complete within {self.timeout} s")
+
     def finish_fill(self, handle) -> None:
         """Second half: wait for the messages and copy the owners' rows into this rank's halo rows."""
         works, fields = handle
-        for work in works:
-            work.wait()
+        self._wait(works, "the halo fill")
         for other, theirs, mine in self.peers:
             if mine is not None:
                 buf = self._staging(fields[0], len(fields), other, mine, "recv")
@@ -186,8 +207,7 @@ class HaloExchanger:
     def finish_reduce(self, handle) -> None:
         """Second half: add what the others accumulated for this rank's nodes, and zero the halo rows."""
         works, grads = handle
-        for work in works:
-            work.wait()
+        self._wait(works, "the halo reduction")
         for other, theirs, mine in self.peers:
             if theirs is not None:
                 buf = self._staging(grads[0], len(grads), other, theirs, "recv")
@@ -201,6 +221,172 @@ class HaloExchanger:
         """Backward exchange: send the gradient rows accumulated for other ranks' nodes to their
         owners, add what the others accumulated for this rank's nodes, and zero the halo rows."""
         self.finish_reduce(self.start_reduce(*grads))
+
+
+class NativeHaloExchanger:
+    """The halo exchange through the library's own NCCL path (``gm_halo_*``): same interface as :class:`HaloExchanger`.
+
+    The communicator is created collectively over ``group`` (default: the world): rank 0's NCCL id travels through
+    ``torch.distributed``.  An exchange enqueues one NCCL group on the CURRENT stream (or, for the split calls, on a
+    side stream ordered against it with events) and returns; nothing waits on the host."""
+
+    def __init__(self, plan: BandPlan, rank: int, device: torch.device, group: dist.ProcessGroup | None = None) -> None:
+        from gm_attention_b200 import _lib
+
+        self._lib = _lib
+        self.plan, self.rank, self.device = plan, rank, device
+        self.elo, self.ehi = plan.extended(rank)
+        self.lo, self.hi = plan.owned(rank)
+        self.peers = [(other, plan.needs(other, rank), plan.needs(rank, other)) for other in range(plan.world)
+                      if other != rank and (plan.needs(other, rank) is not None or plan.needs(rank, other) is not None)]
+        ident = torch.zeros(128, dtype=torch.uint8)
+        if rank == 0:
+            raw = (ctypes.c_ubyte * 128)()
+            _lib.call("gm_halo_unique_id", ctypes.addressof(raw))
+            ident = torch.tensor(list(raw), dtype=torch.uint8)
+        ident = ident.to(device)
+        dist.broadcast(ident, 0, group=group)
+        raw = (ctypes.c_ubyte * 128)(*ident.cpu().tolist())
+        comm = ctypes.c_void_p()
+        with torch.cuda.device(device):
+            _lib.call("gm_halo_comm_create", ctypes.addressof(raw), rank, plan.world, ctypes.byref(comm))
+        self.comm = comm
+        self.side = torch.cuda.Stream(device)
+        self._staging: dict = {}
+        self._op_cache: dict = {}
+
+    def close(self) -> None:
+        if self.comm:
+            torch.cuda.synchronize(self.device)
+            self._lib.call("gm_halo_comm_destroy", self.comm)
+            self.comm = ctypes.c_void_p()
+
+    def _local(self, rows: tuple[int, int]) -> tuple[int, int]:
+        return rows[0] - self.elo, rows[1] - self.elo
+
+    def _ops(self, key: tuple, build) -> tuple:
+        """ctypes argument arrays of an exchange, cached by the buffers' addresses and shapes."""
+        hit = self._op_cache.get(key)
+        if hit is None:
+            ops = build()
+            n = len(ops)
+            hit = (n, (ctypes.c_int * n)(*[o[0] for o in ops]), (ctypes.c_int * n)(*[o[1] for o in ops]),
+                   (ctypes.c_void_p * n)(*[o[2] for o in ops]), (ctypes.c_int64 * n)(*[o[3] for o in ops]))
+            if len(self._op_cache) > 64:
+                self._op_cache.clear()
+            self._op_cache[key] = hit
+        return hit
+
+    def _exchange(self, ops: tuple, stream: torch.cuda.Stream) -> None:
+        n, peers, sends, pointers, nbytes = ops
+        with torch.cuda.device(self.device):
+            self._lib.call("gm_halo_exchange", self.comm, n, peers, sends, pointers, nbytes, stream.cuda_stream)
+
+    @staticmethod
+    def _slabs(field: Tensor, r0: int, r1: int):
+        """(address, bytes) of the rows r0 .. r1 - 1 of every sample of a (batch, rows, nlon, D) field: contiguous each."""
+        row_bytes = field.shape[2] * field.shape[3] * field.element_size()
+        sample_bytes = field.shape[1] * row_bytes
+        base = field.data_ptr()
+        return [(base + b * sample_bytes + r0 * row_bytes, (r1 - r0) * row_bytes) for b in range(field.shape[0])]
+
+    def _fill_ops(self, fields: tuple[Tensor, ...]) -> tuple:
+        def build():
+            ops = []
+            for other, theirs, mine in self.peers:
+                for f in fields:
+                    if theirs is not None:
+                        ops += [(other, 1, ptr, n) for ptr, n in self._slabs(f, *self._local(theirs))]
+                    if mine is not None:
+                        ops += [(other, 0, ptr, n) for ptr, n in self._slabs(f, *self._local(mine))]
+            return ops
+        return self._ops(("fill", *(f.data_ptr() for f in fields), tuple(fields[0].shape), fields[0].dtype), build)
+
+    def fill_halos(self, *fields: Tensor, stream: torch.cuda.Stream | None = None) -> None:
+        """Forward exchange on the current stream: every field's halo rows receive the owners' rows."""
+        for f in fields:
+            if not f.is_contiguous():
+                raise RuntimeError("halo exchange needs contiguous (batch, rows, nlon, D) fields")
+        self._exchange(self._fill_ops(fields), stream or torch.cuda.current_stream(self.device))
+
+    def start_fill(self, *fields: Tensor):
+        """The forward exchange on a side stream: work that does not read the halo rows can be launched on the current
+        stream before :meth:`finish_fill` and runs while the rows travel."""
+        self.side.wait_stream(torch.cuda.current_stream(self.device))
+        self.fill_halos(*fields, stream=self.side)
+        done = torch.cuda.Event()
+        done.record(self.side)
+        return done
+
+    def finish_fill(self, done) -> None:
+        torch.cuda.current_stream(self.device).wait_event(done)
+
+    def _recv_buffer(self, like: Tensor, count: int, other: int, rows: tuple[int, int]) -> Tensor:
+        key = (count, other, rows, tuple(like.shape), like.dtype)
+        buf = self._staging.get(key)
+        if buf is None:
+            buf = torch.empty((count, like.shape[0], rows[1] - rows[0], *like.shape[2:]), dtype=like.dtype, device=like.device)
+            self._staging[key] = buf
+        return buf
+
+    def _reduce_ops(self, grads: tuple[Tensor, ...]) -> tuple:
+        """Sends per (field, sample) slab of the halo rows; receives per (field, sample) slab of one staging buffer per
+        peer: both sides post the same messages in the same order."""
+        def build():
+            ops = []
+            for other, theirs, mine in self.peers:
+                if mine is not None:  # halo rows I hold partial sums for: they belong to `other`
+                    for g in grads:
+                        ops += [(other, 1, ptr, n) for ptr, n in self._slabs(g, *self._local(mine))]
+                if theirs is not None:  # rows of mine `other` holds partial sums for
+                    buf = self._recv_buffer(grads[0], len(grads), other, theirs)
+                    slab = buf[0, 0].numel() * buf.element_size()
+                    for slot in range(len(grads)):
+                        ops += [(other, 0, buf[slot, b].data_ptr(), slab) for b in range(buf.shape[1])]
+            return ops
+        return self._ops(("reduce", *(g.data_ptr() for g in grads), tuple(grads[0].shape), grads[0].dtype), build)
+
+    def _land(self, grads: tuple[Tensor, ...], stream: torch.cuda.Stream, zero_halo: bool) -> None:
+        """Add the received partial sums to this rank's rows (one launch per peer and field); zero the halo rows."""
+        code = self._lib.dtype_code(grads[0].dtype)
+        row_elems = grads[0].shape[2] * grads[0].shape[3]
+        with torch.cuda.device(self.device), torch.cuda.stream(stream):
+            for other, theirs, _ in self.peers:
+                if theirs is None:
+                    continue
+                buf = self._recv_buffer(grads[0], len(grads), other, theirs)
+                r0, r1 = self._local(theirs)
+                for slot, g in enumerate(grads):
+                    self._lib.call("gm_halo_accumulate", g.data_ptr() + r0 * row_elems * g.element_size(), buf[slot].data_ptr(), g.shape[0],
+                                   (r1 - r0) * row_elems, g.shape[1] * row_elems, (r1 - r0) * row_elems, code, stream.cuda_stream)
+            if zero_halo:
+                for g in grads:
+                    if self.lo > self.elo:
+                        g[:, : self.lo - self.elo].zero_()
+                    if self.ehi > self.hi:
+                        g[:, self.hi - self.elo:].zero_()
+
+    def reduce_halos(self, *grads: Tensor, zero_halo: bool = True) -> None:
+        """Backward exchange on the current stream: the partial sums this rank formed for other ranks' rows go to
+        their owners, the sums others formed for this rank's rows are added in, the halo rows are zeroed."""
+        stream = torch.cuda.current_stream(self.device)
+        self._exchange(self._reduce_ops(grads), stream)
+        self._land(grads, stream, zero_halo)
+
+    def start_reduce(self, *grads: Tensor):
+        """The backward exchange on a side stream.  The halo rows' sums must be final on the current stream; the rank's
+        own rows may still be written until :meth:`finish_reduce`, which adds the received sums on the current stream."""
+        self.side.wait_stream(torch.cuda.current_stream(self.device))
+        self._exchange(self._reduce_ops(grads), self.side)
+        done = torch.cuda.Event()
+        done.record(self.side)
+        return done, grads
+
+    def finish_reduce(self, handle, zero_halo: bool = True) -> None:
+        done, grads = handle
+        stream = torch.cuda.current_stream(self.device)
+        stream.wait_event(done)
+        self._land(grads, stream, zero_halo)
 
 
 @dataclass(frozen=True)

@@ -360,6 +360,43 @@ int gm_lattice_attention_backward_tc4_passes(const void* dout, const void* q, co
 
 int gm_lattice_attention_tc4_wait_expired(int* expired);
 
+/* ------------------------------------------------------------------------
+ * Halo exchange of the latitude-band decomposition (no counterpart in the
+ * reference, which has no distributed code).  One process per GPU; a rank
+ * holds its band of lattice rows plus the rows either side that its
+ * neighbourhoods reach.  An exchange is a list of point-to-point operations
+ * (peer rank, send or receive, device pointer, bytes), issued as ONE NCCL
+ * group on `stream`: sends read field memory in place, receives land in this
+ * GPU's own memory; nothing blocks the host.  NCCL is looked up at run time in
+ * the libnccl.so.2 the process has loaded (GM_ERR_UNSUPPORTED if there is none).
+ *
+ *   gm_halo_unique_id    rank 0 creates the 128-byte id every rank passes to
+ *   gm_halo_comm_create  (collective over the ranks; binds to the current device)
+ *   gm_halo_comm_error   NCCL's asynchronous error state of the communicator
+ *                        (0: none), for a host-side watchdog
+ *   gm_halo_move         packs the rows a neighbour needs into one buffer, unpacks
+ *                        or adds a received buffer (one launch each way): NCCL
+ *                        costs ~10 us per point-to-point operation, so a
+ *                        neighbour gets ONE message per direction
+ *   gm_halo_accumulate   dst slab s += src slab s for `slabs` slabs of
+ *                        slab_elems elements, dst_stride / src_stride elements
+ *                        apart: adds the partial sums a neighbour sent for this
+ *                        rank's rows (dtype GM_F32, GM_F64 or GM_BF16)
+ * ------------------------------------------------------------------------ */
+int gm_halo_unique_id(void* id128);
+int gm_halo_comm_create(const void* id128, int rank, int world, void** comm);
+int gm_halo_comm_destroy(void* comm);
+int gm_halo_comm_error(void* comm, int* async_error);
+int gm_halo_exchange(void* comm, int n_ops, const int* peers, const int* sends, void* const* pointers, const int64_t* nbytes,
+                     void* stream);
+int gm_halo_accumulate(void* dst, const void* src, int64_t slabs, int64_t slab_elems, int64_t dst_stride, int64_t src_stride,
+                       int dtype, void* stream);
+/* Slabs of up to 4 fields <-> one packed buffer laid out (field, sample, slab): mode 0 packs, 1 unpacks, 2 adds the
+ * buffer to the fields (GM_BF16 or GM_F32).  fields[i]: sample 0's slab of field i; samples sample_bytes apart;
+ * slab_bytes each; everything in 16-byte units.  One launch. */
+int gm_halo_move(int mode, void* const* fields, int n_fields, int64_t batch, int64_t slab_bytes, int64_t sample_bytes, void* packed,
+                 int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -105,3 +105,37 @@ def test_sharded_layer_equals_unsharded(tmp_path, cuts):
     world = len(cuts) - 1
     mp.spawn(_worker, args=(world, _free_port(), cuts, str(tmp_path)), nprocs=world, join=True)
     assert sorted(os.listdir(tmp_path)) == [f"ok{r}" for r in range(world)]
+
+
+def _silent_peer(rank: int, world: int, port: int, result_dir: str) -> None:
+    """Rank 1 never posts its side of the exchange: rank 0's wait runs out and reports it (no hang)."""
+    import time
+
+    from gm_attention_b200.parallel import HaloTimeout
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        plan = BandPlan(8, 4, 1, (0, 4, 8))
+        field = torch.zeros(1, plan.extended(rank)[1] - plan.extended(rank)[0], 4, 3)
+        if rank == 0:
+            ex = HaloExchanger(plan, rank, timeout=1.5)
+            start = time.monotonic()
+            try:
+                ex.fill_halos(field)
+            except HaloTimeout as exc:
+                assert "did not complete" in str(exc) and time.monotonic() - start < 30
+                open(os.path.join(result_dir, "timed_out"), "w").close()
+        else:
+            time.sleep(4.0)  # posts nothing; stays alive until rank 0 has given up
+        open(os.path.join(result_dir, f"done{rank}"), "w").close()
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:  # noqa: BLE001  (the aborted exchange may have left the group unusable)
+            pass
+
+
+def test_a_peer_that_never_posts_times_out(tmp_path):
+    mp.spawn(_silent_peer, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    assert sorted(os.listdir(tmp_path)) == ["done0", "done1", "timed_out"]

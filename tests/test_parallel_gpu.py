@@ -19,14 +19,14 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _rank(rank: int, world: int, port: int, out_dir: str) -> None:
+def _rank(rank: int, world: int, port: int, out_dir: str, native: bool) -> None:
     import torch.distributed as dist
 
     from gm_attention_b200.attention import AttentionTables, build_lattice_tables, lattice_attention_backward, lattice_attention_forward
     from gm_attention_b200.fields import FieldType
     from gm_attention_b200.geometry import compute_edge_geometry, midpoint_lattice
     from gm_attention_b200.nn import fused_attention as fa
-    from gm_attention_b200.parallel import BandPlan, HaloExchanger, band_geometry, row_degrees
+    from gm_attention_b200.parallel import BandPlan, HaloExchanger, NativeHaloExchanger, band_geometry, row_degrees
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
@@ -57,7 +57,8 @@ def _rank(rank: int, world: int, port: int, out_dir: str) -> None:
         q, k, v, g = (f[:, elo:ehi].contiguous() for f in fields)
         k[:, : lo - elo] = float("nan"); k[:, hi - elo:] = float("nan")  # halos must come from the owners
         v[:, : lo - elo] = float("nan"); v[:, hi - elo:] = float("nan")
-        halo = HaloExchanger(plan, rank)
+        # the library's own NCCL groups (sends and receives in place), or torch.distributed point-to-point with staging
+        halo = NativeHaloExchanger(plan, rank, device) if native else HaloExchanger(plan, rank)
         halo.fill_halos(k, v)
         flat = lambda t: t.reshape(-1, D)
         out, lse = lattice_attention_forward(flat(q), flat(k), flat(v), local, tensor_cores=False)
@@ -108,13 +109,16 @@ def _rank(rank: int, world: int, port: int, out_dir: str) -> None:
             assert err < 2e-2, f"rank {rank} bf16 {name}: {err}"
         open(os.path.join(out_dir, f"ok{rank}"), "w").close()
     finally:
+        if native and "halo" in locals():
+            halo.close()
         dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_sharded_layer_on_gpus(tmp_path):
+@pytest.mark.parametrize("native", [True, False], ids=["library-nccl", "torch-distributed"])
+def test_sharded_layer_on_gpus(tmp_path, native):
     import torch.multiprocessing as mp
 
     world = min(torch.cuda.device_count(), 4)
-    mp.spawn(_rank, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_rank, args=(world, _free_port(), str(tmp_path), native), nprocs=world, join=True)
     assert sorted(os.listdir(tmp_path)) == [f"ok{r}" for r in range(world)]
