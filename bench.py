@@ -55,10 +55,12 @@ def parse() -> argparse.Namespace:
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--dtype", choices=["bf16", "f32"], default="bf16")
     p.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    p.add_argument("--workload", choices=["headline", "mid", "small", "ops"], default="headline",
+    p.add_argument("--workload", choices=["headline", "mid", "small", "ops", "conv", "conv-mid"], default="headline",
                    help="headline (default): 256 x 512, batch 8; mid / small: 128 x 256 x 4 and 64 x 128 x 2 (profiling and smoke sizes); "
                         "ops: times every op-level entry point (scores+softmax, depthwise conv, factored kernel, pair term) "
-                        "against its own interface bytes and prints one JSON object")
+                        "against its own interface bytes and prints one JSON object; conv: the depthwise convolution with its radial "
+                        "network on the 256 x 512 lattice, radius 4 pi / 256, batch 4, 64 x (m = 0, 1, 2), forward + backward (conv-mid: "
+                        "128 x 256, for profiler captures)")
     p.add_argument("--kernel", choices=["lattice", "csr"], default="lattice",
                    help="lattice: compact-table fast path (default); csr: general per-edge-table kernels")
     p.add_argument("--radius-rows", type=float, default=None,
@@ -66,7 +68,7 @@ def parse() -> argparse.Namespace:
     p.add_argument("--overlap", action="store_true",
                    help="N > 1: run the layer around the halo exchange (interior rows while the halos travel) instead of exchanging "
                         "before / after it; measured equal within 1 %% at N = 8 (the exchange is latency, not bandwidth), so off by default")
-    p.add_argument("--halo", choices=["native", "torch"], default="native",
+    p.add_argument("--halo", choices=["native", "native-slabs", "torch"], default="native",
                    help="N > 1: native = the library's own NCCL groups issued from C (default); torch = torch.distributed point-to-point with staging buffers")
     p.add_argument("--per-rank", action="store_true",
                    help="every rank prints its own per-step timings (halo exchange in, forward, backward, halo sums out) to stderr")
@@ -326,8 +328,8 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
     # the library's own NCCL groups (sends / receives in place, nothing on the host); --halo torch: torch.distributed with staging
     halo = None
     if world > 1:
-        halo = NativeHaloExchanger(plan, rank, device) if args.halo == "native" else HaloExchanger(plan, rank)
-    reduce_kw = {"zero_halo": False} if args.halo == "native" else {}  # the halo rows of dk / dv are not part of the rank's result
+        halo = NativeHaloExchanger(plan, rank, device, packed=args.halo == "native") if args.halo != "torch" else HaloExchanger(plan, rank)
+    reduce_kw = {"zero_halo": False} if args.halo != "torch" else {}  # the halo rows of dk / dv are not part of the rank's result
     fwd_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     bwd_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
 
@@ -351,7 +353,8 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
             if index is not None:
                 fwd_ev[index][1].record()
                 bwd_ev[index][0].record()
-            ws = (torch.zeros_like(flat(q)), torch.zeros_like(flat(q)), torch.zeros_like(flat(q)),
+            # every row the rank owns is written by one of the passes below; the halo rows of dq are not part of its result
+            ws = (torch.empty_like(flat(q)), torch.empty_like(flat(q)), torch.empty_like(flat(q)),
                   torch.empty((batch * n_ext, heads), dtype=torch.float32, device=device))
             attention_backward(flat(g), flat(q), flat(k), flat(v), out, lse, split.full, passes=3, workspace=ws)
             attention_backward(flat(g), flat(q), flat(k), flat(v), out, lse, split.halo_sources, passes=4, workspace=ws)
@@ -552,7 +555,7 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
                 geo2 = fa.geometry(edges2, radius, "hard", torch.float32)
                 gen2 = AttentionTables(geo2.transport, geo2.bias, geo2.inside, geo2.row_ptr, geo2.source, p.rows, heads, 1.0 / math.sqrt(attn.dimension))
                 e_tables = build_lattice_tables(gen2, e2e_rows, nlon, p.rows, heads, gen2.scale)
-                e_halo = NativeHaloExchanger(plan2, rank, device) if args.halo == "native" else HaloExchanger(plan2, rank)
+                e_halo = NativeHaloExchanger(plan2, rank, device, packed=args.halo == "native") if args.halo != "torch" else HaloExchanger(plan2, rank)
                 shape2 = (batch, e2e_rows, nlon, D)
                 e_host = [torch.empty(shape2, dtype=dtype).pin_memory() for _ in range(4)]
                 for r in range(lo2, hi2):
@@ -759,8 +762,188 @@ def run_ops(args: argparse.Namespace) -> None:
                       "ops": results}))
 
 
+def run_conv(args: argparse.Namespace) -> None:
+    """Depthwise steerable convolution, forward + backward, with its radial network: 256 x 512 lattice, radius 4 pi / 256,
+    batch 4, field type 64 x (m = 0, 1, 2) (D = 320, a_0 = 64, W = 512; 22 999 040 edges per sample), radial network of 4
+    Gaussians -> 16 -> (64 | 512).  One step = radial network on the table entries, fold, apply, and the backward of all
+    three (field gradient, table gradient, network gradients).  Single GPU."""
+    import numpy as np
+    import torch
+
+    from gm_attention_b200.fields import FieldType
+    from gm_attention_b200.geometry import compute_edge_geometry, midpoint_lattice
+    from gm_attention_b200.nn import fused_attention as fa
+    from gm_attention_b200.nn.lattice_depthwise import RadialCoefficients, _apply, _table_gradient, conv_tables, fold, lattice_depthwise
+
+    nlat, nlon, batch, copies = (256, 512, 4, 64) if args.workload == "conv" else (128, 256, 4, 64)
+    radius = 4 * math.pi / nlat
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32
+    elem = 2 if args.dtype == "bf16" else 4
+    head = FieldType({0: copies, 1: copies, 2: copies})
+    D, a0, w = head.dimension, copies, 8 * copies
+    lattice = midpoint_lattice(nlat, nlon, device)
+    edges = compute_edge_geometry(lattice, lattice.frames, radius, max_frequency=4, dtype=torch.float32)
+    geo = fa.geometry(edges, radius, "hard", torch.float32)
+    owner = type("Layer", (), {})()
+    plan = fa._plan(owner, head, head, 1)
+    tables = conv_tables(geo, edges.distances.float(), geo.weights, plan.rows, nlat, nlon)
+    e1, n1 = edges.n_edges, nlat * nlon
+    del edges, geo
+    torch.manual_seed(0)
+    net = RadialCoefficients(a0, w, radius, n_radial_basis=4, radial_hidden_features=(16,), device=device)
+    gen = torch.Generator().manual_seed(0)
+    host = [torch.randn(batch * n1, D, generator=gen).to(dtype).pin_memory() for _ in range(2)]
+    v, g = (h.to(device) for h in host)
+    v.requires_grad_(True)
+    peak, peak_kind = 6650.0, "fallback"
+    try:
+        peak, peak_kind = float(json.loads((ROOT / "MEASURED_PEAKS.json").read_text())["hbm_gbs"]), "measured"
+    except (OSError, KeyError, ValueError):
+        pass
+
+    def step():
+        v.grad = None
+        net.zero_grad(set_to_none=True)
+        rc, cc = net(tables.distances)
+        y = lattice_depthwise(v, rc, cc, tables)
+        y.backward(g)
+        return y.detach(), v.grad
+
+    for _ in range(max(args.warmup, 3)):
+        y, dv = step()
+    torch.cuda.synchronize()
+
+    # ---- parity: sampled targets / sources of the last sample against the CPU oracle of the reference's depthwise op,
+    # fed with this step's own coefficients expanded to the sampled edges
+    parity = None
+    if not args.no_parity:
+        from oracle import geometry_np as GN
+        from oracle import sampled as SP
+
+        with torch.no_grad():
+            rc_t, cc_t = net(tables.distances)
+        lat = tables.lattice
+        t_rows = [0, 1, 4, 9, nlat // 2, nlat - 1]
+        targets = np.array([r * nlon + c for r in t_rows for c in (0, nlon - 1, nlon // 2 + 1)], np.int64)
+        sources = np.array([9 * nlon, (nlat // 2) * nlon + nlon - 1], np.int64)
+        sample = SP.sample_problem(GN.midpoint_lattice(nlat, nlon), radius, targets, sources, 4, np.float32)
+        span = 2 * lat.halo + 1
+        cnt, lo, off = (x.cpu().numpy().reshape(-1) for x in (lat.win_cnt, lat.win_lo, lat.win_off))
+        tgt, src = np.repeat(sample.nodes, np.diff(sample.row_ptr)), sample.nodes[sample.source_index]
+        win = (tgt // nlon) * span + (src // nlon - tgt // nlon + lat.halo)
+        entry = torch.from_numpy(off[win] + (src % nlon - tgt % nlon - lo[win]) % nlon).to(device)
+        b = batch - 1
+        pick = lambda x, nodes: x[torch.from_numpy(b * n1 + nodes).to(device)].float().cpu().numpy()
+        want = SP.run_conv(sample, pick(v.detach(), sample.nodes), pick(g, sample.nodes), rc_t[entry].float().cpu().numpy(),
+                           cc_t[entry].float().cpu().numpy(), np.array(plan.rows, np.int64), radius, a0, w)
+        got = {"out": pick(y, sample.targets), "dv": pick(dv, sample.sources)}
+        errs = {n: float(np.abs(got[n] - want[n]).max() / max(float(np.abs(want[n]).max()), 1e-30)) for n in got}
+        tolerance = 2e-2 if args.dtype == "bf16" else 2e-5
+        parity = {"max_rel": max(errs.values()), "per_tensor": errs, "tolerance": tolerance, "targets": int(targets.shape[0]),
+                  "sources": int(sources.shape[0]), "oracle_edges": sample.n_edges,
+                  "against": "CPU oracle of the reference's depthwise op (C restatement pinned to its compiled driver), float32, on the same "
+                             "rounded inputs, per-edge coefficients = this step's table entries"}
+        if not parity["max_rel"] < tolerance:
+            print(json.dumps({"error": "parity check failed", "parity": parity}), file=sys.stderr)
+            sys.exit(3)
+
+    clocks = ClockSampler(0)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    with clocks:
+        torch.cuda.synchronize()
+        for a_ev, b_ev in ev:
+            a_ev.record()
+            step()
+            b_ev.record()
+        torch.cuda.synchronize()
+    ms_step = statistics.mean(a.elapsed_time(b) for a, b in ev)
+
+    # ---- the three kernels alone
+    with torch.no_grad():
+        table = fold(*net(tables.distances), tables)
+        t_table = table.index_select(0, tables.lattice.t_entry)
+        kernels = {"apply (forward)": lambda: _apply(v.detach(), table, tables, False),
+                   "apply, transposed (field gradient)": lambda: _apply(g, t_table, tables, True),
+                   "table_grad": lambda: _table_gradient(g, v.detach(), tables)}
+        kernel_ms = {}
+        for name, fn in kernels.items():
+            fn()
+            pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(5)]
+            for a_ev, b_ev in pairs:
+                a_ev.record(); fn(); b_ev.record()
+            torch.cuda.synchronize()
+            kernel_ms[name] = statistics.mean(a.elapsed_time(b) for a, b in pairs)
+    top = max(kernel_ms, key=kernel_ms.get)
+    n_nodes, total_edges = batch * n1, batch * e1
+    table_bytes = table.numel() * 4
+    bytes_of = {"apply (forward)": 2 * n_nodes * D * elem + table_bytes, "apply, transposed (field gradient)": 2 * n_nodes * D * elem + table_bytes,
+                "table_grad": 2 * n_nodes * D * elem + table_bytes}
+    flops_pass = 2.0 * (a0 + 4 * 2 * copies) * total_edges
+    achieved = bytes_of[top] / (kernel_ms[top] * 1e-3) / 1e9
+
+    # ---- end to end from pinned host buffers: v and g in, y and dv out, every step
+    e2e = None
+    if not args.no_e2e:
+        outs = [torch.empty_like(host[0]).pin_memory() for _ in range(2)]
+        pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(max(3, args.steps // 2))]
+        for a_ev, b_ev in pairs:
+            a_ev.record()
+            with torch.no_grad():
+                v.copy_(host[0], non_blocking=True)
+                g.copy_(host[1], non_blocking=True)
+            y, dv = step()
+            outs[0].copy_(y, non_blocking=True)
+            outs[1].copy_(dv, non_blocking=True)
+            b_ev.record()
+        torch.cuda.synchronize()
+        e_ms = statistics.mean(a.elapsed_time(b) for a, b in pairs[1:])
+        e2e = {"value": total_edges / (e_ms * 1e-3), "unit": "edges/s", "h2d_bytes_per_step": 2 * n_nodes * D * elem,
+               "d2h_bytes_per_step": 2 * n_nodes * D * elem, "ms_per_step": e_ms, "steps": len(pairs) - 1}
+
+    cpu = None
+    if not args.no_cpu_baseline:
+        from oracle import geometry_np as GN
+        from oracle import sampled as SP
+
+        row = nlat // 4
+        whole = SP.sample_problem(GN.midpoint_lattice(nlat, nlon), radius, row * nlon + np.arange(nlon, dtype=np.int64), np.zeros(0, np.int64), 4, np.float32)
+        rng = np.random.default_rng(0)
+        cv, cg = (rng.standard_normal((whole.nodes.shape[0], D)).astype(np.float32) for _ in range(2))
+        crc, ccc = rng.standard_normal((whole.n_edges, a0)).astype(np.float32), rng.standard_normal((whole.n_edges, w)).astype(np.float32)
+        t0 = time.perf_counter()
+        reps = 0
+        while time.perf_counter() - t0 < 10.0:
+            SP.run_conv(whole, cv, cg, crc, ccc, np.array(plan.rows, np.int64), radius, a0, w)
+            reps += 1
+        seconds = time.perf_counter() - t0
+        cpu = {"value": reps * whole.n_edges / seconds, "unit": "edges/s", "cores": 1, "kind": "port",
+               "sample": f"all {nlon} targets of lattice row {row} of one sample ({whole.n_edges} edges), float32, forward + backward of the depthwise op "
+                         f"with per-edge coefficients given (the reference's radial network per edge is NOT timed), {reps} repetitions", "seconds": seconds}
+
+    print(json.dumps({
+        "metric": "depthwise-conv fwd+bwd neighbour-edges/sec", "value": total_edges / (ms_step * 1e-3), "unit": "edges/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": args.dtype, "data": "synthetic",
+        "config": {"workload": f"depthwise steerable convolution fwd+bwd with its radial network, {nlat}x{nlon} midpoint equiangular lattice, radius "
+                               f"4pi/{nlat}, batch {batch}, {copies}x(m=0,1,2), D={D}, a0={a0}, W={w}, {e1} edges per sample, {tables.n_entries} table entries",
+                   "parallelism": "single GPU", "l2": "inputs larger than L2 (no flush needed)"},
+        "roofline": {"bound": "hbm", "kernel": f"conv kernel: {top}", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": peak_kind, "algorithmic_bytes_per_launch": bytes_of[top], "launch_ms": kernel_ms[top],
+                     "kernels_ms": kernel_ms, "fp32_fma_tflops_per_kernel": {k: flops_pass / (ms * 1e-3) / 1e12 for k, ms in kernel_ms.items()},
+                     "note": "FMA-bound by construction: 4 multiply-adds per complex copy, edge and sample against ~0.01 B of compulsory traffic"},
+        "gpu_launches": args.steps * 3, "clocks": clocks.summary(), "e2e": e2e, "parity": parity, "cpu_baseline": cpu}))
+
+
 def main() -> None:
     args = parse()
+    if args.workload in ("conv", "conv-mid"):
+        if args.impl == "reference" or args.gpus > 1:
+            print(json.dumps({"impl": args.impl, "unavailable": "the depthwise workload is measured on one GPU, its CPU figure is the cpu_baseline of that line"}))
+            return
+        run_conv(args)
+        return
     if args.workload == "ops":
         run_ops(args)
         return

@@ -53,6 +53,8 @@ SIGNATURES: dict[str, list[Any]] = {
     "gm_halo_exchange": [_P, _I, _P, _P, _P, _P, _P],
     "gm_halo_accumulate": [_P, _P, _L, _L, _L, _L, _I, _P],
     "gm_halo_move": [_I, _P, _I, _L, _L, _L, _P, _I, _P],
+    "gm_lattice_conv_apply": [_P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "gm_lattice_conv_table_grad": [_P, _P, _P, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "gm_attention_backward_static": [_P] * 12 + [_L, _L, _L, _I, _I, _I, _I, _D, _I, _P, _P, _P, _P],
 }
 #: entry points that return a size instead of a status

@@ -160,6 +160,10 @@ class LatticeTables:
     tc_win_off: Tensor | None = None
     t_tc_entries: Tensor | None = None
     t_tc_win_off: Tensor | None = None
+    # where the entries came from: the per-edge index (an edge of the target in column 0) of every entry, and the forward
+    # entry of every transposed entry
+    entry_edge: Tensor | None = None
+    t_entry: Tensor | None = None
 
     def host_descriptor(self) -> Any:
         flat = [x for row in self.desc_rows for x in row]
@@ -309,6 +313,7 @@ def build_lattice_tables(geometry: Any, rows: int, nlon: int, desc_rows: tuple[t
     width = 2 * halo + 1
     order = np.lexsort((dlon, drow, owner_row))
     owner_row, drow, dlon, tau, bias = owner_row[order], drow[order], dlon[order], tau[order], bias[order]
+    entry_edge = index[order]
     win_cnt = np.zeros((rows, width), np.int32)
     win_lo = np.zeros((rows, width), np.int32)
     win_off = np.zeros((rows, width), np.int32)
@@ -329,6 +334,7 @@ def build_lattice_tables(geometry: Any, rows: int, nlon: int, desc_rows: tuple[t
     t_lo = np.zeros_like(win_lo)
     t_off = np.zeros_like(win_off)
     t_entries = np.zeros_like(entries)
+    t_entry = np.zeros(key.size, np.int64)
     cursor = 0
     for j in range(rows):
         for c in range(width):
@@ -342,6 +348,7 @@ def build_lattice_tables(geometry: Any, rows: int, nlon: int, desc_rows: tuple[t
             a = int(win_off[i, cc])
             t_cnt[j, c], t_lo[j, c], t_off[j, c] = n, -(int(win_lo[i, cc]) + n - 1), cursor
             t_entries[cursor:cursor + n] = entries[a:a + n][::-1]
+            t_entry[cursor:cursor + n] = np.arange(a + n - 1, a - 1, -1)
             cursor += n
     cost = win_cnt.sum(1)
     t_cost = t_cnt.sum(1)
@@ -355,7 +362,7 @@ def build_lattice_tables(geometry: Any, rows: int, nlon: int, desc_rows: tuple[t
         tc = (dev(tc_e), dev(tc_o), dev(t_tc_e), dev(t_tc_o))
     return LatticeTables(rows, nlon, halo, stride, norders, dev(win_cnt), dev(win_lo), dev(win_off), dev(entries), dev(row_order),
                          dev(t_cnt), dev(t_lo), dev(t_off), dev(t_entries), dev(t_row_order), tuple(tuple(int(x) for x in r) for r in desc_rows),
-                         heads, float(scale), int(geometry.source.shape[0]), *tc)
+                         heads, float(scale), int(geometry.source.shape[0]), *tc, dev(entry_edge.astype(np.int64)), dev(t_entry))
 
 
 def _check_lattice(q: Tensor, k: Tensor, v: Tensor, t: LatticeTables) -> tuple[torch.device, int]:

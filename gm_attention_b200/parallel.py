@@ -227,14 +227,17 @@ class NativeHaloExchanger:
     """The halo exchange through the library's own NCCL path (``gm_halo_*``): same interface as :class:`HaloExchanger`.
 
     The communicator is created collectively over ``group`` (default: the world): rank 0's NCCL id travels through
-    ``torch.distributed``.  An exchange enqueues one NCCL group on the CURRENT stream (or, for the split calls, on a
-    side stream ordered against it with events) and returns; nothing waits on the host."""
+    ``torch.distributed``.  An exchange is: one launch per neighbour packing the rows it needs (all fields, all samples)
+    into one buffer, ONE NCCL group of one message per neighbour and direction, one launch per neighbour unpacking
+    (forward) or adding (backward) what arrived -- all enqueued on the CURRENT stream (or, for the split calls, on a side
+    stream ordered against it with events); nothing waits on the host.  ``packed=False`` sends every (field, sample)
+    slab as its own message straight out of field memory instead: no packing launches, many more NCCL operations."""
 
-    def __init__(self, plan: BandPlan, rank: int, device: torch.device, group: dist.ProcessGroup | None = None) -> None:
+    def __init__(self, plan: BandPlan, rank: int, device: torch.device, group: dist.ProcessGroup | None = None, packed: bool = True) -> None:
         from gm_attention_b200 import _lib
 
         self._lib = _lib
-        self.plan, self.rank, self.device = plan, rank, device
+        self.plan, self.rank, self.device, self.packed = plan, rank, device, packed
         self.elo, self.ehi = plan.extended(rank)
         self.lo, self.hi = plan.owned(rank)
         self.peers = [(other, plan.needs(other, rank), plan.needs(rank, other)) for other in range(plan.world)
@@ -252,8 +255,8 @@ class NativeHaloExchanger:
             _lib.call("gm_halo_comm_create", ctypes.addressof(raw), rank, plan.world, ctypes.byref(comm))
         self.comm = comm
         self.side = torch.cuda.Stream(device)
-        self._staging: dict = {}
-        self._op_cache: dict = {}
+        self._buffers: dict = {}
+        self._plans: dict = {}
 
     def close(self) -> None:
         if self.comm:
@@ -264,23 +267,14 @@ class NativeHaloExchanger:
     def _local(self, rows: tuple[int, int]) -> tuple[int, int]:
         return rows[0] - self.elo, rows[1] - self.elo
 
-    def _ops(self, key: tuple, build) -> tuple:
-        """ctypes argument arrays of an exchange, cached by the buffers' addresses and shapes."""
-        hit = self._op_cache.get(key)
-        if hit is None:
-            ops = build()
-            n = len(ops)
-            hit = (n, (ctypes.c_int * n)(*[o[0] for o in ops]), (ctypes.c_int * n)(*[o[1] for o in ops]),
-                   (ctypes.c_void_p * n)(*[o[2] for o in ops]), (ctypes.c_int64 * n)(*[o[3] for o in ops]))
-            if len(self._op_cache) > 64:
-                self._op_cache.clear()
-            self._op_cache[key] = hit
-        return hit
-
-    def _exchange(self, ops: tuple, stream: torch.cuda.Stream) -> None:
-        n, peers, sends, pointers, nbytes = ops
-        with torch.cuda.device(self.device):
-            self._lib.call("gm_halo_exchange", self.comm, n, peers, sends, pointers, nbytes, stream.cuda_stream)
+    def _buffer(self, kind: str, like: Tensor, count: int, other: int, rows: tuple[int, int]) -> Tensor:
+        """One packed buffer per (direction, peer) for all fields of an exchange: (count, batch, rows, nlon, D)."""
+        key = (kind, count, other, rows, tuple(like.shape), like.dtype)
+        buf = self._buffers.get(key)
+        if buf is None:
+            buf = torch.empty((count, like.shape[0], rows[1] - rows[0], *like.shape[2:]), dtype=like.dtype, device=like.device)
+            self._buffers[key] = buf
+        return buf
 
     @staticmethod
     def _slabs(field: Tensor, r0: int, r1: int):
@@ -290,24 +284,90 @@ class NativeHaloExchanger:
         base = field.data_ptr()
         return [(base + b * sample_bytes + r0 * row_bytes, (r1 - r0) * row_bytes) for b in range(field.shape[0])]
 
-    def _fill_ops(self, fields: tuple[Tensor, ...]) -> tuple:
-        def build():
-            ops = []
-            for other, theirs, mine in self.peers:
-                for f in fields:
-                    if theirs is not None:
-                        ops += [(other, 1, ptr, n) for ptr, n in self._slabs(f, *self._local(theirs))]
-                    if mine is not None:
-                        ops += [(other, 0, ptr, n) for ptr, n in self._slabs(f, *self._local(mine))]
-            return ops
-        return self._ops(("fill", *(f.data_ptr() for f in fields), tuple(fields[0].shape), fields[0].dtype), build)
+    def _plan(self, kind: str, fields: tuple[Tensor, ...]) -> tuple:
+        """ctypes arguments of an exchange, cached by the fields' addresses and shape: (moves before, messages, moves
+        after).  A move is the argument tuple of ``gm_halo_move`` up to the stream; the messages are the arrays of
+        ``gm_halo_exchange``.  ``kind``: "fill" sends the rows neighbours need of MY rows and receives my halo rows;
+        "reduce" sends my halo rows' sums and receives, into buffers, the sums neighbours formed for my rows."""
+        key = (kind, self.packed, *(f.data_ptr() for f in fields), tuple(fields[0].shape), fields[0].dtype)
+        hit = self._plans.get(key)
+        if hit is not None:
+            return hit
+        like, count = fields[0], len(fields)
+        row_bytes = like.shape[2] * like.shape[3] * like.element_size()
+        sample_bytes = like.shape[1] * row_bytes
+        code = self._lib.dtype_code(like.dtype) if like.dtype in (torch.float32, torch.bfloat16) else 0
+
+        def move(mode: int, rows: tuple[int, int], buf: Tensor) -> tuple:
+            r0, r1 = self._local(rows)
+            bases = (ctypes.c_void_p * count)(*[f.data_ptr() + r0 * row_bytes for f in fields])
+            return (mode, bases, count, like.shape[0], (r1 - r0) * row_bytes, sample_bytes, buf.data_ptr(), code)
+
+        before, after, ops = [], [], []
+        for other, theirs, mine in self.peers:
+            outgoing, incoming = (theirs, mine) if kind == "fill" else (mine, theirs)
+            if outgoing is not None:
+                if self.packed:
+                    buf = self._buffer("send", like, count, other, outgoing)
+                    before.append(move(0, outgoing, buf))
+                    ops.append((other, 1, buf.data_ptr(), buf.numel() * buf.element_size()))
+                else:
+                    for f in fields:
+                        ops += [(other, 1, ptr, n) for ptr, n in self._slabs(f, *self._local(outgoing))]
+            if incoming is not None:
+                if self.packed or kind == "reduce":
+                    buf = self._buffer("recv", like, count, other, incoming)
+                    after.append(move(1 if kind == "fill" else 2, incoming, buf))
+                if self.packed:
+                    ops.append((other, 0, buf.data_ptr(), buf.numel() * buf.element_size()))
+                elif kind == "fill":
+                    for f in fields:
+                        ops += [(other, 0, ptr, n) for ptr, n in self._slabs(f, *self._local(incoming))]
+                else:
+                    slab = buf[0, 0].numel() * buf.element_size()
+                    ops += [(other, 0, buf[slot, b].data_ptr(), slab) for slot in range(count) for b in range(buf.shape[1])]
+        n = len(ops)
+        messages = (n, (ctypes.c_int * n)(*[o[0] for o in ops]), (ctypes.c_int * n)(*[o[1] for o in ops]),
+                    (ctypes.c_void_p * n)(*[o[2] for o in ops]), (ctypes.c_int64 * n)(*[o[3] for o in ops]))
+        if len(self._plans) > 64:
+            self._plans.clear()
+        hit = self._plans[key] = (before, messages, after)
+        return hit
+
+    def _check(self, fields: tuple[Tensor, ...]) -> None:
+        if len(fields) > 4:
+            raise RuntimeError("at most four fields per halo exchange")
+        for f in fields:
+            if not f.is_contiguous() or f.shape != fields[0].shape or f.dtype != fields[0].dtype:
+                raise RuntimeError("halo exchange needs contiguous (batch, rows, nlon, D) fields of one shape and dtype")
+
+    def _send(self, plan: tuple, stream: torch.cuda.Stream) -> None:
+        before, (n, peers, sends, pointers, nbytes), _ = plan
+        with torch.cuda.device(self.device):
+            for args in before:
+                self._lib.call("gm_halo_move", *args, stream.cuda_stream)
+            self._lib.call("gm_halo_exchange", self.comm, n, peers, sends, pointers, nbytes, stream.cuda_stream)
+
+    def _land(self, plan: tuple, stream: torch.cuda.Stream) -> None:
+        with torch.cuda.device(self.device):
+            for args in plan[2]:
+                self._lib.call("gm_halo_move", *args, stream.cuda_stream)
+
+    def _zero_halo(self, grads: tuple[Tensor, ...], stream: torch.cuda.Stream) -> None:
+        with torch.cuda.stream(stream):
+            for g in grads:
+                if self.lo > self.elo:
+                    g[:, : self.lo - self.elo].zero_()
+                if self.ehi > self.hi:
+                    g[:, self.hi - self.elo:].zero_()
 
     def fill_halos(self, *fields: Tensor, stream: torch.cuda.Stream | None = None) -> None:
         """Forward exchange on the current stream: every field's halo rows receive the owners' rows."""
-        for f in fields:
-            if not f.is_contiguous():
-                raise RuntimeError("halo exchange needs contiguous (batch, rows, nlon, D) fields")
-        self._exchange(self._fill_ops(fields), stream or torch.cuda.current_stream(self.device))
+        self._check(fields)
+        stream = stream or torch.cuda.current_stream(self.device)
+        plan = self._plan("fill", fields)
+        self._send(plan, stream)
+        self._land(plan, stream)
 
     def start_fill(self, *fields: Tensor):
         """The forward exchange on a side stream: work that does not read the halo rows can be launched on the current
@@ -321,72 +381,35 @@ class NativeHaloExchanger:
     def finish_fill(self, done) -> None:
         torch.cuda.current_stream(self.device).wait_event(done)
 
-    def _recv_buffer(self, like: Tensor, count: int, other: int, rows: tuple[int, int]) -> Tensor:
-        key = (count, other, rows, tuple(like.shape), like.dtype)
-        buf = self._staging.get(key)
-        if buf is None:
-            buf = torch.empty((count, like.shape[0], rows[1] - rows[0], *like.shape[2:]), dtype=like.dtype, device=like.device)
-            self._staging[key] = buf
-        return buf
-
-    def _reduce_ops(self, grads: tuple[Tensor, ...]) -> tuple:
-        """Sends per (field, sample) slab of the halo rows; receives per (field, sample) slab of one staging buffer per
-        peer: both sides post the same messages in the same order."""
-        def build():
-            ops = []
-            for other, theirs, mine in self.peers:
-                if mine is not None:  # halo rows I hold partial sums for: they belong to `other`
-                    for g in grads:
-                        ops += [(other, 1, ptr, n) for ptr, n in self._slabs(g, *self._local(mine))]
-                if theirs is not None:  # rows of mine `other` holds partial sums for
-                    buf = self._recv_buffer(grads[0], len(grads), other, theirs)
-                    slab = buf[0, 0].numel() * buf.element_size()
-                    for slot in range(len(grads)):
-                        ops += [(other, 0, buf[slot, b].data_ptr(), slab) for b in range(buf.shape[1])]
-            return ops
-        return self._ops(("reduce", *(g.data_ptr() for g in grads), tuple(grads[0].shape), grads[0].dtype), build)
-
-    def _land(self, grads: tuple[Tensor, ...], stream: torch.cuda.Stream, zero_halo: bool) -> None:
-        """Add the received partial sums to this rank's rows (one launch per peer and field); zero the halo rows."""
-        code = self._lib.dtype_code(grads[0].dtype)
-        row_elems = grads[0].shape[2] * grads[0].shape[3]
-        with torch.cuda.device(self.device), torch.cuda.stream(stream):
-            for other, theirs, _ in self.peers:
-                if theirs is None:
-                    continue
-                buf = self._recv_buffer(grads[0], len(grads), other, theirs)
-                r0, r1 = self._local(theirs)
-                for slot, g in enumerate(grads):
-                    self._lib.call("gm_halo_accumulate", g.data_ptr() + r0 * row_elems * g.element_size(), buf[slot].data_ptr(), g.shape[0],
-                                   (r1 - r0) * row_elems, g.shape[1] * row_elems, (r1 - r0) * row_elems, code, stream.cuda_stream)
-            if zero_halo:
-                for g in grads:
-                    if self.lo > self.elo:
-                        g[:, : self.lo - self.elo].zero_()
-                    if self.ehi > self.hi:
-                        g[:, self.hi - self.elo:].zero_()
-
     def reduce_halos(self, *grads: Tensor, zero_halo: bool = True) -> None:
         """Backward exchange on the current stream: the partial sums this rank formed for other ranks' rows go to
         their owners, the sums others formed for this rank's rows are added in, the halo rows are zeroed."""
+        self._check(grads)
         stream = torch.cuda.current_stream(self.device)
-        self._exchange(self._reduce_ops(grads), stream)
-        self._land(grads, stream, zero_halo)
+        plan = self._plan("reduce", grads)
+        self._send(plan, stream)
+        self._land(plan, stream)
+        if zero_halo:
+            self._zero_halo(grads, stream)
 
     def start_reduce(self, *grads: Tensor):
         """The backward exchange on a side stream.  The halo rows' sums must be final on the current stream; the rank's
         own rows may still be written until :meth:`finish_reduce`, which adds the received sums on the current stream."""
+        self._check(grads)
         self.side.wait_stream(torch.cuda.current_stream(self.device))
-        self._exchange(self._reduce_ops(grads), self.side)
+        plan = self._plan("reduce", grads)
+        self._send(plan, self.side)
         done = torch.cuda.Event()
         done.record(self.side)
-        return done, grads
+        return done, grads, plan
 
     def finish_reduce(self, handle, zero_halo: bool = True) -> None:
-        done, grads = handle
+        done, grads, plan = handle
         stream = torch.cuda.current_stream(self.device)
         stream.wait_event(done)
-        self._land(grads, stream, zero_halo)
+        self._land(plan, stream)
+        if zero_halo:
+            self._zero_halo(grads, stream)
 
 
 @dataclass(frozen=True)

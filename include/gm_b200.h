@@ -397,6 +397,47 @@ int gm_halo_accumulate(void* dst, const void* src, int64_t slabs, int64_t slab_e
 int gm_halo_move(int mode, void* const* fields, int n_fields, int64_t batch, int64_t slab_bytes, int64_t sample_bytes, void* packed,
                  int dtype, void* stream);
 
+/* ---------------------------------------------------------------------------
+ * Depthwise steerable convolution on a longitude-symmetric lattice with the
+ * per-edge coefficient stream of gm_conv_forward replaced by a table per
+ * (target row, source row, longitude offset).
+ *
+ * Replaces, for lattices, the reference's depthwise op fed by its per-edge radial
+ * network: nn/depthwise.py:206-238 (stacked_coefficients) ->
+ * nn/fused_attention.py:309-321 (forward_depthwise) -> nn/fused/attention.h:174-206,
+ * 265-287.  The caller folds every entry's coefficients, transport phase,
+ * (r/c)^{2n} e^{2 i n phi} and aggregation weight into
+ *   table (entries, table_width) float32:  one factor per scalar channel (padded
+ *   to a multiple of 4 columns), then per complex copy the row-major 2 x 2 matrix
+ *   of  z -> w (A tau z + omega B conj(tau z))  acting on (re z, im z)
+ * (gm_attention_b200/nn/lattice_depthwise.py: fold).  Windows as in
+ * gm_lattice_attention_forward: win_cnt / win_lo / win_off (rows, 2 * halo + 1),
+ * win_off counting table entries.
+ *
+ *   items (n_items, 3) int32: kind (0: complex copy, 1: two scalar channels), the
+ *       item's first column in the field (even), its first column in the table.
+ *   x, y: (batch, rows * nlon, width) GM_F32 or GM_BF16 (fp32 arithmetic); nlon a
+ *       multiple of 8; width even.
+ *
+ * gm_lattice_conv_apply: y[target] = sum over the target's entries of
+ *   table[entry] x[source], for the target rows listed in order[0 .. n_order)
+ *   (other rows of y are left untouched).  transpose != 0 applies the transposed
+ *   matrices: with the transposed windows and the table gathered into their entry
+ *   order this is the gradient with respect to x.  Only true neighbours are read.
+ * gm_lattice_conv_table_grad: dtable[entry] = sum over the longitudes and samples
+ *   of g[target] (x) x[source]  (scalar channels: the products; complex copies:
+ *   the 2 x 2 outer product).  blocks (n_blocks, 2) int32 = (window index =
+ *   target row * (2 * halo + 1) + source row - target row + halo, first offset):
+ *   8 consecutive offsets per block; entries no block covers are left untouched.
+ * No atomics: results do not depend on the launch geometry.
+ * ------------------------------------------------------------------------ */
+int gm_lattice_conv_apply(const void* x, const float* table, const int32_t* items, int n_items, const int32_t* win_cnt,
+                          const int32_t* win_lo, const int32_t* win_off, const int32_t* order, int n_order, int rows, int nlon,
+                          int batch, int width, int halo, int table_width, int transpose, int dtype, void* y, void* stream);
+int gm_lattice_conv_table_grad(const void* g, const void* x, const int32_t* items, int n_items, const int32_t* win_cnt,
+                               const int32_t* win_lo, const int32_t* win_off, const int32_t* blocks, int64_t n_blocks, int rows,
+                               int nlon, int batch, int width, int halo, int table_width, int dtype, float* dtable, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -46,6 +46,12 @@ class Sample:
     bias: np.ndarray
     inside: np.ndarray
     n_edges: int
+    # the depthwise op's per-edge constants (nn/fused_attention.py:213-222): geodesic distance, (cos, sin)(k phi) for
+    # k <= max_frequency, window value and tangent quadrature weight
+    distances: np.ndarray | None = None
+    angular: np.ndarray | None = None
+    window: np.ndarray | None = None
+    quadrature: np.ndarray | None = None
 
     def position(self, original: np.ndarray) -> np.ndarray:
         return np.searchsorted(self.nodes, original)
@@ -99,8 +105,9 @@ def sample_problem(lat: G.Lattice, radius: float, targets, sources, max_frequenc
     win = _window(e.distances, radius, window)
     bias = (np.log(np.maximum(win, tiny)) + np.log(np.maximum(e.tangent_quadrature_weights, tiny))).astype(dtype)
     transport = np.ascontiguousarray(np.stack([e.transport_phases.real, e.transport_phases.imag], -1).astype(dtype))
+    angular = np.ascontiguousarray(np.stack([e.angular_phases.real, e.angular_phases.imag], -1).astype(dtype))
     return Sample(nodes, targets, sources, e.row_ptr, e.source_index.copy(), transport, bias, (win > 0).astype(np.uint8),
-                  int(e.n_edges))
+                  int(e.n_edges), e.distances.astype(dtype), angular, win.astype(dtype), e.tangent_quadrature_weights.astype(dtype))
 
 
 def run(sample: Sample, gather: Callable[[np.ndarray], tuple[np.ndarray, np.ndarray, np.ndarray, np.ndarray]], desc: np.ndarray,
@@ -114,6 +121,23 @@ def run(sample: Sample, gather: Callable[[np.ndarray], tuple[np.ndarray, np.ndar
     dq, dk, dv = O.attention_backward(g, q, k, v, *args)
     tp, sp = sample.position(sample.targets), sample.position(sample.sources)
     return {"out": out[tp], "dq": dq[tp], "dk": dk[sp], "dv": dv[sp]}
+
+
+def run_conv(sample: Sample, v: np.ndarray, g: np.ndarray, rc: np.ndarray, cc: np.ndarray, desc: np.ndarray, cutoff: float,
+             a0: int, w: int) -> dict[str, np.ndarray]:
+    """The depthwise op (``nn/fused/attention.h:174-232, 265-287``) on the reduced graph: ``v`` / ``g`` rows of ONE sample on
+    ``sample.nodes``, ``rc (E, a0)`` / ``cc (E, w)`` per reduced edge, aggregation weight = window x tangent quadrature
+    weight.  Returns ``out`` on the targets, ``dv`` on the sources and the per-edge ``drc`` / ``dcc`` (edges of complete
+    rows only carry meaning; ``g`` must be zero on the rows of incomplete targets for ``dv`` to be exact -- it is, for
+    those rows have no edges here)."""
+    dt = v.dtype.type
+    args = (np.ascontiguousarray(rc[None]), np.ascontiguousarray(cc[None]), sample.transport, sample.angular,
+            (sample.distances / dt(cutoff)).astype(dt), (sample.window * sample.quadrature).astype(dt), np.asarray(desc, np.int64),
+            sample.row_ptr, sample.source_index, a0, w)
+    out = O.conv_forward(np.ascontiguousarray(v), *args)
+    dv, drc, dcc = O.conv_backward(np.ascontiguousarray(g), np.ascontiguousarray(v), *args)
+    tp, sp = sample.position(sample.targets), sample.position(sample.sources)
+    return {"out": out[tp], "dv": dv[sp], "drc": drc.reshape(-1, a0), "dcc": dcc.reshape(-1, w)}
 
 
 def default_sample_nodes(nlat: int, nlon: int, row_lo: int = 0, row_hi: int | None = None,

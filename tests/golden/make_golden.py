@@ -20,7 +20,10 @@ no JIT).  Outputs are small ``.npz`` files:
 * ``attention_<case>.npz``        -- seeded inputs, ``Softmax`` alpha, the fused
   layer's output (reference fused Softmax + eager transport / segment sum) and
   the gradients autograd returns for ``q, k, v``;
-* ``plans.npz``                   -- descriptor rows of the reference planner.
+* ``plans.npz``                   -- descriptor rows of the reference planner;
+* ``depthwise_<case>.npz``        -- a depthwise ``SO2Convolution`` (radial network included) on a small lattice through
+  the reference's eager path: its parameters, the per-edge coefficients of ``stacked_coefficients``, a seeded field and
+  output gradient, the output, and autograd's gradients for the field and every parameter.
 """
 
 from __future__ import annotations
@@ -43,6 +46,8 @@ sys.path.insert(0, str(REPO))
 from gm_attention.discretization.edge_geometry import compute_edge_geometry  # noqa: E402
 from gm_attention.nn import fused_attention as ref_fa  # noqa: E402
 from gm_attention.nn._scatter import gather_to_edges, scatter_add_to_nodes  # noqa: E402
+from gm_attention.nn.convolution import SO2Convolution  # noqa: E402
+from gm_attention.nn.depthwise import stacked_coefficients  # noqa: E402
 from gm_attention.nn.kernels import transport_field  # noqa: E402
 from gm_attention.representations.field_type import SO2FeatureField, SO2FieldType  # noqa: E402
 
@@ -133,11 +138,40 @@ def dump_plans() -> None:
                         summary=np.array([plan.heads, plan.width, plan.a_0, plan.complex_width, plan.max_order], np.int64))
 
 
+def depthwise_case(name: str, nlat: int, nlon: int, radius: float, types: dict[int, int], normalize: bool, seed: int) -> None:
+    """nn/convolution.py:297-356 with depthwise=True through the eager path (GM_FUSED_ATTENTION off)."""
+    dtype = torch.float64
+    edges = reference_edges(nlat, nlon, radius, dtype)
+    field_type = SO2FieldType(types)
+    torch.manual_seed(seed)
+    conv = SO2Convolution(field_type, field_type, cutoff=radius, window="hard", depthwise=True, normalize=normalize, n_radial_basis=4,
+                          radial_hidden_features=(16,), dtype=dtype)
+    gen = torch.Generator().manual_seed(seed + 100)
+    n = nlat * nlon
+    flat = torch.randn(n, field_type.dimension, generator=gen, dtype=dtype).requires_grad_(True)
+    dout = torch.randn(n, field_type.dimension, generator=gen, dtype=dtype)
+    mode, ref_fa.MODE = ref_fa.MODE, "0"
+    try:
+        out = conv(SO2FeatureField.from_flat(field_type, flat), edges).to_flat()
+        out.backward(dout)
+        rc, cc = stacked_coefficients([conv.kernel], edges)
+    finally:
+        ref_fa.MODE = mode
+    params = {k.replace(".", "__"): v.detach().numpy() for k, v in conv.kernel.named_parameters()}
+    grads = {"grad__" + k.replace(".", "__"): v.grad.numpy() for k, v in conv.kernel.named_parameters()}
+    np.savez_compressed(HERE / f"depthwise_{name}.npz", nlat=nlat, nlon=nlon, radius=radius, normalize=int(normalize),
+                        types=np.array(sorted(types.items()), np.int64), v=flat.detach().numpy(), dout=dout.numpy(), out=out.detach().numpy(),
+                        dv=flat.grad.numpy(), rc=rc[0].detach().numpy(), cc=cc[0].detach().numpy(), distances=edges.distances.numpy(),
+                        **params, **grads)
+
+
 if __name__ == "__main__":
     build_ref.build()
     dump_geometry()
     dump_plans()
     attention_case("f64_hard", 8, 16, 2 * math.pi / 8, {0: 3, 1: 2, 2: 1}, 2, 2, torch.float64, "hard", 0)
     attention_case("f32_quartic", 8, 16, 2.5 * math.pi / 8, {0: 2, 1: 2}, 4, 1, torch.float32, "quartic", 1)
+    depthwise_case("plain", 8, 16, 2 * math.pi / 8, {0: 4, 1: 3, 2: 2}, False, 3)
+    depthwise_case("normalized", 8, 16, 2.5 * math.pi / 8, {0: 2, 1: 2, 2: 2}, True, 4)
     for f in sorted(HERE.glob("*.npz")):
         print(f.name, f.stat().st_size)

@@ -102,3 +102,30 @@ def test_unsupported_head_count_is_a_clear_error():
     q, = seeded((c.n_nodes, c.width), 1, np.float32)
     with pytest.raises(RuntimeError, match="heads must be 1, 2, 4 or 8"):
         attention_forward(cuda(q), cuda(q), cuda(q), tables_for(c, np.float32))
+
+
+@pytest.mark.parametrize("path", ["csr", "lattice_fma"])
+def test_one_infinite_value_reaches_its_neighbours_only(path):
+    """The reference's edge loop (plain float arithmetic, ``nn/fused/attention.h:295-316`` + the eager value path) lets
+    a non-finite value of a node reach exactly the targets that see the node, in that column.  The general kernels and
+    the FMA lattice kernels do the same; the oracle on the same field is the witness.  (The tensor-core lattice kernels
+    do not: they multiply whole tiles by zero weights.)"""
+    from gm_attention_b200.attention import attention_forward, build_lattice_tables, lattice_attention_forward
+
+    c = make_case(12, 24, 3 * math.pi / 12, {0: 4, 1: 4, 2: 4}, 2, dtype=np.float32)
+    q, k, v = seeded((c.n_nodes, c.width), 77, np.float32, 3)
+    node, column = 5 * c.nlon + 23, 6  # a scalar channel of the second head
+    v[node, column] = np.inf
+    want = O.attention_forward(q, k, v, c.transport, c.bias, c.inside, c.desc, c.row_ptr, c.source, c.heads, c.scale, 1)
+    seen_by = np.unique(c.target[c.source == node])
+    assert np.array_equal(np.flatnonzero(~np.isfinite(want).all(1)), seen_by) and np.isfinite(np.delete(want, column, 1)).all()
+    t = tables_for(c, np.float32)
+    if path == "csr":
+        out, _ = attention_forward(cuda(q), cuda(k), cuda(v), t)
+    else:
+        lat = build_lattice_tables(t, c.nlat, c.nlon, t.rows, c.heads, c.scale)
+        out, _ = lattice_attention_forward(cuda(q), cuda(k), cuda(v), lat, tensor_cores=False)
+    out = out.cpu().numpy()
+    assert np.array_equal(np.isfinite(out), np.isfinite(want))
+    finite = np.isfinite(want)
+    assert_close(out[finite], want[finite], 1e-5, 1e-6 * max(1.0, np.abs(want[finite]).max()), "finite entries")
