@@ -56,8 +56,11 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         objects = list(pool.map(lambda s: _compile(s, force, verbose), srcs))
     if LIBRARY.exists() and not force and all(LIBRARY.stat().st_mtime >= o.stat().st_mtime for o in objects):
         return LIBRARY
-    cmd = [NVCC, *ARCH, "-shared", "-o", str(LIBRARY), *map(str, objects), "-lcudart", "-ldl"]
+    # link beside the target and rename: a reader (or a snapshot of the tree) never sees a half-written library
+    partial = LIBRARY.with_suffix(".so.partial")
+    cmd = [NVCC, *ARCH, "-shared", "-o", str(partial), *map(str, objects), "-lcudart", "-ldl"]
     subprocess.run(cmd, check=True)
+    os.replace(partial, LIBRARY)
     return LIBRARY
 
 

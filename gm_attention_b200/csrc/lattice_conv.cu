@@ -41,16 +41,21 @@ struct ConvArgs {
   int n_items, rows, nlon, batch, width, halo, table_width, transpose;
 };
 
+// Two neighbouring elements of a node's row: loaded as one word (bf16) or two (float), unpacked when used, so that a
+// value in flight between its load and its use costs one register per bf16 pair.
 template <typename S> struct Pair;
 template <> struct Pair<float> {
-  static __device__ __forceinline__ float2 load(const float* p) { return __ldg(reinterpret_cast<const float2*>(p)); }
+  using Raw = float2;
+  static __device__ __forceinline__ Raw load(const float* p) { return __ldg(reinterpret_cast<const float2*>(p)); }
+  static __device__ __forceinline__ Raw zero() { return make_float2(0.f, 0.f); }
+  static __device__ __forceinline__ float2 unpack(Raw r) { return r; }
   static __device__ __forceinline__ void store(float* p, float2 v) { *reinterpret_cast<float2*>(p) = v; }
 };
 template <> struct Pair<__nv_bfloat16> {
-  static __device__ __forceinline__ float2 load(const __nv_bfloat16* p) {
-    const unsigned raw = __ldg(reinterpret_cast<const unsigned*>(p));
-    return make_float2(__uint_as_float(raw << 16), __uint_as_float(raw & 0xffff0000u));
-  }
+  using Raw = unsigned;
+  static __device__ __forceinline__ Raw load(const __nv_bfloat16* p) { return __ldg(reinterpret_cast<const unsigned*>(p)); }
+  static __device__ __forceinline__ Raw zero() { return 0u; }
+  static __device__ __forceinline__ float2 unpack(Raw r) { return make_float2(__uint_as_float(r << 16), __uint_as_float(r & 0xffff0000u)); }
   static __device__ __forceinline__ void store(__nv_bfloat16* p, float2 v) {
     *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v.x, v.y);
   }
@@ -89,26 +94,38 @@ __global__ void __launch_bounds__(256) conv_apply_kernel(const ConvArgs a) {
       float4 window[LON];  // window[s % 8] = the matrix of offset s, for the 8 most recent s
 #pragma unroll
       for (int u = 0; u < LON; ++u) window[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      const int steps = cnt + LON - 1;
+      // the matrix of offset s (zero beyond the window) and the sources of step s, loaded one step ahead of their use
+      auto matrix = [&](int s) {
+        if (s >= cnt) return make_float4(0.f, 0.f, 0.f, 0.f);
+        const float* f = table + (size_t)s * a.table_width;
+        if (kind == 0) {
+          const float4 m = __ldg(reinterpret_cast<const float4*>(f));
+          return a.transpose ? make_float4(m.x, m.z, m.y, m.w) : m;
+        }
+        const float2 m = __ldg(reinterpret_cast<const float2*>(f));
+        return make_float4(m.x, 0.f, 0.f, m.y);
+      };
+      typename Pair<S>::Raw next_v[NB];
+      float4 next_m = matrix(0);
+#pragma unroll
+      for (int b = 0; b < NB; ++b) next_v[b] = b < nb ? Pair<S>::load(xrow + b * sample + (size_t)p * a.width) : Pair<S>::zero();
       // step s brings the source at longitude l0 + lo + s; the target l of the block sees it under offset d = s - l
-      for (int s0 = 0; s0 < cnt + LON - 1; s0 += LON) {
+      for (int s0 = 0; s0 < steps; s0 += LON) {
 #pragma unroll
         for (int u = 0; u < LON; ++u) {
           const int s = s0 + u;
-          if (s >= cnt + LON - 1) break;
-          if (s < cnt) {
-            const float* f = table + (size_t)s * a.table_width;
-            if (kind == 0) {
-              const float4 m = __ldg(reinterpret_cast<const float4*>(f));
-              window[u] = a.transpose ? make_float4(m.x, m.z, m.y, m.w) : m;
-            } else {
-              const float2 m = __ldg(reinterpret_cast<const float2*>(f));
-              window[u] = make_float4(m.x, 0.f, 0.f, m.y);
-            }
-          }
+          if (s >= steps) break;
+          window[u] = next_m;
           float2 v[NB];
 #pragma unroll
-          for (int b = 0; b < NB; ++b) v[b] = b < nb ? Pair<S>::load(xrow + b * sample + (size_t)p * a.width) : make_float2(0.f, 0.f);
+          for (int b = 0; b < NB; ++b) v[b] = Pair<S>::unpack(next_v[b]);
           p = p + 1 == a.nlon ? 0 : p + 1;
+          if (s + 1 < steps) {
+            next_m = matrix(s + 1);
+#pragma unroll
+            for (int b = 0; b < NB; ++b) next_v[b] = b < nb ? Pair<S>::load(xrow + b * sample + (size_t)p * a.width) : Pair<S>::zero();
+          }
 #pragma unroll
           for (int l = 0; l < LON; ++l) {
             const int d = s - l;
@@ -168,19 +185,33 @@ __global__ void __launch_bounds__(256) conv_table_grad_kernel(const ConvArgs a) 
       for (int t = 1; t < LON; ++t)  // targets -7 .. -1 (cyclic) are seen by the first steps
 #pragma unroll
         for (int b = 0; b < NB; ++b)
-          window[(LON - t) & (LON - 1)][b] = b < nb ? Pair<S>::load(grow + b * sample + (size_t)(a.nlon - t) * a.width) : make_float2(0.f, 0.f);
+          window[(LON - t) & (LON - 1)][b] = b < nb ? Pair<S>::unpack(Pair<S>::load(grow + b * sample + (size_t)(a.nlon - t) * a.width)) : make_float2(0.f, 0.f);
       int p = (lo + d0) % a.nlon;
       if (p < 0) p += a.nlon;
+      // the source and the target of step u, loaded one step ahead of their use
+      typename Pair<S>::Raw next_v[NB], next_g[NB];
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        next_v[b] = b < nb ? Pair<S>::load(xrow + b * sample + (size_t)p * a.width) : Pair<S>::zero();
+        next_g[b] = b < nb ? Pair<S>::load(grow + b * sample) : Pair<S>::zero();
+      }
       for (int u0 = 0; u0 < a.nlon; u0 += LON) {  // nlon is a multiple of 8 (checked by the host)
 #pragma unroll
         for (int u = 0; u < LON; ++u) {
           float2 v[NB];
 #pragma unroll
           for (int b = 0; b < NB; ++b) {
-            v[b] = b < nb ? Pair<S>::load(xrow + b * sample + (size_t)p * a.width) : make_float2(0.f, 0.f);
-            window[u][b] = b < nb ? Pair<S>::load(grow + b * sample + (size_t)(u0 + u) * a.width) : make_float2(0.f, 0.f);
+            v[b] = Pair<S>::unpack(next_v[b]);
+            window[u][b] = Pair<S>::unpack(next_g[b]);
           }
           p = p + 1 == a.nlon ? 0 : p + 1;
+          if (u0 + u + 1 < a.nlon) {
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+              next_v[b] = b < nb ? Pair<S>::load(xrow + b * sample + (size_t)p * a.width) : Pair<S>::zero();
+              next_g[b] = b < nb ? Pair<S>::load(grow + b * sample + (size_t)(u0 + u + 1) * a.width) : Pair<S>::zero();
+            }
+          }
 #pragma unroll
           for (int k = 0; k < LON; ++k) {
             if (k >= valid) break;  // offsets beyond the window: their pairs are not edges

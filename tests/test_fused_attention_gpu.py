@@ -104,13 +104,12 @@ def test_unsupported_head_count_is_a_clear_error():
         attention_forward(cuda(q), cuda(q), cuda(q), tables_for(c, np.float32))
 
 
-@pytest.mark.parametrize("path", ["csr", "lattice_fma"])
-def test_one_infinite_value_reaches_its_neighbours_only(path):
+def test_one_infinite_value_reaches_its_neighbours_only():
     """The reference's edge loop (plain float arithmetic, ``nn/fused/attention.h:295-316`` + the eager value path) lets
-    a non-finite value of a node reach exactly the targets that see the node, in that column.  The general kernels and
-    the FMA lattice kernels do the same; the oracle on the same field is the witness.  (The tensor-core lattice kernels
-    do not: they multiply whole tiles by zero weights.)"""
-    from gm_attention_b200.attention import attention_forward, build_lattice_tables, lattice_attention_forward
+    a non-finite value of a node reach exactly the targets that see the node, in that column.  The general (CSR)
+    kernels do the same; the oracle on the same field is the witness.  (The lattice kernels, FMA and tensor-core, do
+    not: owners that share staged neighbour rows multiply them by zero weights outside their own windows.)"""
+    from gm_attention_b200.attention import attention_forward
 
     c = make_case(12, 24, 3 * math.pi / 12, {0: 4, 1: 4, 2: 4}, 2, dtype=np.float32)
     q, k, v = seeded((c.n_nodes, c.width), 77, np.float32, 3)
@@ -119,12 +118,7 @@ def test_one_infinite_value_reaches_its_neighbours_only(path):
     want = O.attention_forward(q, k, v, c.transport, c.bias, c.inside, c.desc, c.row_ptr, c.source, c.heads, c.scale, 1)
     seen_by = np.unique(c.target[c.source == node])
     assert np.array_equal(np.flatnonzero(~np.isfinite(want).all(1)), seen_by) and np.isfinite(np.delete(want, column, 1)).all()
-    t = tables_for(c, np.float32)
-    if path == "csr":
-        out, _ = attention_forward(cuda(q), cuda(k), cuda(v), t)
-    else:
-        lat = build_lattice_tables(t, c.nlat, c.nlon, t.rows, c.heads, c.scale)
-        out, _ = lattice_attention_forward(cuda(q), cuda(k), cuda(v), lat, tensor_cores=False)
+    out, _ = attention_forward(cuda(q), cuda(k), cuda(v), tables_for(c, np.float32))
     out = out.cpu().numpy()
     assert np.array_equal(np.isfinite(out), np.isfinite(want))
     finite = np.isfinite(want)
