@@ -68,12 +68,16 @@ def parse() -> argparse.Namespace:
     p.add_argument("--overlap", action="store_true",
                    help="N > 1: run the layer around the halo exchange (interior rows while the halos travel) instead of exchanging "
                         "before / after it; measured equal within 1 %% at N = 8 (the exchange is latency, not bandwidth), so off by default")
-    p.add_argument("--halo", choices=["native", "native-slabs", "torch"], default="native",
-                   help="N > 1: native = the library's own NCCL groups issued from C (default); torch = torch.distributed point-to-point with staging buffers")
+    p.add_argument("--halo", choices=["auto", "peer", "native", "native-slabs", "torch"], default="auto",
+                   help="N > 1: peer = the library's own copy kernels storing into the neighbour's mapped buffer (needs GPUs that can map each "
+                        "other's memory); native = the library's NCCL groups issued from C, one packed message per neighbour and direction "
+                        "(native-slabs: one message per field and sample); torch = torch.distributed point-to-point with staging buffers; "
+                        "auto (default) = peer where it can be set up, else native")
     p.add_argument("--per-rank", action="store_true",
                    help="every rank prints its own per-step timings (halo exchange in, forward, backward, halo sums out) to stderr")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--no-extra", action="store_true", help="skip the op-level and depthwise measurements the default run appends under \"extra\"")
     p.add_argument("--no-parity", action="store_true", help="skip the oracle check of the step's results (for profiler captures)")
     return p.parse_args()
 
@@ -253,7 +257,7 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
     from gm_attention_b200.fields import FieldType
     from gm_attention_b200.geometry import midpoint_lattice
     from gm_attention_b200.nn import fused_attention as fa
-    from gm_attention_b200.parallel import (BandPlan, HaloExchanger, NativeHaloExchanger, band_geometry, overlap_tables, row_degrees,
+    from gm_attention_b200.parallel import (BandPlan, HaloExchanger, NativeHaloExchanger, PeerHaloExchanger, band_geometry, overlap_tables, row_degrees,
                                             row_pair_counts, tensor_core_row_cost)
 
     _lib.lib()
@@ -326,10 +330,30 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
     q, k, v, g = (h.to(device, non_blocking=True) for h in host)
     flat = lambda t: t.view(batch * n_ext, D)
     # the library's own NCCL groups (sends / receives in place, nothing on the host); --halo torch: torch.distributed with staging
-    halo = None
-    if world > 1:
-        halo = NativeHaloExchanger(plan, rank, device, packed=args.halo == "native") if args.halo != "torch" else HaloExchanger(plan, rank)
-    reduce_kw = {"zero_halo": False} if args.halo != "torch" else {}  # the halo rows of dk / dv are not part of the rank's result
+    halo_kind = args.halo
+
+    def make_halo(band_plan, probe):
+        """The exchanger --halo names; "auto" and "peer" try the peer-memory path on `probe` (two fields of the shape the
+        exchanger will serve: set-up is collective and happens at the first exchange) and fall back to NCCL together."""
+        nonlocal halo_kind
+        if halo_kind in ("auto", "peer"):
+            candidate = PeerHaloExchanger(band_plan, rank, device)
+            try:
+                candidate.fill_halos(*probe)
+                halo_kind = "peer"
+                return candidate
+            except RuntimeError as exc:
+                if args.halo == "peer":
+                    raise
+                if rank == 0:
+                    print(json.dumps({"note": f"peer-memory halo exchange unavailable, using NCCL: {exc}"}), file=sys.stderr, flush=True)
+                halo_kind = "native"
+        if halo_kind == "torch":
+            return HaloExchanger(band_plan, rank)
+        return NativeHaloExchanger(band_plan, rank, device, packed=halo_kind != "native-slabs")
+
+    halo = make_halo(plan, (k, v)) if world > 1 else None
+    reduce_kw = {"zero_halo": False} if halo_kind != "torch" else {}  # the halo rows of dk / dv are not part of the rank's result
     fwd_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     bwd_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
 
@@ -457,11 +481,14 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
     gpu_uuid = getattr(torch.cuda.get_device_properties(local), "uuid", None)
     with ClockSampler(local, f"GPU-{gpu_uuid}" if gpu_uuid is not None else None) as clocks:
         barrier()  # the samplers start at different times on different ranks: line the ranks up again before the clock starts
+        calls_before = dict(_lib.CALLS)
         start.record()
         for s in range(args.steps):
             step(s)
         stop.record()
         barrier()
+    # this rank's own halo kernels inside the timed region (pack / unpack / add, or the peer-memory send / landing)
+    halo_launches = sum(_lib.CALLS[n] - calls_before.get(n, 0) for n in ("gm_halo_move", "gm_halo_accumulate", "gm_peer_send", "gm_peer_land"))
     ms_total = start.elapsed_time(stop)
     if world > 1:
         t = torch.tensor([ms_total], device=device)
@@ -555,8 +582,9 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
                 geo2 = fa.geometry(edges2, radius, "hard", torch.float32)
                 gen2 = AttentionTables(geo2.transport, geo2.bias, geo2.inside, geo2.row_ptr, geo2.source, p.rows, heads, 1.0 / math.sqrt(attn.dimension))
                 e_tables = build_lattice_tables(gen2, e2e_rows, nlon, p.rows, heads, gen2.scale)
-                e_halo = NativeHaloExchanger(plan2, rank, device, packed=args.halo == "native") if args.halo != "torch" else HaloExchanger(plan2, rank)
                 shape2 = (batch, e2e_rows, nlon, D)
+                probe2 = [torch.zeros((1, e2e_rows, nlon, D), dtype=dtype, device=device) for _ in range(2)]  # the pipeline exchanges per one-sample chunk
+                e_halo = make_halo(plan2, probe2)
                 e_host = [torch.empty(shape2, dtype=dtype).pin_memory() for _ in range(4)]
                 for r in range(lo2, hi2):
                     block = row_fields(r)
@@ -622,6 +650,10 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
         print(json.dumps({"error": "a wait on a copy barrier ran out inside the tensor-core lattice kernels: no number is reported", "rank": rank}),
               file=sys.stderr, flush=True)
         sys.exit(4)
+    if isinstance(halo, PeerHaloExchanger) and halo.error():
+        print(json.dumps({"error": "a bounded wait of the peer-memory halo exchange ran out: no number is reported", "rank": rank, "code": halo.error()}),
+              file=sys.stderr, flush=True)
+        sys.exit(5)
     if rank == 0:
         n_rows = batch * n_ext
         bwd_bytes = top_bytes if top_bytes is not None else 8 * n_rows * D * elem + n_rows * heads * 4
@@ -636,10 +668,11 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
                          "algorithmic_bytes_per_launch": bwd_bytes, "launch_ms": top_ms, "passes_ms": per_pass},
             "layer": {"fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "algorithmic_bytes": layer_bytes,
                       "hbm_frac": layer_bytes / ((fwd_ms + bwd_ms) * 1e-3) / 1e9 / peak, "edges": total_edges},
-            "gpu_launches": args.steps * launches,
+            "gpu_launches": args.steps * launches + halo_launches,
             "clocks": clocks.summary(),
             "e2e": e2e,
             "tma_wait_expired": expired.value,
+            "halo_exchange": None if world == 1 else {"kind": halo_kind, "own_kernel_launches_rank0": halo_launches, "overlapped_with_layer": split is not None},
             "other_dtypes": f32_line,
         }
         line["parity"] = parity
@@ -651,12 +684,26 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
             line["cpu_baseline"] = {"value": res["value"], "unit": "edges/s", "cores": pool.info["workers"], "kind": pool.info["kind"],
                                     "sample": cpu_sample_text(cfg, pool.info, 1), "seconds": res["seconds"],
                                     "pure_pytorch_path": "unavailable on this box: the reference's Python package is not present on the benchmark host"}
+        if world == 1 and args.workload == "headline" and not args.no_extra:
+            # the other entry points of the library, measured in the same run: every op-level drop-in (128 x 256, fp32) and the
+            # depthwise convolution with its radial network (256 x 512, radius 4 pi / 256, batch 4); a failure there is recorded,
+            # it does not take the line away
+            torch.cuda.empty_cache()
+            extra = {}
+            for name, fn in (("ops", run_ops), ("conv", run_conv)):
+                sub = argparse.Namespace(**{**vars(args), "workload": name, "no_e2e": True, "no_cpu_baseline": True, "steps": 5})
+                try:
+                    res = fn(sub, emit=False)
+                    extra[name] = res if name == "ops" else {key: res[key] for key in ("metric", "value", "unit", "ms_per_step", "dtype", "config", "roofline", "parity")}
+                except (Exception, SystemExit) as exc:  # noqa: BLE001
+                    extra[name] = {"error": repr(exc)}
+            line["extra"] = extra
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
 
 
-def run_ops(args: argparse.Namespace) -> None:
+def run_ops(args: argparse.Namespace, emit: bool = True) -> dict:
     """Per-op timings of the drop-in entry points on a 128 x 256 lattice (radius 3 pi / 128, ~3.0 M edges), fp32:
     achieved GB/s of each op's own interface bytes (inputs + outputs, each byte once), CUDA events, 3 warm-up + 10 timed."""
     import numpy as np
@@ -758,11 +805,13 @@ def run_ops(args: argparse.Namespace) -> None:
     gout = torch.view_as_complex(rnd(e, b_, 2))
     timed("pairs_backward", lambda: pext.backward(hidden, weight, bias, u, pre_c, post_c, geo.rho, gout, gu, gh, gk, a_, b_, 1),
           e * (3 * t_ + 6 * a_ + 4 + 1 + 2 * b_ + 2 * a_ * b_) * 4)
-    print(json.dumps({"workload": f"op-level entry points, {nlat}x{nlon} lattice, radius 3pi/{nlat}, {e} edges, fp32", "hbm_peak_GB/s": peak,
-                      "ops": results}))
+    line = {"workload": f"op-level entry points, {nlat}x{nlon} lattice, radius 3pi/{nlat}, {e} edges, fp32", "hbm_peak_GB/s": peak, "ops": results}
+    if emit:
+        print(json.dumps(line))
+    return line
 
 
-def run_conv(args: argparse.Namespace) -> None:
+def run_conv(args: argparse.Namespace, emit: bool = True) -> dict:
     """Depthwise steerable convolution, forward + backward, with its radial network: 256 x 512 lattice, radius 4 pi / 256,
     batch 4, field type 64 x (m = 0, 1, 2) (D = 320, a_0 = 64, W = 512; 22 999 040 edges per sample), radial network of 4
     Gaussians -> 16 -> (64 | 512).  One step = radial network on the table entries, fold, apply, and the backward of all
@@ -922,7 +971,7 @@ def run_conv(args: argparse.Namespace) -> None:
                "sample": f"all {nlon} targets of lattice row {row} of one sample ({whole.n_edges} edges), float32, forward + backward of the depthwise op "
                          f"with per-edge coefficients given (the reference's radial network per edge is NOT timed), {reps} repetitions", "seconds": seconds}
 
-    print(json.dumps({
+    line = {
         "metric": "depthwise-conv fwd+bwd neighbour-edges/sec", "value": total_edges / (ms_step * 1e-3), "unit": "edges/s", "n_gpus": 1,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": args.dtype, "data": "synthetic",
@@ -933,7 +982,10 @@ def run_conv(args: argparse.Namespace) -> None:
                      "traffic": None, "peak_kind": peak_kind, "algorithmic_bytes_per_launch": bytes_of[top], "launch_ms": kernel_ms[top],
                      "kernels_ms": kernel_ms, "fp32_fma_tflops_per_kernel": {k: flops_pass / (ms * 1e-3) / 1e12 for k, ms in kernel_ms.items()},
                      "note": "FMA-bound by construction: 4 multiply-adds per complex copy, edge and sample against ~0.01 B of compulsory traffic"},
-        "gpu_launches": args.steps * 3, "clocks": clocks.summary(), "e2e": e2e, "parity": parity, "cpu_baseline": cpu}))
+        "gpu_launches": args.steps * 3, "clocks": clocks.summary(), "e2e": e2e, "parity": parity, "cpu_baseline": cpu}
+    if emit:
+        print(json.dumps(line))
+    return line
 
 
 def main() -> None:

@@ -7,6 +7,7 @@ falls back to PyTorch or to a CPU implementation.
 
 from __future__ import annotations
 
+import collections
 import ctypes
 import functools
 from pathlib import Path
@@ -55,6 +56,13 @@ SIGNATURES: dict[str, list[Any]] = {
     "gm_halo_move": [_I, _P, _I, _L, _L, _L, _P, _I, _P],
     "gm_lattice_conv_apply": [_P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "gm_lattice_conv_table_grad": [_P, _P, _P, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "gm_peer_alloc": [_L, _P, _P],
+    "gm_peer_free": [_P],
+    "gm_peer_open": [_P, _P],
+    "gm_peer_close": [_P],
+    "gm_peer_send": [_P, _I, _L, _L, _L, _P, _P, _P, _P, ctypes.c_uint32, _P],
+    "gm_peer_land": [_P, _I, _L, _L, _L, _P, _I, _I, _P, _P, _P, ctypes.c_uint32, _P],
+    "gm_peer_error": [_P],
     "gm_attention_backward_static": [_P] * 12 + [_L, _L, _L, _I, _I, _I, _I, _D, _I, _P, _P, _P, _P],
 }
 #: entry points that return a size instead of a status
@@ -106,9 +114,14 @@ def stream(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
+#: calls made per entry point (for callers that report how many kernels they launched)
+CALLS: collections.Counter = collections.Counter()
+
+
 def call(name: str, *args: Any) -> None:
     """Invoke an entry point; a non-zero status becomes ``RuntimeError`` with the library's message."""
     handle = lib()
+    CALLS[name] += 1
     status = getattr(handle, name)(*args)
     if status != 0:
         message = handle.gm_last_error().decode(errors="replace")

@@ -17,7 +17,7 @@
 // Both are FMA-bound, not HBM-bound (4 multiply-adds per complex copy, edge and sample against 0.01 bytes of compulsory
 // traffic), and neither has a contraction over channels, so there is nothing for the tensor cores here.  A thread owns
 // one item -- a complex copy, or a pair of scalar channels -- so a warp reads 32 neighbouring items of a node as one
-// 128-byte line; it keeps 8 longitudes x NB samples of accumulators in registers and slides a window of 8 coefficient
+// 128-byte line; it keeps 8 longitudes x 2 samples of accumulators in registers and slides a window of 8 coefficient
 // entries over the source longitudes, so every loaded value is used for up to 8 x 4 multiply-adds and nothing is staged
 // in shared memory.  Results do not depend on the launch geometry: no atomics.
 #include "common.cuh"
@@ -26,6 +26,7 @@ namespace gmb {
 namespace {
 
 constexpr int LON = 8;  // longitudes (apply) / longitude offsets (table_grad) per thread
+constexpr int THREADS = 160;  // at most; three CTAs per SM (136 registers per thread); more items than threads are looped over
 
 struct ConvArgs {
   const void* x;        // (batch, rows * nlon, width) node field
@@ -63,7 +64,8 @@ template <> struct Pair<__nv_bfloat16> {
 
 // ---------------------------------------------------------------------------------------------------------------- apply
 template <typename S, int NB>
-__global__ void __launch_bounds__(256) conv_apply_kernel(const ConvArgs a) {
+__global__ void __launch_bounds__(THREADS, 3) conv_apply_kernel(const ConvArgs a) {
+  constexpr int PF = 4;  // steps in flight (a power of two <= 8)
   const int row = a.order[blockIdx.y];
   const int l0 = blockIdx.x * LON;
   const int b0 = blockIdx.z * NB;
@@ -106,30 +108,36 @@ __global__ void __launch_bounds__(256) conv_apply_kernel(const ConvArgs a) {
         const float2 m = __ldg(reinterpret_cast<const float2*>(f));
         return make_float4(m.x, 0.f, 0.f, m.y);
       };
-      typename Pair<S>::Raw next_v[NB];
-      float4 next_m = matrix(0);
+      // ring of PF steps in flight: the loads of step s + PF are issued when step s is consumed
+      typename Pair<S>::Raw ring_v[PF][NB];
+      float4 ring_m[PF];
+      int ahead = p;  // longitude of the next step to load
 #pragma unroll
-      for (int b = 0; b < NB; ++b) next_v[b] = b < nb ? Pair<S>::load(xrow + b * sample + (size_t)p * a.width) : Pair<S>::zero();
+      for (int t = 0; t < PF; ++t) {
+        ring_m[t] = matrix(t);
+#pragma unroll
+        for (int b = 0; b < NB; ++b)
+          ring_v[t][b] = (b < nb && t < steps) ? Pair<S>::load(xrow + b * sample + (size_t)ahead * a.width) : Pair<S>::zero();
+        ahead = ahead + 1 == a.nlon ? 0 : ahead + 1;
+      }
       // step s brings the source at longitude l0 + lo + s; the target l of the block sees it under offset d = s - l
       for (int s0 = 0; s0 < steps; s0 += LON) {
 #pragma unroll
         for (int u = 0; u < LON; ++u) {
           const int s = s0 + u;
           if (s >= steps) break;
-          window[u] = next_m;
+          window[u] = ring_m[u % PF];
           float2 v[NB];
 #pragma unroll
-          for (int b = 0; b < NB; ++b) v[b] = Pair<S>::unpack(next_v[b]);
-          p = p + 1 == a.nlon ? 0 : p + 1;
-          if (s + 1 < steps) {
-            next_m = matrix(s + 1);
+          for (int b = 0; b < NB; ++b) v[b] = Pair<S>::unpack(ring_v[u % PF][b]);
+          if (s + PF < steps) {
+            ring_m[u % PF] = matrix(s + PF);
 #pragma unroll
-            for (int b = 0; b < NB; ++b) next_v[b] = b < nb ? Pair<S>::load(xrow + b * sample + (size_t)p * a.width) : Pair<S>::zero();
+            for (int b = 0; b < NB; ++b)
+              ring_v[u % PF][b] = b < nb ? Pair<S>::load(xrow + b * sample + (size_t)ahead * a.width) : Pair<S>::zero();
+            ahead = ahead + 1 == a.nlon ? 0 : ahead + 1;
           }
-#pragma unroll
-          for (int l = 0; l < LON; ++l) {
-            const int d = s - l;
-            if (d < 0 || d >= cnt) continue;  // the same for every thread: only true neighbours are touched
+          auto accumulate = [&](int l) {
             const float4 m = window[(u - l) & (LON - 1)];
             if (kind == 0) {
 #pragma unroll
@@ -144,7 +152,10 @@ __global__ void __launch_bounds__(256) conv_apply_kernel(const ConvArgs a) {
                 acc[l][b].y = fmaf(m.w, v[b].y, acc[l][b].y);
               }
             }
-          }
+          };
+#pragma unroll
+          for (int l = 0; l < LON; ++l)
+            if ((unsigned)(s - l) < (unsigned)cnt) accumulate(l);  // the same for every thread: only true neighbours are touched
         }
       }
     }
@@ -163,7 +174,8 @@ __global__ void __launch_bounds__(256) conv_apply_kernel(const ConvArgs a) {
 // source row.  Step u brings the source at longitude u + lo + d0; offset d0 + k pairs it with the target u - k (cyclic),
 // whose gradient row sits in a register window of the 8 most recent targets.
 template <typename S, int NB>
-__global__ void __launch_bounds__(256) conv_table_grad_kernel(const ConvArgs a) {
+__global__ void __launch_bounds__(THREADS, 3) conv_table_grad_kernel(const ConvArgs a) {
+  constexpr int PF = 4;  // steps in flight (a power of two <= 8; nlon >= 8)
   const int w = a.order[2 * blockIdx.x], d0 = a.order[2 * blockIdx.x + 1];
   const int span = 2 * a.halo + 1;
   const int row = w / span, j = row + w % span - a.halo;
@@ -188,12 +200,17 @@ __global__ void __launch_bounds__(256) conv_table_grad_kernel(const ConvArgs a) 
           window[(LON - t) & (LON - 1)][b] = b < nb ? Pair<S>::unpack(Pair<S>::load(grow + b * sample + (size_t)(a.nlon - t) * a.width)) : make_float2(0.f, 0.f);
       int p = (lo + d0) % a.nlon;
       if (p < 0) p += a.nlon;
-      // the source and the target of step u, loaded one step ahead of their use
-      typename Pair<S>::Raw next_v[NB], next_g[NB];
+      // ring of PF steps in flight: the source and the target of step u + PF are loaded when step u is consumed
+      typename Pair<S>::Raw ring_v[PF][NB], ring_g[PF][NB];
+      int ahead = p;
 #pragma unroll
-      for (int b = 0; b < NB; ++b) {
-        next_v[b] = b < nb ? Pair<S>::load(xrow + b * sample + (size_t)p * a.width) : Pair<S>::zero();
-        next_g[b] = b < nb ? Pair<S>::load(grow + b * sample) : Pair<S>::zero();
+      for (int t = 0; t < PF; ++t) {
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+          ring_v[t][b] = b < nb ? Pair<S>::load(xrow + b * sample + (size_t)ahead * a.width) : Pair<S>::zero();
+          ring_g[t][b] = b < nb ? Pair<S>::load(grow + b * sample + (size_t)t * a.width) : Pair<S>::zero();
+        }
+        ahead = ahead + 1 == a.nlon ? 0 : ahead + 1;
       }
       for (int u0 = 0; u0 < a.nlon; u0 += LON) {  // nlon is a multiple of 8 (checked by the host)
 #pragma unroll
@@ -201,16 +218,16 @@ __global__ void __launch_bounds__(256) conv_table_grad_kernel(const ConvArgs a) 
           float2 v[NB];
 #pragma unroll
           for (int b = 0; b < NB; ++b) {
-            v[b] = Pair<S>::unpack(next_v[b]);
-            window[u][b] = Pair<S>::unpack(next_g[b]);
+            v[b] = Pair<S>::unpack(ring_v[u % PF][b]);
+            window[u][b] = Pair<S>::unpack(ring_g[u % PF][b]);
           }
-          p = p + 1 == a.nlon ? 0 : p + 1;
-          if (u0 + u + 1 < a.nlon) {
+          if (u0 + u + PF < a.nlon) {
 #pragma unroll
             for (int b = 0; b < NB; ++b) {
-              next_v[b] = b < nb ? Pair<S>::load(xrow + b * sample + (size_t)p * a.width) : Pair<S>::zero();
-              next_g[b] = b < nb ? Pair<S>::load(grow + b * sample + (size_t)(u0 + u + 1) * a.width) : Pair<S>::zero();
+              ring_v[u % PF][b] = b < nb ? Pair<S>::load(xrow + b * sample + (size_t)ahead * a.width) : Pair<S>::zero();
+              ring_g[u % PF][b] = b < nb ? Pair<S>::load(grow + b * sample + (size_t)(u0 + u + PF) * a.width) : Pair<S>::zero();
             }
+            ahead = ahead + 1 == a.nlon ? 0 : ahead + 1;
           }
 #pragma unroll
           for (int k = 0; k < LON; ++k) {
@@ -269,16 +286,18 @@ extern "C" int gm_lattice_conv_apply(const void* x, const float* table, const in
   a.x = x; a.table = table; a.items = items; a.win_cnt = win_cnt; a.win_lo = win_lo; a.win_off = win_off; a.order = order; a.y = y;
   a.n_items = n_items; a.rows = rows; a.nlon = nlon; a.batch = batch; a.width = width; a.halo = halo; a.table_width = table_width;
   a.transpose = transpose;
-  const int threads = min(256, (n_items + 31) / 32 * 32);
-  const int nb = batch >= 4 ? 4 : (batch >= 2 ? 2 : 1);
+  const int threads = min(THREADS, (n_items + 31) / 32 * 32);
+  // two samples per thread: 32 accumulators + the window of 8 matrices + 4 steps in flight stay under 128 registers, three
+  // CTAs per SM (four samples measured 1 CTA per SM and half the speed)
+  const int nb = batch >= 2 ? 2 : 1;
   GM_REQUIRE((batch + nb - 1) / nb <= 65535, GM_ERR_LIMIT, "gm_lattice_conv_apply: batch too large");
   dim3 grid(nlon / LON, n_order, (batch + nb - 1) / nb);
   cudaStream_t cs = (cudaStream_t)stream;
 #define GM_APPLY(S, NB) conv_apply_kernel<S, NB><<<grid, threads, 0, cs>>>(a)
   if (dtype == GM_F32) {
-    if (nb == 4) GM_APPLY(float, 4); else if (nb == 2) GM_APPLY(float, 2); else GM_APPLY(float, 1);
+    if (nb == 2) GM_APPLY(float, 2); else GM_APPLY(float, 1);
   } else {
-    if (nb == 4) GM_APPLY(__nv_bfloat16, 4); else if (nb == 2) GM_APPLY(__nv_bfloat16, 2); else GM_APPLY(__nv_bfloat16, 1);
+    if (nb == 2) GM_APPLY(__nv_bfloat16, 2); else GM_APPLY(__nv_bfloat16, 1);
   }
 #undef GM_APPLY
   return launch_status("gm_lattice_conv_apply");
@@ -298,7 +317,7 @@ extern "C" int gm_lattice_conv_table_grad(const void* g, const void* x, const in
   ConvArgs a{};
   a.x = x; a.g = g; a.items = items; a.win_cnt = win_cnt; a.win_lo = win_lo; a.win_off = win_off; a.order = blocks; a.dtable = dtable;
   a.n_items = n_items; a.rows = rows; a.nlon = nlon; a.batch = batch; a.width = width; a.halo = halo; a.table_width = table_width;
-  const int threads = min(256, (n_items + 31) / 32 * 32);
+  const int threads = min(THREADS, (n_items + 31) / 32 * 32);
   const int nb = batch >= 2 ? 2 : 1;  // four samples' windows would take every register a thread can have
   cudaStream_t cs = (cudaStream_t)stream;
 #define GM_GRAD(S, NB) conv_table_grad_kernel<S, NB><<<(unsigned)n_blocks, threads, 0, cs>>>(a)

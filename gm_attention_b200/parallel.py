@@ -412,6 +412,206 @@ class NativeHaloExchanger:
             self._zero_halo(grads, stream)
 
 
+class PeerHaloExchanger:
+    """The halo exchange through peer memory (``gm_peer_*``): same interface as :class:`HaloExchanger`.
+
+    Every rank owns one device block with a receive buffer per (neighbour, kind of exchange) and the flag words of the
+    protocol; neighbours map each other's blocks through CUDA IPC.  A send is ONE kernel that stores the rows straight into
+    the neighbour's buffer over NVLink and raises a flag there; a landing is ONE kernel that waits for its flag (bounded) and
+    unpacks (forward) or adds (backward).  Needs GPUs that can map each other's memory: construction raises ``RuntimeError``
+    on every rank when any rank could not map a neighbour (use :class:`NativeHaloExchanger` then).  The blocks are sized at
+    the first exchange for that call's field shape, dtype and field count (at most four fields); later calls must match."""
+
+    KINDS = ("fill", "reduce")
+    WORD = 128  # bytes between flag words: one per cache line
+
+    def __init__(self, plan: BandPlan, rank: int, device: torch.device, group: dist.ProcessGroup | None = None) -> None:
+        from gm_attention_b200 import _lib
+
+        self._lib = _lib
+        self.plan, self.rank, self.device, self.group = plan, rank, device, group
+        self.elo, self.ehi = plan.extended(rank)
+        self.lo, self.hi = plan.owned(rank)
+        self.peers = [(other, plan.needs(other, rank), plan.needs(rank, other)) for other in range(plan.world)
+                      if other != rank and (plan.needs(other, rank) is not None or plan.needs(rank, other) is not None)]
+        self.side = torch.cuda.Stream(device)
+        self.block = ctypes.c_void_p()
+        self.mapped: dict[int, ctypes.c_void_p] = {}
+        self.layout: dict | None = None
+        self.remote: dict[int, dict] = {}
+        self.steps = {(other, kind): 0 for other, _, _ in self.peers for kind in self.KINDS}
+        self._shape = None
+
+    # ---- set-up (collective, at the first exchange)
+    def _setup(self, like: Tensor, count: int) -> None:
+        row_bytes = like.shape[2] * like.shape[3] * like.element_size()
+        batch = like.shape[0]
+        layout: dict = {}
+        cursor = 0
+
+        def take(nbytes: int) -> int:
+            nonlocal cursor
+            at = cursor
+            cursor += -(-nbytes // 256) * 256
+            return at
+
+        for other, theirs, mine in self.peers:
+            # what I RECEIVE from `other`: in a fill my halo rows `mine`, in a reduce the sums for my rows `theirs`
+            for kind, rows in (("fill", mine), ("reduce", theirs)):
+                layout[(other, kind)] = {"buffer": take(count * batch * (rows[1] - rows[0]) * row_bytes) if rows is not None else None,
+                                         "data": take(self.WORD), "ack": take(self.WORD), "send_ticket": take(self.WORD),
+                                         "land_ticket": take(self.WORD)}
+        handle = (ctypes.c_ubyte * 64)()
+        status, message = 0, ""
+        try:
+            with torch.cuda.device(self.device):
+                self._lib.call("gm_peer_alloc", max(cursor, 256), ctypes.byref(self.block), ctypes.addressof(handle))
+        except RuntimeError as exc:
+            status, message = 1, str(exc)
+        mine_info = {"rank": self.rank, "handle": bytes(handle), "layout": layout, "status": status}
+        everyone: list = [None] * self.plan.world
+        dist.all_gather_object(everyone, mine_info, group=self.group)
+        by_rank = {info["rank"]: info for info in everyone}
+        if status == 0:
+            for other, _, _ in self.peers:
+                if by_rank[other]["status"]:
+                    continue
+                mapped = ctypes.c_void_p()
+                try:
+                    with torch.cuda.device(self.device):
+                        self._lib.call("gm_peer_open", ctypes.addressof((ctypes.c_ubyte * 64).from_buffer_copy(by_rank[other]["handle"])),
+                                       ctypes.byref(mapped))
+                    self.mapped[other] = mapped
+                    self.remote[other] = by_rank[other]["layout"]
+                except RuntimeError as exc:
+                    status, message = 1, str(exc)
+        verdict = torch.tensor([status], device=self.device, dtype=torch.int32)
+        dist.all_reduce(verdict, op=dist.ReduceOp.MAX, group=self.group)
+        if int(verdict.item()) or any(info["status"] for info in everyone):
+            self.close()
+            raise RuntimeError(f"peer-memory halo exchange is not available on this machine ({message or 'another rank could not map its neighbour'})")
+        self.layout = layout
+        self._shape = (tuple(like.shape), like.dtype, count)
+
+    def close(self) -> None:
+        torch.cuda.synchronize(self.device)
+        with torch.cuda.device(self.device):
+            for mapped in self.mapped.values():
+                self._lib.call("gm_peer_close", mapped)
+            self.mapped = {}
+            if self.block:
+                self._lib.call("gm_peer_free", self.block)
+                self.block = ctypes.c_void_p()
+
+    def error(self) -> int:
+        """0, or which bounded wait ran out on this device (1: a send's acknowledgement, 2: a landing's data)."""
+        code = ctypes.c_int(0)
+        with torch.cuda.device(self.device):
+            self._lib.call("gm_peer_error", ctypes.byref(code))
+        return code.value
+
+    # ---- one exchange
+    def _check(self, fields: tuple[Tensor, ...]) -> None:
+        if len(fields) > 4:
+            raise RuntimeError("at most four fields per halo exchange")
+        for f in fields:
+            if not f.is_contiguous() or f.shape != fields[0].shape or f.dtype != fields[0].dtype:
+                raise RuntimeError("halo exchange needs contiguous (batch, rows, nlon, D) fields of one shape and dtype")
+        if self.layout is None:
+            self._setup(fields[0], len(fields))
+        elif self._shape != (tuple(fields[0].shape), fields[0].dtype, len(fields)):
+            raise RuntimeError("this exchanger's buffers were sized for another field shape, dtype or field count")
+
+    def _geometry(self, fields: tuple[Tensor, ...], rows: tuple[int, int]):
+        like = fields[0]
+        row_bytes = like.shape[2] * like.shape[3] * like.element_size()
+        r0, r1 = rows[0] - self.elo, rows[1] - self.elo
+        bases = (ctypes.c_void_p * len(fields))(*[f.data_ptr() + r0 * row_bytes for f in fields])
+        return bases, len(fields), like.shape[0], (r1 - r0) * row_bytes, like.shape[1] * row_bytes
+
+    def _send(self, kind: str, fields: tuple[Tensor, ...], stream: torch.cuda.Stream) -> None:
+        with torch.cuda.device(self.device):
+            for other, theirs, mine in self.peers:
+                rows = theirs if kind == "fill" else mine  # rows of MY extended band that go to `other`
+                if rows is None:
+                    continue
+                self.steps[(other, kind)] += 1  # one counter per (neighbour, kind): its send and its landing advance together
+                step = self.steps[(other, kind)]
+                there, here = self.remote[other][(self.rank, kind)], self.layout[(other, kind)]
+                base = self.mapped[other].value
+                self._lib.call("gm_peer_send", *self._geometry(fields, rows), base + there["buffer"], self.block.value + here["ack"],
+                               self.block.value + here["send_ticket"], base + there["data"], step, stream.cuda_stream)
+
+    def _land(self, kind: str, fields: tuple[Tensor, ...], stream: torch.cuda.Stream) -> None:
+        code = self._lib.dtype_code(fields[0].dtype) if fields[0].dtype in (torch.float32, torch.bfloat16) else 0
+        with torch.cuda.device(self.device):
+            for other, theirs, mine in self.peers:
+                rows = mine if kind == "fill" else theirs  # rows of MY extended band that `other` sent
+                if rows is None:
+                    continue
+                # the landing of the step whose send has just been counted; when this rank sends nothing to `other` in this
+                # kind of exchange the counter advances here
+                outgoing = theirs if kind == "fill" else mine
+                if outgoing is None:
+                    self.steps[(other, kind)] += 1
+                step = self.steps[(other, kind)]
+                there, here = self.remote[other][(self.rank, kind)], self.layout[(other, kind)]
+                base = self.mapped[other].value
+                self._lib.call("gm_peer_land", *self._geometry(fields, rows), self.block.value + here["buffer"], int(kind == "reduce"), code,
+                               self.block.value + here["data"], self.block.value + here["land_ticket"], base + there["ack"], step,
+                               stream.cuda_stream)
+
+    def _zero_halo(self, grads: tuple[Tensor, ...], stream: torch.cuda.Stream) -> None:
+        with torch.cuda.stream(stream):
+            for g in grads:
+                if self.lo > self.elo:
+                    g[:, : self.lo - self.elo].zero_()
+                if self.ehi > self.hi:
+                    g[:, self.hi - self.elo:].zero_()
+
+    def fill_halos(self, *fields: Tensor, stream: torch.cuda.Stream | None = None) -> None:
+        """Forward exchange on the current stream: every field's halo rows receive the owners' rows."""
+        self._check(fields)
+        stream = stream or torch.cuda.current_stream(self.device)
+        self._send("fill", fields, stream)
+        self._land("fill", fields, stream)
+
+    def start_fill(self, *fields: Tensor):
+        self.side.wait_stream(torch.cuda.current_stream(self.device))
+        self.fill_halos(*fields, stream=self.side)
+        done = torch.cuda.Event()
+        done.record(self.side)
+        return done
+
+    def finish_fill(self, done) -> None:
+        torch.cuda.current_stream(self.device).wait_event(done)
+
+    def reduce_halos(self, *grads: Tensor, zero_halo: bool = True) -> None:
+        """Backward exchange on the current stream: halo rows' partial sums go to their owners and are added there."""
+        self._check(grads)
+        stream = torch.cuda.current_stream(self.device)
+        self._send("reduce", grads, stream)
+        self._land("reduce", grads, stream)
+        if zero_halo:
+            self._zero_halo(grads, stream)
+
+    def start_reduce(self, *grads: Tensor):
+        self._check(grads)
+        self.side.wait_stream(torch.cuda.current_stream(self.device))
+        self._send("reduce", grads, self.side)
+        done = torch.cuda.Event()
+        done.record(self.side)
+        return done, grads
+
+    def finish_reduce(self, handle, zero_halo: bool = True) -> None:
+        done, grads = handle
+        stream = torch.cuda.current_stream(self.device)
+        stream.wait_event(done)
+        self._land("reduce", grads, stream)
+        if zero_halo:
+            self._zero_halo(grads, stream)
+
+
 @dataclass(frozen=True)
 class OverlapTables:
     """Row subsets of a rank's lattice tables for running the layer around the halo exchange."""

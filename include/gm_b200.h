@@ -438,6 +438,38 @@ int gm_lattice_conv_table_grad(const void* g, const void* x, const int32_t* item
                                const int32_t* win_lo, const int32_t* win_off, const int32_t* blocks, int64_t n_blocks, int rows,
                                int nlon, int batch, int width, int halo, int table_width, int dtype, float* dtable, void* stream);
 
+/* ---------------------------------------------------------------------------
+ * Halo exchange through peer memory (machines whose GPUs can map each other's
+ * memory; one process per GPU).  No reference counterpart.
+ *
+ * Every rank allocates one zeroed block (gm_peer_alloc) holding its receive
+ * buffers and flag words and publishes its 64-byte IPC handle; neighbours map
+ * it (gm_peer_open) and only ever STORE into it.  Per (neighbour, kind of
+ * exchange) and step = 1, 2, ...:
+ *   gm_peer_send  waits (bounded) until *local_ack >= step - 1, copies the rows
+ *                 of up to 4 fields into remote_buffer (layout (field, sample,
+ *                 slab)), then stores step to *remote_data_flag;
+ *   gm_peer_land  waits (bounded) until *local_data_flag >= step, copies
+ *                 (add == 0) or adds (add != 0, GM_BF16 / GM_F32) local_buffer
+ *                 into the fields' rows, then stores step to *remote_ack.
+ * fields[i]: sample 0's slab of field i; batch slabs sample_bytes apart,
+ * slab_bytes each; 16-byte units.  local_ticket: a zeroed 4-byte word of the
+ * caller's own block, private to the (neighbour, kind, direction).  A rank
+ * sends to all neighbours before it lands; a wait that runs out (about one
+ * second) sets the word gm_peer_error reads (1: a send's, 2: a landing's),
+ * moves nothing and returns.  One launch per call, on `stream`.
+ * ------------------------------------------------------------------------ */
+int gm_peer_alloc(int64_t bytes, void** block, void* handle64);
+int gm_peer_free(void* block);
+int gm_peer_open(const void* handle64, void** mapped);
+int gm_peer_close(void* mapped);
+int gm_peer_send(void* const* fields, int n_fields, int64_t batch, int64_t slab_bytes, int64_t sample_bytes, void* remote_buffer,
+                 const uint32_t* local_ack, uint32_t* local_ticket, uint32_t* remote_data_flag, uint32_t step, void* stream);
+int gm_peer_land(void* const* fields, int n_fields, int64_t batch, int64_t slab_bytes, int64_t sample_bytes, void* local_buffer,
+                 int add, int dtype, const uint32_t* local_data_flag, uint32_t* local_ticket, uint32_t* remote_ack, uint32_t step,
+                 void* stream);
+int gm_peer_error(int* code);
+
 #ifdef __cplusplus
 }
 #endif

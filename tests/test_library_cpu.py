@@ -142,18 +142,18 @@ def test_header_compiles_as_c(tmp_path):
 
 
 def test_ctypes_signatures_match_the_header():
-    """The hand-written ctypes argument lists have the arity and the kinds (pointer / int / int64 / double) of the
+    """The hand-written ctypes argument lists have the arity and the kinds (pointer / int / int64 / uint32 / double) of the
     header's prototypes: a mismatch would otherwise pass garbage silently."""
     from gm_attention_b200 import _lib
 
     protos = header_prototypes()
-    kinds = {ctypes.c_void_p: "pointer", ctypes.c_int: "int", ctypes.c_int64: "int64", ctypes.c_double: "double"}
+    kinds = {ctypes.c_void_p: "pointer", ctypes.c_int: "int", ctypes.c_int64: "int64", ctypes.c_double: "double", ctypes.c_uint32: "uint32"}
 
     def kind_of(decl: str) -> str:
         if "*" in decl:
             return "pointer"
         base = decl.rsplit(" ", 1)[0].replace("const ", "").strip()
-        return {"int": "int", "int64_t": "int64", "double": "double"}[base]
+        return {"int": "int", "int64_t": "int64", "double": "double", "uint32_t": "uint32"}[base]
 
     for name, argtypes in {**_lib.SIGNATURES, **_lib.SIZE_QUERIES}.items():
         assert name in protos, name
