@@ -17,9 +17,9 @@
 // Both are FMA-bound, not HBM-bound (4 multiply-adds per complex copy, edge and sample against 0.01 bytes of compulsory
 // traffic), and neither has a contraction over channels, so there is nothing for the tensor cores here.  A thread owns
 // one item -- a complex copy, or a pair of scalar channels -- so a warp reads 32 neighbouring items of a node as one
-// 128-byte line; it keeps 8 longitudes x 2 samples of accumulators in registers and slides a window of 8 coefficient
-// entries over the source longitudes, so every loaded value is used for up to 8 x 4 multiply-adds and nothing is staged
-// in shared memory.  Results do not depend on the launch geometry: no atomics.
+// 128-byte line; it keeps 8 longitudes x 2 samples of accumulators in registers and slides a register window of 8
+// source longitudes (apply) or 8 target longitudes (table_grad) past them, so every loaded value is used for 8 x 4
+// multiply-adds and nothing is staged in shared memory.  Results do not depend on the launch geometry: no atomics.
 #include "common.cuh"
 
 namespace gmb {
@@ -93,14 +93,11 @@ __global__ void __launch_bounds__(THREADS, 3) conv_apply_kernel(const ConvArgs a
       const S* xrow = x + (size_t)j * a.nlon * a.width + col;
       int p = (l0 + lo) % a.nlon;
       if (p < 0) p += a.nlon;
-      float4 window[LON];  // window[s % 8] = the matrix of offset s, for the 8 most recent s
-#pragma unroll
-      for (int u = 0; u < LON; ++u) window[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-      const int steps = cnt + LON - 1;
-      // the matrix of offset s (zero beyond the window) and the sources of step s, loaded one step ahead of their use
-      auto matrix = [&](int s) {
-        if (s >= cnt) return make_float4(0.f, 0.f, 0.f, 0.f);
-        const float* f = table + (size_t)s * a.table_width;
+      // Position t of the source row is longitude l0 + lo + t; under offset d the block's target l sees position d + l.
+      // A register window holds the 8 most recent positions and slides by one per offset, so every offset is 8 targets x
+      // NB samples of multiply-adds on true neighbours only: no ramp, no validity tests.
+      auto matrix = [&](int d) {
+        const float* f = table + (size_t)d * a.table_width;
         if (kind == 0) {
           const float4 m = __ldg(reinterpret_cast<const float4*>(f));
           return a.transpose ? make_float4(m.x, m.z, m.y, m.w) : m;
@@ -108,54 +105,61 @@ __global__ void __launch_bounds__(THREADS, 3) conv_apply_kernel(const ConvArgs a
         const float2 m = __ldg(reinterpret_cast<const float2*>(f));
         return make_float4(m.x, 0.f, 0.f, m.y);
       };
-      // ring of PF steps in flight: the loads of step s + PF are issued when step s is consumed
+      int ahead = p;  // longitude of the next position to load
+      auto source = [&](int b) { return b < nb ? Pair<S>::load(xrow + b * sample + (size_t)ahead * a.width) : Pair<S>::zero(); };
+      auto advance = [&]() { ahead = ahead + 1 == a.nlon ? 0 : ahead + 1; };
+      float2 xs[LON][NB];  // xs[t % 8] = position t
+#pragma unroll
+      for (int t = 0; t < LON - 1; ++t) {
+#pragma unroll
+        for (int b = 0; b < NB; ++b) xs[t][b] = Pair<S>::unpack(source(b));
+        advance();
+      }
+      // ring of PF offsets in flight: matrix d + PF and position d + 7 + PF are loaded when offset d is consumed
       typename Pair<S>::Raw ring_v[PF][NB];
       float4 ring_m[PF];
-      int ahead = p;  // longitude of the next step to load
 #pragma unroll
       for (int t = 0; t < PF; ++t) {
-        ring_m[t] = matrix(t);
+        if (t < cnt) {
+          ring_m[t] = matrix(t);
 #pragma unroll
-        for (int b = 0; b < NB; ++b)
-          ring_v[t][b] = (b < nb && t < steps) ? Pair<S>::load(xrow + b * sample + (size_t)ahead * a.width) : Pair<S>::zero();
-        ahead = ahead + 1 == a.nlon ? 0 : ahead + 1;
+          for (int b = 0; b < NB; ++b) ring_v[t][b] = source(b);
+          advance();
+        }
       }
-      // step s brings the source at longitude l0 + lo + s; the target l of the block sees it under offset d = s - l
-      for (int s0 = 0; s0 < steps; s0 += LON) {
+      for (int d0 = 0; d0 < cnt; d0 += LON) {
 #pragma unroll
         for (int u = 0; u < LON; ++u) {
-          const int s = s0 + u;
-          if (s >= steps) break;
-          window[u] = ring_m[u % PF];
-          float2 v[NB];
+          const int d = d0 + u;
+          if (d >= cnt) break;
+          const float4 m = ring_m[u % PF];
 #pragma unroll
-          for (int b = 0; b < NB; ++b) v[b] = Pair<S>::unpack(ring_v[u % PF][b]);
-          if (s + PF < steps) {
-            ring_m[u % PF] = matrix(s + PF);
+          for (int b = 0; b < NB; ++b) xs[(u + LON - 1) & (LON - 1)][b] = Pair<S>::unpack(ring_v[u % PF][b]);
+          if (d + PF < cnt) {
+            ring_m[u % PF] = matrix(d + PF);
 #pragma unroll
-            for (int b = 0; b < NB; ++b)
-              ring_v[u % PF][b] = b < nb ? Pair<S>::load(xrow + b * sample + (size_t)ahead * a.width) : Pair<S>::zero();
-            ahead = ahead + 1 == a.nlon ? 0 : ahead + 1;
+            for (int b = 0; b < NB; ++b) ring_v[u % PF][b] = source(b);
+            advance();
           }
-          auto accumulate = [&](int l) {
-            const float4 m = window[(u - l) & (LON - 1)];
-            if (kind == 0) {
+          if (kind == 0) {
+#pragma unroll
+            for (int l = 0; l < LON; ++l)
 #pragma unroll
               for (int b = 0; b < NB; ++b) {
-                acc[l][b].x = fmaf(m.x, v[b].x, fmaf(m.y, v[b].y, acc[l][b].x));
-                acc[l][b].y = fmaf(m.z, v[b].x, fmaf(m.w, v[b].y, acc[l][b].y));
+                const float2 v = xs[(u + l) & (LON - 1)][b];
+                acc[l][b].x = fmaf(m.x, v.x, fmaf(m.y, v.y, acc[l][b].x));
+                acc[l][b].y = fmaf(m.z, v.x, fmaf(m.w, v.y, acc[l][b].y));
               }
-            } else {  // two independent scalar channels: no cross terms, so a non-finite value stays in its channel
+          } else {  // two independent scalar channels: no cross terms, so a non-finite value stays in its channel
+#pragma unroll
+            for (int l = 0; l < LON; ++l)
 #pragma unroll
               for (int b = 0; b < NB; ++b) {
-                acc[l][b].x = fmaf(m.x, v[b].x, acc[l][b].x);
-                acc[l][b].y = fmaf(m.w, v[b].y, acc[l][b].y);
+                const float2 v = xs[(u + l) & (LON - 1)][b];
+                acc[l][b].x = fmaf(m.x, v.x, acc[l][b].x);
+                acc[l][b].y = fmaf(m.w, v.y, acc[l][b].y);
               }
-            }
-          };
-#pragma unroll
-          for (int l = 0; l < LON; ++l)
-            if ((unsigned)(s - l) < (unsigned)cnt) accumulate(l);  // the same for every thread: only true neighbours are touched
+          }
         }
       }
     }

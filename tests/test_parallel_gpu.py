@@ -137,3 +137,47 @@ def test_sharded_layer_on_gpus(tmp_path, kind):
     if made == [f"skip{r}" for r in range(world)]:
         pytest.skip("these GPUs cannot map each other's memory")
     assert made == [f"ok{r}" for r in range(world)]
+
+
+def test_peer_protocol_on_one_gpu():
+    """The send / landing kernels of the peer-memory exchange with the "neighbour's" block being this process's own: every
+    kernel finds its flag already raised by the kernel before it on the stream, so nothing ever waits on a concurrent
+    kernel.  Three steps of copy and of add, bf16 and float32; the flags must carry the step, or the landing would run
+    out of patience and report it."""
+    import ctypes
+
+    from gm_attention_b200 import _lib
+
+    device = torch.device("cuda", 0)
+    batch, rows, nlon, width, r0, r1 = 3, 10, 8, 40, 2, 5
+    for dtype in (torch.bfloat16, torch.float32):
+        elem = torch.empty((), dtype=dtype).element_size()
+        row_bytes = nlon * width * elem
+        slab, sample = (r1 - r0) * row_bytes, rows * row_bytes
+        buffer_bytes = 2 * batch * slab
+        block, handle = ctypes.c_void_p(), (ctypes.c_ubyte * 64)()
+        _lib.call("gm_peer_alloc", buffer_bytes + 4 * 128, ctypes.byref(block), ctypes.addressof(handle))
+        words = [block.value + buffer_bytes + 128 * i for i in range(4)]  # data flag, acknowledgement, send ticket, land ticket
+        try:
+            gen = torch.Generator(device="cuda").manual_seed(3)
+            for step in (1, 2, 3):
+                src = [torch.randn(batch, rows, nlon, width, generator=gen, device=device).to(dtype) for _ in range(2)]
+                dst = [torch.randn(batch, rows, nlon, width, generator=gen, device=device).to(dtype) for _ in range(2)]
+                before = [d.clone() for d in dst]
+                pointers = lambda fields: (ctypes.c_void_p * 2)(*[f.data_ptr() + r0 * row_bytes for f in fields])
+                stream = torch.cuda.current_stream(device).cuda_stream
+                add = step == 2
+                _lib.call("gm_peer_send", pointers(src), 2, batch, slab, sample, block.value, words[1], words[2], words[0], step, stream)
+                _lib.call("gm_peer_land", pointers(dst), 2, batch, slab, sample, block.value, int(add), _lib.dtype_code(dtype), words[0], words[3],
+                          words[1], step, stream)
+                torch.cuda.synchronize()
+                code = ctypes.c_int(-1)
+                _lib.call("gm_peer_error", ctypes.byref(code))
+                assert code.value == 0
+                for s_, d_, b_ in zip(src, dst, before):
+                    want = b_.clone()
+                    want[:, r0:r1] = (b_[:, r0:r1].float() + s_[:, r0:r1].float()).to(dtype) if add else s_[:, r0:r1]
+                    assert torch.equal(d_, want)
+        finally:
+            torch.cuda.synchronize()
+            _lib.call("gm_peer_free", block)
