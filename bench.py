@@ -416,6 +416,18 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
+    if isinstance(halo, PeerHaloExchanger):
+        # a bounded wait of the peer-memory exchange that ran out during the warm-up: every rank falls back to NCCL together
+        code = torch.tensor([halo.error()], device=device, dtype=torch.int32)
+        dist.all_reduce(code, op=dist.ReduceOp.MAX)
+        if int(code.item()):
+            if args.halo == "peer":
+                print(json.dumps({"error": "a bounded wait of the peer-memory halo exchange ran out", "rank": rank, "code": int(code.item())}), file=sys.stderr, flush=True)
+                sys.exit(5)
+            halo, halo_kind = NativeHaloExchanger(plan, rank, device), "native"
+            for _ in range(3):
+                step()
+            barrier()
 
     # ---- parity self-check at the workload's own size: one more step, compared with the CPU oracle on sampled targets
     # (out, dq) and sources (dk, dv) of this rank's rows -- complete CSR rows cut out of the GLOBAL lattice, so with

@@ -430,6 +430,8 @@ def lattice_attention_forward(q: Tensor, k: Tensor, v: Tensor, t: LatticeTables,
     if lse is None:
         lse = torch.empty((q.shape[0], t.heads), dtype=torch.float32, device=device) if full else \
             torch.full((q.shape[0], t.heads), float("-inf"), dtype=torch.float32, device=device)
+    if t.row_order.numel() == 0:  # a band too narrow to have rows of this class (e.g. no row clear of the halo)
+        return out, lse
     desc = t.host_descriptor()
     four = tensor_cores and FOUR_HEADS == "1" and four_head_layout_supported(t, q.shape[1])
     off, ent, stride = (t.tc_win_off, t.tc_entries, t.tc_entries.shape[1]) if four else (t.win_off, t.entries, t.entry_stride)
@@ -461,13 +463,23 @@ def lattice_attention_backward(dout: Tensor, q: Tensor, k: Tensor, v: Tensor, ou
     else:
         dq, dk, dv = alloc(q), alloc_t(q), alloc_t(q)
         delta = torch.empty((q.shape[0], t.heads), dtype=torch.float32, device=device)
+    # passes over an empty row list are dropped (a band too narrow to have rows of that class)
+    if t.row_order.numel() == 0:
+        passes &= ~3
+    if t.t_row_order.numel() == 0:
+        passes &= ~4
+    if passes == 0 or (t.row_order.numel() == 0 and t.t_row_order.numel() == 0):
+        return dq, dk, dv
     desc = t.host_descriptor()
     four = tensor_cores and FOUR_HEADS == "1" and four_head_layout_supported(t, q.shape[1])
     off, ent, t_off, t_ent, stride = (t.tc_win_off, t.tc_entries, t.t_tc_win_off, t.t_tc_entries, t.tc_entries.shape[1]) if four else \
         (t.win_off, t.entries, t.t_win_off, t.t_entries, t.entry_stride)
+    # an empty list still needs an address (the entry points refuse null pointers): the other list's, with a count of zero
+    rows_ptr = _lib.ptr(t.row_order) or _lib.ptr(t.t_row_order)
+    t_rows_ptr = _lib.ptr(t.t_row_order) or _lib.ptr(t.row_order)
     common = (_lib.ptr(dout), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(lse), _lib.ptr(t.win_cnt), _lib.ptr(t.win_lo),
-              _lib.ptr(off), _lib.ptr(ent), _lib.ptr(t.row_order), t.row_order.numel(), _lib.ptr(t.t_win_cnt),
-              _lib.ptr(t.t_win_lo), _lib.ptr(t_off), _lib.ptr(t_ent), _lib.ptr(t.t_row_order), t.t_row_order.numel(),
+              _lib.ptr(off), _lib.ptr(ent), rows_ptr, t.row_order.numel(), _lib.ptr(t.t_win_cnt),
+              _lib.ptr(t.t_win_lo), _lib.ptr(t_off), _lib.ptr(t_ent), t_rows_ptr, t.t_row_order.numel(),
               ctypes.addressof(desc), len(t.desc_rows), t.rows, t.nlon, batch, q.shape[1], t.heads, t.halo, stride, t.orders,
               float(t.scale))
     outputs = (_lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(delta), _lib.stream(device))

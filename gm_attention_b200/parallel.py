@@ -477,10 +477,10 @@ class PeerHaloExchanger:
                 if by_rank[other]["status"]:
                     continue
                 mapped = ctypes.c_void_p()
+                theirs_handle = (ctypes.c_ubyte * 64).from_buffer_copy(by_rank[other]["handle"])  # kept alive across the call
                 try:
                     with torch.cuda.device(self.device):
-                        self._lib.call("gm_peer_open", ctypes.addressof((ctypes.c_ubyte * 64).from_buffer_copy(by_rank[other]["handle"])),
-                                       ctypes.byref(mapped))
+                        self._lib.call("gm_peer_open", ctypes.addressof(theirs_handle), ctypes.byref(mapped))
                     self.mapped[other] = mapped
                     self.remote[other] = by_rank[other]["layout"]
                 except RuntimeError as exc:
