@@ -68,11 +68,11 @@ def parse() -> argparse.Namespace:
     p.add_argument("--overlap", action="store_true",
                    help="N > 1: run the layer around the halo exchange (interior rows while the halos travel) instead of exchanging "
                         "before / after it; measured equal within 1 %% at N = 8 (the exchange is latency, not bandwidth), so off by default")
-    p.add_argument("--halo", choices=["auto", "peer", "native", "native-slabs", "torch"], default="native",
+    p.add_argument("--halo", choices=["auto", "peer", "native", "native-slabs", "torch"], default="auto",
                    help="N > 1: peer = the library's own copy kernels storing into the neighbour's mapped buffer (needs GPUs that can map each "
-                        "other's memory); native = the library's NCCL groups issued from C, one packed message per neighbour and direction (default) "
+                        "other's memory); native = the library's NCCL groups issued from C, one packed message per neighbour and direction "
                         "(native-slabs: one message per field and sample); torch = torch.distributed point-to-point with staging buffers; "
-                        "auto = peer where it can be set up, else native; default native")
+                        "auto (default) = peer where it can be set up and its waits stay within their bounds during the warm-up, else native")
     p.add_argument("--per-rank", action="store_true",
                    help="every rank prints its own per-step timings (halo exchange in, forward, backward, halo sums out) to stderr")
     p.add_argument("--no-cpu-baseline", action="store_true")

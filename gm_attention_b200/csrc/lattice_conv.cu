@@ -63,11 +63,12 @@ template <> struct Pair<__nv_bfloat16> {
 };
 
 // ---------------------------------------------------------------------------------------------------------------- apply
-template <typename S, int NB>
+// TL targets (consecutive longitudes) x NB samples per thread.
+template <typename S, int NB, int TL>
 __global__ void __launch_bounds__(THREADS, 3) conv_apply_kernel(const ConvArgs a) {
   constexpr int PF = 4;  // steps in flight (a power of two <= 8)
   const int row = a.order[blockIdx.y];
-  const int l0 = blockIdx.x * LON;
+  const int l0 = blockIdx.x * TL;
   const int b0 = blockIdx.z * NB;
   const int span = 2 * a.halo + 1;
   const size_t sample = (size_t)a.rows * a.nlon * a.width;
@@ -77,9 +78,9 @@ __global__ void __launch_bounds__(THREADS, 3) conv_apply_kernel(const ConvArgs a
 
   for (int item = threadIdx.x; item < a.n_items; item += blockDim.x) {
     const int kind = a.items[3 * item], col = a.items[3 * item + 1], fcol = a.items[3 * item + 2];
-    float2 acc[LON][NB];
+    float2 acc[TL][NB];
 #pragma unroll
-    for (int l = 0; l < LON; ++l)
+    for (int l = 0; l < TL; ++l)
 #pragma unroll
       for (int b = 0; b < NB; ++b) acc[l][b] = make_float2(0.f, 0.f);
 
@@ -108,9 +109,9 @@ __global__ void __launch_bounds__(THREADS, 3) conv_apply_kernel(const ConvArgs a
       int ahead = p;  // longitude of the next position to load
       auto source = [&](int b) { return b < nb ? Pair<S>::load(xrow + b * sample + (size_t)ahead * a.width) : Pair<S>::zero(); };
       auto advance = [&]() { ahead = ahead + 1 == a.nlon ? 0 : ahead + 1; };
-      float2 xs[LON][NB];  // xs[t % 8] = position t
+      float2 xs[TL][NB];  // xs[t % 8] = position t
 #pragma unroll
-      for (int t = 0; t < LON - 1; ++t) {
+      for (int t = 0; t < TL - 1; ++t) {
 #pragma unroll
         for (int b = 0; b < NB; ++b) xs[t][b] = Pair<S>::unpack(source(b));
         advance();
@@ -127,14 +128,14 @@ __global__ void __launch_bounds__(THREADS, 3) conv_apply_kernel(const ConvArgs a
           advance();
         }
       }
-      for (int d0 = 0; d0 < cnt; d0 += LON) {
+      for (int d0 = 0; d0 < cnt; d0 += TL) {
 #pragma unroll
-        for (int u = 0; u < LON; ++u) {
+        for (int u = 0; u < TL; ++u) {
           const int d = d0 + u;
           if (d >= cnt) break;
           const float4 m = ring_m[u % PF];
 #pragma unroll
-          for (int b = 0; b < NB; ++b) xs[(u + LON - 1) & (LON - 1)][b] = Pair<S>::unpack(ring_v[u % PF][b]);
+          for (int b = 0; b < NB; ++b) xs[(u + TL - 1) & (TL - 1)][b] = Pair<S>::unpack(ring_v[u % PF][b]);
           if (d + PF < cnt) {
             ring_m[u % PF] = matrix(d + PF);
 #pragma unroll
@@ -143,19 +144,19 @@ __global__ void __launch_bounds__(THREADS, 3) conv_apply_kernel(const ConvArgs a
           }
           if (kind == 0) {
 #pragma unroll
-            for (int l = 0; l < LON; ++l)
+            for (int l = 0; l < TL; ++l)
 #pragma unroll
               for (int b = 0; b < NB; ++b) {
-                const float2 v = xs[(u + l) & (LON - 1)][b];
+                const float2 v = xs[(u + l) & (TL - 1)][b];
                 acc[l][b].x = fmaf(m.x, v.x, fmaf(m.y, v.y, acc[l][b].x));
                 acc[l][b].y = fmaf(m.z, v.x, fmaf(m.w, v.y, acc[l][b].y));
               }
           } else {  // two independent scalar channels: no cross terms, so a non-finite value stays in its channel
 #pragma unroll
-            for (int l = 0; l < LON; ++l)
+            for (int l = 0; l < TL; ++l)
 #pragma unroll
               for (int b = 0; b < NB; ++b) {
-                const float2 v = xs[(u + l) & (LON - 1)][b];
+                const float2 v = xs[(u + l) & (TL - 1)][b];
                 acc[l][b].x = fmaf(m.x, v.x, acc[l][b].x);
                 acc[l][b].y = fmaf(m.w, v.y, acc[l][b].y);
               }
@@ -164,7 +165,7 @@ __global__ void __launch_bounds__(THREADS, 3) conv_apply_kernel(const ConvArgs a
       }
     }
 #pragma unroll
-    for (int l = 0; l < LON; ++l) {
+    for (int l = 0; l < TL; ++l) {
       if (l0 + l >= a.nlon) break;
 #pragma unroll
       for (int b = 0; b < NB; ++b)
@@ -291,13 +292,14 @@ extern "C" int gm_lattice_conv_apply(const void* x, const float* table, const in
   a.n_items = n_items; a.rows = rows; a.nlon = nlon; a.batch = batch; a.width = width; a.halo = halo; a.table_width = table_width;
   a.transpose = transpose;
   const int threads = min(THREADS, (n_items + 31) / 32 * 32);
-  // two samples per thread: 32 accumulators + the window of 8 matrices + 4 steps in flight stay under 128 registers, three
-  // CTAs per SM (four samples measured 1 CTA per SM and half the speed)
-  const int nb = batch >= 2 ? 2 : 1;
+  // 32 accumulators + a window of as many sources + 4 steps in flight stay under 128 registers: three CTAs per SM (four
+  // samples x 8 targets measured one CTA per SM and half the speed)
+  // (16 targets x 1 sample per thread -- the same registers -- measured the same 8.05 ms in bf16 and 4 % slower in float32)
+  const int nb = batch >= 2 ? 2 : 1, tl = LON;
   GM_REQUIRE((batch + nb - 1) / nb <= 65535, GM_ERR_LIMIT, "gm_lattice_conv_apply: batch too large");
-  dim3 grid(nlon / LON, n_order, (batch + nb - 1) / nb);
+  dim3 grid(nlon / tl, n_order, (batch + nb - 1) / nb);
   cudaStream_t cs = (cudaStream_t)stream;
-#define GM_APPLY(S, NB) conv_apply_kernel<S, NB><<<grid, threads, 0, cs>>>(a)
+#define GM_APPLY(S, NB) conv_apply_kernel<S, NB, LON><<<grid, threads, 0, cs>>>(a)
   if (dtype == GM_F32) {
     if (nb == 2) GM_APPLY(float, 2); else GM_APPLY(float, 1);
   } else {

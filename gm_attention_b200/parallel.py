@@ -717,10 +717,12 @@ def tensor_core_row_cost(pair_counts: Tensor) -> list[float]:
     steps of 16; a CTA stages the neighbour row in chunks and pays a fixed cost per owner tile.  The weights are a
     fit to measured times of row groups from the pole to the equator of a 256 x 512 lattice (within 15 % for every
     group; the bands of an 8-way split, each timed alone, come out within 3 % of one another).  Narrow equatorial
-    windows cost several times more PER EDGE than whole-row polar windows, which an edge-count balance ignores."""
+    windows cost several times more PER EDGE than whole-row polar windows, which an edge-count balance ignores.  The constant
+    per row was re-fitted on a 4-way split (bands [0, 40), [40, 128) and their mirror images timed side by side: with the
+    constant at 10 the equatorial bands took 4.08 ms against 3.90 ms for the polar ones)."""
     cnt = pair_counts.to(torch.float64)
     present = cnt > 0
     steps = torch.ceil((7 + cnt) / 16)
     chunks = torch.ceil((63 + cnt) / 80) + torch.ceil((31 + cnt) / 80)
     cost = torch.where(present, 7.1 * steps + 2.9 * chunks, torch.zeros_like(cnt))
-    return (10.0 + cost.sum(1)).tolist()
+    return (14.5 + cost.sum(1)).tolist()
