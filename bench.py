@@ -500,7 +500,7 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
         stop.record()
         barrier()
     # this rank's own halo kernels inside the timed region (pack / unpack / add, or the peer-memory send / landing)
-    halo_launches = sum(_lib.CALLS[n] - calls_before.get(n, 0) for n in ("gm_halo_move", "gm_halo_accumulate", "gm_peer_send", "gm_peer_land"))
+    halo_launches = sum(_lib.CALLS[n] - calls_before.get(n, 0) for n in ("gm_halo_move", "gm_halo_accumulate", "gm_peer_send", "gm_peer_land", "gm_peer_send_many", "gm_peer_land_many"))
     ms_total = start.elapsed_time(stop)
     if world > 1:
         t = torch.tensor([ms_total], device=device)

@@ -62,6 +62,8 @@ SIGNATURES: dict[str, list[Any]] = {
     "gm_peer_close": [_P],
     "gm_peer_send": [_P, _I, _L, _L, _L, _P, _P, _P, _P, ctypes.c_uint32, _P],
     "gm_peer_land": [_P, _I, _L, _L, _L, _P, _I, _I, _P, _P, _P, ctypes.c_uint32, _P],
+    "gm_peer_send_many": [_I, _P, _I, _L, _P, _L, _P, _P, _P, _P, _P, _P],
+    "gm_peer_land_many": [_I, _P, _I, _L, _P, _L, _P, _I, _I, _P, _P, _P, _P, _P],
     "gm_peer_error": [_P],
     "gm_attention_backward_static": [_P] * 12 + [_L, _L, _L, _I, _I, _I, _I, _D, _I, _P, _P, _P, _P],
 }

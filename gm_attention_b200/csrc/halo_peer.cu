@@ -30,8 +30,6 @@ __device__ unsigned g_peer_error = 0;  // 1: a send waited too long for an ackno
 
 constexpr unsigned POLL_LIMIT = 4u << 20;  // x ~250 ns of nanosleep: about a second
 
-struct PeerFields { void* base[4]; };
-
 __device__ __forceinline__ unsigned load_acquire_sys(const unsigned* p) {
   unsigned v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -71,15 +69,30 @@ __device__ __forceinline__ void signal_when_all_done(unsigned* ticket, unsigned 
   }
 }
 
+// One neighbour's share of a launch: the rows of up to 4 fields, the buffer they go to / come from, and the words of the
+// protocol.  A launch serves one or two neighbours (a band has at most two sides), so that their transfers overlap.
+struct PeerLane {
+  void* base[4];          // sample 0's slab of each field
+  uint4* buffer;          // layout (field, sample, slab), 16-byte units
+  int64_t slab_vec;
+  const unsigned* wait_flag;
+  unsigned wait_value;
+  unsigned* ticket;
+  unsigned* signal_flag;
+  unsigned step;
+};
+struct PeerLanes { PeerLane lane[2]; };
+
 // MODE 0: fields' slabs -> remote buffer, then the remote data flag.  MODE 1 / 2: local buffer -> fields' slabs
-// (copy / add), then the remote acknowledgement.  Buffer layout (field, sample, slab), 16-byte units.
+// (copy / add), then the remote acknowledgement.  blockIdx.z = lane * n_fields + field.
 template <int MODE>
-__global__ void peer_kernel(PeerFields fields, uint4* __restrict__ buffer, int64_t slab_vec, int64_t sample_vec, int bf16_add,
-                            const unsigned* wait_flag, unsigned wait_value, unsigned* ticket, unsigned* signal_flag, unsigned step) {
-  const bool ready = wait_for(wait_flag, wait_value, MODE == 0 ? 1u : 2u);
-  const int f = blockIdx.z, b = blockIdx.y;
-  uint4* field = reinterpret_cast<uint4*>(fields.base[f]) + (int64_t)b * sample_vec;
-  uint4* buf = buffer + ((int64_t)f * gridDim.y + b) * slab_vec;
+__global__ void peer_kernel(PeerLanes lanes, int n_fields, int64_t sample_vec, int bf16_add) {
+  const PeerLane& L = lanes.lane[blockIdx.z / n_fields];
+  const bool ready = wait_for(L.wait_flag, L.wait_value, MODE == 0 ? 1u : 2u);
+  const int f = blockIdx.z % n_fields, b = blockIdx.y;
+  const int64_t slab_vec = L.slab_vec;
+  uint4* field = reinterpret_cast<uint4*>(L.base[f]) + (int64_t)b * sample_vec;
+  uint4* buf = L.buffer + ((int64_t)f * gridDim.y + b) * slab_vec;
   // a wait that ran out: no data moves and nothing is signalled (the ticket is still taken, so the counter stays whole)
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; ready && i < slab_vec; i += (int64_t)gridDim.x * blockDim.x) {
     if (MODE == 0) {
@@ -106,29 +119,45 @@ __global__ void peer_kernel(PeerFields fields, uint4* __restrict__ buffer, int64
       field[i] = a;
     }
   }
-  signal_when_all_done(ticket, gridDim.x * gridDim.y * gridDim.z, ready ? signal_flag : nullptr, step);
+  signal_when_all_done(L.ticket, gridDim.x * gridDim.y * n_fields, ready ? L.signal_flag : nullptr, L.step);
 }
 
-int launch_peer(int mode, void* const* fields, int n_fields, int64_t batch, int64_t slab_bytes, int64_t sample_bytes, void* buffer, int dtype,
-                const unsigned* wait_flag, unsigned wait_value, unsigned* ticket, unsigned* signal_flag, unsigned step, void* stream,
-                const char* what) {
-  GM_REQUIRE(n_fields >= 1 && n_fields <= 4 && batch >= 1 && batch <= 65535, GM_ERR_ARGUMENT, "%s: bad arguments", what);
-  GM_REQUIRE(fields && buffer && wait_flag && ticket && signal_flag, GM_ERR_ARGUMENT, "%s: null pointer", what);
-  GM_REQUIRE(slab_bytes > 0 && slab_bytes % 16 == 0 && sample_bytes % 16 == 0 && reinterpret_cast<uintptr_t>(buffer) % 16 == 0, GM_ERR_ARGUMENT,
-             "%s: slabs must be whole 16-byte units on 16-byte boundaries", what);
+// n_lanes neighbours (1 or 2) in one launch.  fields: n_lanes * n_fields pointers, lane-major.
+int launch_peer(int mode, int n_lanes, void* const* fields, int n_fields, int64_t batch, const int64_t* slab_bytes, int64_t sample_bytes,
+                void* const* buffers, int dtype, const uint32_t* const* wait_flags, int wait_offset, uint32_t* const* tickets,
+                uint32_t* const* signal_flags, const uint32_t* steps, void* stream, const char* what) {
+  GM_REQUIRE(n_lanes >= 1 && n_lanes <= 2 && n_fields >= 1 && n_fields <= 4 && batch >= 1 && batch <= 65535, GM_ERR_ARGUMENT, "%s: bad arguments", what);
+  GM_REQUIRE(fields && slab_bytes && buffers && wait_flags && tickets && signal_flags && steps && sample_bytes % 16 == 0, GM_ERR_ARGUMENT,
+             "%s: null pointer or a sample stride that is not a multiple of 16 bytes", what);
   GM_REQUIRE(mode != 2 || dtype == GM_BF16 || dtype == GM_F32, GM_ERR_UNSUPPORTED, "%s: sums in bf16 or fp32", what);
-  PeerFields f{};
-  for (int i = 0; i < n_fields; ++i) {
-    GM_REQUIRE(fields[i] && reinterpret_cast<uintptr_t>(fields[i]) % 16 == 0, GM_ERR_ARGUMENT, "%s: field %d is null or not on a 16-byte boundary", what, i);
-    f.base[i] = fields[i];
+  PeerLanes lanes{};
+  int64_t widest = 0;
+  for (int l = 0; l < n_lanes; ++l) {
+    GM_REQUIRE(slab_bytes[l] > 0 && slab_bytes[l] % 16 == 0 && buffers[l] && reinterpret_cast<uintptr_t>(buffers[l]) % 16 == 0, GM_ERR_ARGUMENT,
+               "%s: slabs must be whole 16-byte units on 16-byte boundaries", what);
+    GM_REQUIRE(wait_flags[l] && tickets[l] && signal_flags[l], GM_ERR_ARGUMENT, "%s: null flag word", what);
+    PeerLane& L = lanes.lane[l];
+    for (int i = 0; i < n_fields; ++i) {
+      void* base = fields[l * n_fields + i];
+      GM_REQUIRE(base && reinterpret_cast<uintptr_t>(base) % 16 == 0, GM_ERR_ARGUMENT, "%s: field %d is null or not on a 16-byte boundary", what, i);
+      L.base[i] = base;
+    }
+    L.buffer = static_cast<uint4*>(buffers[l]);
+    L.slab_vec = slab_bytes[l] / 16;
+    L.wait_flag = wait_flags[l];
+    L.wait_value = steps[l] - (unsigned)wait_offset;
+    L.ticket = tickets[l];
+    L.signal_flag = signal_flags[l];
+    L.step = steps[l];
+    widest = L.slab_vec > widest ? L.slab_vec : widest;
   }
-  const int64_t slab_vec = slab_bytes / 16, sample_vec = sample_bytes / 16;
-  const unsigned bx = (unsigned)((slab_vec + 255) / 256 < 32 ? (slab_vec + 255) / 256 : 32);
-  dim3 grid(bx, (unsigned)batch, (unsigned)n_fields);
+  const unsigned bx = (unsigned)((widest + 255) / 256 < 32 ? (widest + 255) / 256 : 32);
+  dim3 grid(bx, (unsigned)batch, (unsigned)(n_fields * n_lanes));
   cudaStream_t cs = (cudaStream_t)stream;
-  if (mode == 0) peer_kernel<0><<<grid, 256, 0, cs>>>(f, (uint4*)buffer, slab_vec, sample_vec, 0, wait_flag, wait_value, ticket, signal_flag, step);
-  else if (mode == 1) peer_kernel<1><<<grid, 256, 0, cs>>>(f, (uint4*)buffer, slab_vec, sample_vec, 0, wait_flag, wait_value, ticket, signal_flag, step);
-  else peer_kernel<2><<<grid, 256, 0, cs>>>(f, (uint4*)buffer, slab_vec, sample_vec, dtype == GM_BF16 ? 1 : 0, wait_flag, wait_value, ticket, signal_flag, step);
+  const int64_t sample_vec = sample_bytes / 16;
+  if (mode == 0) peer_kernel<0><<<grid, 256, 0, cs>>>(lanes, n_fields, sample_vec, 0);
+  else if (mode == 1) peer_kernel<1><<<grid, 256, 0, cs>>>(lanes, n_fields, sample_vec, 0);
+  else peer_kernel<2><<<grid, 256, 0, cs>>>(lanes, n_fields, sample_vec, dtype == GM_BF16 ? 1 : 0);
   return launch_status(what);
 }
 
@@ -178,24 +207,40 @@ extern "C" int gm_peer_close(void* mapped) {
   return GM_OK;
 }
 
-// Sender side: rows of up to 4 fields (fields[i]: sample 0's slab; batch slabs sample_bytes apart, slab_bytes each) ->
-// remote_buffer in the neighbour's block, then remote_data_flag = step.  Waits first until *local_ack >= step - 1.
-// local_ticket: a zeroed word of this rank's own block, private to this (neighbour, kind).
+// Sender side, one neighbour: rows of up to 4 fields (fields[i]: sample 0's slab; batch slabs sample_bytes apart,
+// slab_bytes each) -> remote_buffer in the neighbour's block, then remote_data_flag = step.  Waits first until
+// *local_ack >= step - 1.  local_ticket: a zeroed word of this rank's own block, private to this (neighbour, kind).
 extern "C" int gm_peer_send(void* const* fields, int n_fields, int64_t batch, int64_t slab_bytes, int64_t sample_bytes, void* remote_buffer,
                             const uint32_t* local_ack, uint32_t* local_ticket, uint32_t* remote_data_flag, uint32_t step, void* stream) {
   if (slab_bytes == 0) return GM_OK;
-  return launch_peer(0, fields, n_fields, batch, slab_bytes, sample_bytes, remote_buffer, GM_F32, local_ack, step - 1, local_ticket,
-                     remote_data_flag, step, stream, "gm_peer_send");
+  return launch_peer(0, 1, fields, n_fields, batch, &slab_bytes, sample_bytes, &remote_buffer, GM_F32, &local_ack, 1, &local_ticket,
+                     &remote_data_flag, &step, stream, "gm_peer_send");
 }
 
-// Receiver side: waits until *local_data_flag >= step, then fields' slabs = local_buffer (add == 0) or += local_buffer
-// (add != 0; GM_BF16 or GM_F32), then remote_ack = step in the sender's block.
+// Receiver side, one neighbour: waits until *local_data_flag >= step, then fields' slabs = local_buffer (add == 0) or
+// += local_buffer (add != 0; GM_BF16 or GM_F32), then remote_ack = step in the sender's block.
 extern "C" int gm_peer_land(void* const* fields, int n_fields, int64_t batch, int64_t slab_bytes, int64_t sample_bytes, void* local_buffer,
                             int add, int dtype, const uint32_t* local_data_flag, uint32_t* local_ticket, uint32_t* remote_ack, uint32_t step,
                             void* stream) {
   if (slab_bytes == 0) return GM_OK;
-  return launch_peer(add ? 2 : 1, fields, n_fields, batch, slab_bytes, sample_bytes, local_buffer, dtype, local_data_flag, step, local_ticket,
-                     remote_ack, step, stream, "gm_peer_land");
+  return launch_peer(add ? 2 : 1, 1, fields, n_fields, batch, &slab_bytes, sample_bytes, &local_buffer, dtype, &local_data_flag, 0, &local_ticket,
+                     &remote_ack, &step, stream, "gm_peer_land");
+}
+
+// The same for n_lanes (1 or 2) neighbours in ONE launch, so that the transfers to / from both sides of a band overlap:
+// every per-neighbour argument is an array of n_lanes; fields holds n_lanes * n_fields pointers, neighbour-major.
+extern "C" int gm_peer_send_many(int n_lanes, void* const* fields, int n_fields, int64_t batch, const int64_t* slab_bytes, int64_t sample_bytes,
+                                 void* const* remote_buffers, const uint32_t* const* local_acks, uint32_t* const* local_tickets,
+                                 uint32_t* const* remote_data_flags, const uint32_t* steps, void* stream) {
+  return launch_peer(0, n_lanes, fields, n_fields, batch, slab_bytes, sample_bytes, remote_buffers, GM_F32, local_acks, 1, local_tickets,
+                     remote_data_flags, steps, stream, "gm_peer_send_many");
+}
+
+extern "C" int gm_peer_land_many(int n_lanes, void* const* fields, int n_fields, int64_t batch, const int64_t* slab_bytes, int64_t sample_bytes,
+                                 void* const* local_buffers, int add, int dtype, const uint32_t* const* local_data_flags,
+                                 uint32_t* const* local_tickets, uint32_t* const* remote_acks, const uint32_t* steps, void* stream) {
+  return launch_peer(add ? 2 : 1, n_lanes, fields, n_fields, batch, slab_bytes, sample_bytes, local_buffers, dtype, local_data_flags, 0,
+                     local_tickets, remote_acks, steps, stream, "gm_peer_land_many");
 }
 
 // 0: no wait of gm_peer_send / gm_peer_land has run out on the current device; 1: a send's; 2: a landing's.

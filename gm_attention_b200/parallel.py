@@ -416,9 +416,9 @@ class PeerHaloExchanger:
     """The halo exchange through peer memory (``gm_peer_*``): same interface as :class:`HaloExchanger`.
 
     Every rank owns one device block with a receive buffer per (neighbour, kind of exchange) and the flag words of the
-    protocol; neighbours map each other's blocks through CUDA IPC.  A send is ONE kernel that stores the rows straight into
-    the neighbour's buffer over NVLink and raises a flag there; a landing is ONE kernel that waits for its flag (bounded) and
-    unpacks (forward) or adds (backward).  Needs GPUs that can map each other's memory: construction raises ``RuntimeError``
+    protocol; neighbours map each other's blocks through CUDA IPC.  A send is ONE kernel (for both sides of the band) that stores
+    the rows straight into the neighbours' buffers over NVLink and raises a flag in each; a landing is ONE kernel that waits
+    for its flags (bounded) and unpacks (forward) or adds (backward).  Needs GPUs that can map each other's memory: construction raises ``RuntimeError``
     on every rank when any rank could not map a neighbour (use :class:`NativeHaloExchanger` then).  The blocks are sized at
     the first exchange for that call's field shape, dtype and field count (at most four fields); later calls must match."""
 
@@ -522,44 +522,53 @@ class PeerHaloExchanger:
         elif self._shape != (tuple(fields[0].shape), fields[0].dtype, len(fields)):
             raise RuntimeError("this exchanger's buffers were sized for another field shape, dtype or field count")
 
-    def _geometry(self, fields: tuple[Tensor, ...], rows: tuple[int, int]):
+    def _launch(self, entry: str, lanes: list[dict], fields: tuple[Tensor, ...], extra: tuple, stream: torch.cuda.Stream) -> None:
+        """One launch per pair of neighbours: both sides of a band travel at the same time."""
         like = fields[0]
         row_bytes = like.shape[2] * like.shape[3] * like.element_size()
-        r0, r1 = rows[0] - self.elo, rows[1] - self.elo
-        bases = (ctypes.c_void_p * len(fields))(*[f.data_ptr() + r0 * row_bytes for f in fields])
-        return bases, len(fields), like.shape[0], (r1 - r0) * row_bytes, like.shape[1] * row_bytes
+        count = len(fields)
+        with torch.cuda.device(self.device):
+            for first in range(0, len(lanes), 2):
+                group = lanes[first:first + 2]
+                n = len(group)
+                bases = (ctypes.c_void_p * (n * count))(*[f.data_ptr() + (lane["rows"][0] - self.elo) * row_bytes for lane in group for f in fields])
+                slabs = (ctypes.c_int64 * n)(*[(lane["rows"][1] - lane["rows"][0]) * row_bytes for lane in group])
+                pointers = lambda key: (ctypes.c_void_p * n)(*[lane[key] for lane in group])
+                steps = (ctypes.c_uint32 * n)(*[lane["step"] for lane in group])
+                self._lib.call(entry, n, bases, count, like.shape[0], slabs, like.shape[1] * row_bytes, pointers("buffer"), *extra,
+                               pointers("wait"), pointers("ticket"), pointers("signal"), steps, stream.cuda_stream)
 
     def _send(self, kind: str, fields: tuple[Tensor, ...], stream: torch.cuda.Stream) -> None:
-        with torch.cuda.device(self.device):
-            for other, theirs, mine in self.peers:
-                rows = theirs if kind == "fill" else mine  # rows of MY extended band that go to `other`
-                if rows is None:
-                    continue
-                self.steps[(other, kind)] += 1  # one counter per (neighbour, kind): its send and its landing advance together
-                step = self.steps[(other, kind)]
-                there, here = self.remote[other][(self.rank, kind)], self.layout[(other, kind)]
-                base = self.mapped[other].value
-                self._lib.call("gm_peer_send", *self._geometry(fields, rows), base + there["buffer"], self.block.value + here["ack"],
-                               self.block.value + here["send_ticket"], base + there["data"], step, stream.cuda_stream)
+        lanes = []
+        for other, theirs, mine in self.peers:
+            rows = theirs if kind == "fill" else mine  # rows of MY extended band that go to `other`
+            if rows is None:
+                continue
+            self.steps[(other, kind)] += 1  # one counter per (neighbour, kind): its send and its landing advance together
+            there, here = self.remote[other][(self.rank, kind)], self.layout[(other, kind)]
+            base = self.mapped[other].value
+            lanes.append({"rows": rows, "step": self.steps[(other, kind)], "buffer": base + there["buffer"], "wait": self.block.value + here["ack"],
+                          "ticket": self.block.value + here["send_ticket"], "signal": base + there["data"]})
+        if lanes:
+            self._launch("gm_peer_send_many", lanes, fields, (), stream)
 
     def _land(self, kind: str, fields: tuple[Tensor, ...], stream: torch.cuda.Stream) -> None:
         code = self._lib.dtype_code(fields[0].dtype) if fields[0].dtype in (torch.float32, torch.bfloat16) else 0
-        with torch.cuda.device(self.device):
-            for other, theirs, mine in self.peers:
-                rows = mine if kind == "fill" else theirs  # rows of MY extended band that `other` sent
-                if rows is None:
-                    continue
-                # the landing of the step whose send has just been counted; when this rank sends nothing to `other` in this
-                # kind of exchange the counter advances here
-                outgoing = theirs if kind == "fill" else mine
-                if outgoing is None:
-                    self.steps[(other, kind)] += 1
-                step = self.steps[(other, kind)]
-                there, here = self.remote[other][(self.rank, kind)], self.layout[(other, kind)]
-                base = self.mapped[other].value
-                self._lib.call("gm_peer_land", *self._geometry(fields, rows), self.block.value + here["buffer"], int(kind == "reduce"), code,
-                               self.block.value + here["data"], self.block.value + here["land_ticket"], base + there["ack"], step,
-                               stream.cuda_stream)
+        lanes = []
+        for other, theirs, mine in self.peers:
+            rows = mine if kind == "fill" else theirs  # rows of MY extended band that `other` sent
+            if rows is None:
+                continue
+            # the landing of the step whose send has just been counted; when this rank sends nothing to `other` in this
+            # kind of exchange the counter advances here
+            if (theirs if kind == "fill" else mine) is None:
+                self.steps[(other, kind)] += 1
+            there, here = self.remote[other][(self.rank, kind)], self.layout[(other, kind)]
+            base = self.mapped[other].value
+            lanes.append({"rows": rows, "step": self.steps[(other, kind)], "buffer": self.block.value + here["buffer"],
+                          "wait": self.block.value + here["data"], "ticket": self.block.value + here["land_ticket"], "signal": base + there["ack"]})
+        if lanes:
+            self._launch("gm_peer_land_many", lanes, fields, (int(kind == "reduce"), code), stream)
 
     def _zero_halo(self, grads: tuple[Tensor, ...], stream: torch.cuda.Stream) -> None:
         with torch.cuda.stream(stream):

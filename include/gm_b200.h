@@ -468,6 +468,14 @@ int gm_peer_send(void* const* fields, int n_fields, int64_t batch, int64_t slab_
 int gm_peer_land(void* const* fields, int n_fields, int64_t batch, int64_t slab_bytes, int64_t sample_bytes, void* local_buffer,
                  int add, int dtype, const uint32_t* local_data_flag, uint32_t* local_ticket, uint32_t* remote_ack, uint32_t step,
                  void* stream);
+/* The same for n_lanes (1 or 2) neighbours in ONE launch (the transfers to / from both sides of a band overlap): every
+ * per-neighbour argument is an array of n_lanes; fields holds n_lanes * n_fields pointers, neighbour-major. */
+int gm_peer_send_many(int n_lanes, void* const* fields, int n_fields, int64_t batch, const int64_t* slab_bytes, int64_t sample_bytes,
+                      void* const* remote_buffers, const uint32_t* const* local_acks, uint32_t* const* local_tickets,
+                      uint32_t* const* remote_data_flags, const uint32_t* steps, void* stream);
+int gm_peer_land_many(int n_lanes, void* const* fields, int n_fields, int64_t batch, const int64_t* slab_bytes, int64_t sample_bytes,
+                      void* const* local_buffers, int add, int dtype, const uint32_t* const* local_data_flags,
+                      uint32_t* const* local_tickets, uint32_t* const* remote_acks, const uint32_t* steps, void* stream);
 int gm_peer_error(int* code);
 
 #ifdef __cplusplus

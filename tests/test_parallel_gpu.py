@@ -210,3 +210,52 @@ def test_peer_protocol_on_one_gpu():
         finally:
             torch.cuda.synchronize()
             _lib.call("gm_peer_free", block)
+
+
+def test_peer_protocol_two_neighbours_in_one_launch():
+    """The two-neighbour form of the send / landing kernels, again with this process's own block standing in for both
+    neighbours' (every flag is already raised when its kernel starts): two lanes with different row ranges in one launch."""
+    import ctypes
+
+    from gm_attention_b200 import _lib
+
+    device = torch.device("cuda", 0)
+    batch, rows, nlon, width = 2, 12, 8, 24
+    ranges = [(0, 3), (8, 10)]
+    dtype = torch.bfloat16
+    row_bytes = nlon * width * 2
+    sample = rows * row_bytes
+    slabs = [(b - a) * row_bytes for a, b in ranges]
+    offsets = [0, 2 * batch * slabs[0]]
+    buffers_end = offsets[1] + 2 * batch * slabs[1]
+    block, handle = ctypes.c_void_p(), (ctypes.c_ubyte * 64)()
+    _lib.call("gm_peer_alloc", buffers_end + 8 * 128, ctypes.byref(block), ctypes.addressof(handle))
+    word = lambda lane, i: block.value + buffers_end + 128 * (4 * lane + i)  # per lane: data flag, acknowledgement, send / land ticket
+    array = lambda kind, values: (kind * len(values))(*values)
+    try:
+        gen = torch.Generator(device="cuda").manual_seed(4)
+        for step in (1, 2):
+            src = [torch.randn(batch, rows, nlon, width, generator=gen, device=device).to(dtype) for _ in range(2)]
+            dst = [torch.randn(batch, rows, nlon, width, generator=gen, device=device).to(dtype) for _ in range(2)]
+            before = [d.clone() for d in dst]
+            bases = lambda fields: array(ctypes.c_void_p, [f.data_ptr() + a * row_bytes for a, _ in ranges for f in fields])
+            stream = torch.cuda.current_stream(device).cuda_stream
+            common = (2, batch, array(ctypes.c_int64, slabs), sample, array(ctypes.c_void_p, [block.value + o for o in offsets]))
+            steps = array(ctypes.c_uint32, [step, step])
+            _lib.call("gm_peer_send_many", 2, bases(src), *common, array(ctypes.c_void_p, [word(l, 1) for l in range(2)]),
+                      array(ctypes.c_void_p, [word(l, 2) for l in range(2)]), array(ctypes.c_void_p, [word(l, 0) for l in range(2)]), steps, stream)
+            add = step == 2
+            _lib.call("gm_peer_land_many", 2, bases(dst), *common, int(add), _lib.dtype_code(dtype), array(ctypes.c_void_p, [word(l, 0) for l in range(2)]),
+                      array(ctypes.c_void_p, [word(l, 3) for l in range(2)]), array(ctypes.c_void_p, [word(l, 1) for l in range(2)]), steps, stream)
+            torch.cuda.synchronize()
+            code = ctypes.c_int(-1)
+            _lib.call("gm_peer_error", ctypes.byref(code))
+            assert code.value == 0
+            for s_, d_, b_ in zip(src, dst, before):
+                want = b_.clone()
+                for a, b in ranges:
+                    want[:, a:b] = (b_[:, a:b].float() + s_[:, a:b].float()).to(dtype) if add else s_[:, a:b]
+                assert torch.equal(d_, want)
+    finally:
+        torch.cuda.synchronize()
+        _lib.call("gm_peer_free", block)
