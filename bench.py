@@ -67,7 +67,8 @@ def parse() -> argparse.Namespace:
                    help="neighbourhood radius in lattice row spacings (default: the workload's own, 3); other values are for profiling")
     p.add_argument("--overlap", action="store_true",
                    help="N > 1: run the layer around the halo exchange (interior rows while the halos travel) instead of exchanging "
-                        "before / after it; measured equal within 1 %% at N = 8 (the exchange is latency, not bandwidth), so off by default")
+                        "before / after it; bit-identical results; with the peer-memory exchange measured 0.6 %% faster at N = 4 and 2 %% slower "
+                        "at N = 8 (the split launches cost more than the exchange they hide), so off by default")
     p.add_argument("--halo", choices=["auto", "peer", "native", "native-slabs", "torch"], default="auto",
                    help="N > 1: peer = the library's own copy kernels storing into the neighbour's mapped buffer (needs GPUs that can map each "
                         "other's memory); native = the library's NCCL groups issued from C, one packed message per neighbour and direction "
