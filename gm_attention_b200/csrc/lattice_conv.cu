@@ -7,7 +7,7 @@
 // longitude every one of those quantities depends on (target row, source row, longitude offset) only, and
 // z -> A z + w B conj(z) is a real-linear map of the plane, so the whole edge collapses into ONE real 2 x 2 matrix per
 // (table entry, complex copy) and one real factor per (entry, scalar channel); the caller folds the coefficients into
-// that table (gm_attention_b200/lattice_conv.py: plain tensor algebra on ~45 000 entries, differentiable), and the
+// that table (gm_attention_b200/nn/lattice_depthwise.py: fold; plain tensor algebra on ~45 000 entries, differentiable), and the
 // kernels here are
 //
 //   apply       y[i, l] = sum over entries (j, d) of row i   M[entry] x[j, l + lo + d]      (forward; with the transposed
