@@ -91,3 +91,77 @@ def test_fold_is_the_reference_message():
         torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-5)
         column += 4 * copies
         copy += copies
+
+
+def _apply_on_the_host(x, table, cnt, lo, off, items, nlat, nlon, halo, transpose):
+    """What ``gm_lattice_conv_apply`` computes, as numpy loops over (target row, window, offset)."""
+    y = np.zeros_like(x)
+    grid = x.reshape(nlat, nlon, -1)
+    out = y.reshape(nlat, nlon, -1)
+    span = 2 * halo + 1
+    for i in range(nlat):
+        for c in range(span):
+            j = i + c - halo
+            n = int(cnt[i, c])
+            if not (0 <= j < nlat) or n == 0:
+                continue
+            for d in range(n):
+                entry = table[int(off[i, c]) + d]
+                source = np.roll(grid[j], -(int(lo[i, c]) + d), axis=0)  # source[l] = x[j, l + lo + d]
+                for kind, col, fcol in items:
+                    if kind == 1:
+                        out[i, :, col] += entry[fcol] * source[:, col]
+                        out[i, :, col + 1] += entry[fcol + 1] * source[:, col + 1]
+                    else:
+                        m = entry[fcol:fcol + 4].reshape(2, 2)
+                        m = m.T if transpose else m
+                        out[i, :, col] += m[0, 0] * source[:, col] + m[0, 1] * source[:, col + 1]
+                        out[i, :, col + 1] += m[1, 0] * source[:, col] + m[1, 1] * source[:, col + 1]
+    return y
+
+
+@pytest.mark.parametrize("normalize", [False, True])
+def test_tables_and_fold_reproduce_the_depthwise_op_on_the_host(normalize):
+    """The host side of the lattice convolution -- windows, entry origins, transposed entry order, items, fold -- without a
+    GPU: the table applied along the windows by plain numpy loops equals the reference's depthwise op (C oracle) on the
+    same coefficients expanded to every edge, forward and for the field gradient (transposed windows, transposed matrices)."""
+    import math
+    from types import SimpleNamespace
+
+    from tests.helpers import make_case, seeded
+
+    from gm_attention_b200.nn.lattice_depthwise import conv_tables, fold
+
+    head = {0: 4, 1: 3, 2: 2}
+    c = make_case(8, 16, 2.5 * math.pi / 8, head, 1, dtype=np.float64)
+    weights = c.weights
+    if normalize:
+        mass = np.add.reduceat(c.weights, c.row_ptr[:-1])
+        weights = c.weights / np.repeat(np.maximum(mass, 1e-12), np.diff(c.row_ptr))
+    t = torch.from_numpy
+    geometry = SimpleNamespace(transport=t(c.transport.astype(np.float32)), angular=t(c.angular.astype(np.float32)), rho=t(c.rho.astype(np.float32)),
+                               bias=t(c.bias.astype(np.float32)), inside=t(c.inside), row_ptr=t(c.row_ptr), source=t(c.source))
+    tables = conv_tables(geometry, t((c.rho * c.radius).astype(np.float32)), t(weights.astype(np.float32)), descriptor_rows(c.head_type, 1), c.nlat, c.nlon)
+    lat = tables.lattice
+    assert tables.n_entries * c.nlon == c.source.shape[0] and tables.table_width == 4 + 4 * 5
+    a0, w = 4, 20
+    rc_t, = seeded((tables.n_entries, a0), 51, np.float32)
+    cc_t, = seeded((tables.n_entries, w), 52, np.float32)
+    table = fold(t(rc_t), t(cc_t), tables).numpy().astype(np.float64)
+    v, g = seeded((c.n_nodes, c.width), 53, np.float64, 2)
+    # the same coefficients on every edge of an entry
+    span = 2 * lat.halo + 1
+    cnt, lo, off = (x.numpy() for x in (lat.win_cnt, lat.win_lo, lat.win_off))
+    ri, li, rj, lj = c.target // c.nlon, c.target % c.nlon, c.source // c.nlon, c.source % c.nlon
+    win = (ri, rj - ri + lat.halo)
+    entry = off[win] + (lj - li - lo[win]) % c.nlon
+    args = (rc_t[entry].astype(np.float64)[None], cc_t[entry].astype(np.float64)[None], c.transport, c.angular, c.rho, weights, c.desc, c.row_ptr,
+            c.source, a0, w)
+    want = O.conv_forward(v, *args)
+    want_dv, _, _ = O.conv_backward(g, v, *args)
+    items = tables.items.numpy().tolist()
+    got = _apply_on_the_host(v, table, cnt, lo, off, items, c.nlat, c.nlon, lat.halo, False)
+    np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-5 * np.abs(want).max())
+    t_table = table[lat.t_entry.numpy()]
+    got_dv = _apply_on_the_host(g, t_table, lat.t_win_cnt.numpy(), lat.t_win_lo.numpy(), lat.t_win_off.numpy(), items, c.nlat, c.nlon, lat.halo, True)
+    np.testing.assert_allclose(got_dv, want_dv, rtol=1e-5, atol=1e-5 * np.abs(want_dv).max())
