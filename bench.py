@@ -624,6 +624,7 @@ def run_ours(args: argparse.Namespace, cfg: dict) -> None:
                     halo.reduce_halos(dk.view(shape), dv.view(shape))
                 for dst, src in zip(outs_host, (out, dq, dk, dv)):
                     dst.copy_(src.view(shape), non_blocking=True)
+        barrier()  # pinning hundreds of MB takes the ranks different times: the bounded waits of the exchange assume aligned starts
         for _ in range(2):
             e2e_step()
         e2e_join()
