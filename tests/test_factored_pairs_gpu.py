@@ -38,7 +38,7 @@ FACTORED_CASES = [
     ({0: 2, 1: 2}, {0: 2, 1: 3}, 5),
     ({0: 8, 1: 8, 2: 8}, {0: 4, 1: 4, 2: 4}, 17),  # value kernel of the 32 x 64 configuration: 13 blocks, wc 48, wr 4
     ({1: 3}, {0: 2, 2: 2}, 4),                       # no real block
-    ({0: 32, 1: 32, 2: 32, 3: 32}, {0: 8, 1: 8, 2: 8, 3: 8}, 17),  # the 128 x 256 layer (8 x (m <= 3) -> 32 x (m <= 3)): packed width 392 > the reference's 320
+    ({0: 32, 1: 32, 2: 32, 3: 32}, {0: 8, 1: 8, 2: 8, 3: 8}, 17),  # the 128 x 256 layer (32 x (m <= 3) -> 8 x (m <= 3)): packed width 392 > the reference's 320
 ]
 
 
